@@ -1,0 +1,137 @@
+/*
+ * moe_b200 -- C ABI of the B200 (sm_100a) MoE-layer hot path.
+ *
+ * The reference project exposes this path as Python functions only (package
+ * `kernels`); it has no FFI of its own.  Each entry point below names the
+ * reference function (file:line inside the reference project) whose device work
+ * it replaces.  A Python binding calls these through ctypes on the caller's
+ * thread; see INTEGRATION.md for the stub.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer, borrowed for the duration of the call,
+ *     unless the parameter comment says "host";
+ *   - the library never allocates or frees memory on behalf of these calls:
+ *     scratch is passed in as (ws, ws_bytes), sized by the matching *_workspace
+ *     query (the one exception is declared at the end of this file);
+ *   - every call only enqueues work on `stream` (a cudaStream_t passed as void*)
+ *     and returns without synchronising;
+ *   - return value: 0 ok; negative = argument / shape error found on the host
+ *     before any launch; positive = CUDA runtime error code.  A message for the
+ *     last non-zero return on the calling thread is at moe_last_error();
+ *   - kernels that wait on barriers do so with a time limit; if a limit is hit
+ *     the kernel stores a non-zero code in the caller's `status` word (device
+ *     int32[MOE_STATUS_WORDS], may be NULL) and returns normally.
+ */
+#ifndef MOE_B200_H_
+#define MOE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_OK 0
+#define MOE_ERR_ARG (-1)          /* bad pointer / size / alignment            */
+#define MOE_ERR_UNSUPPORTED (-2)  /* shape outside what the kernels cover      */
+#define MOE_ERR_WORKSPACE (-3)    /* ws_bytes smaller than the query's answer  */
+#define MOE_ERR_DEVICE (-4)       /* not an sm_100 device                      */
+
+#define MOE_STATUS_WORDS 4        /* int32 words in a status buffer            */
+
+/* softmax / selection convention of the router */
+#define MOE_TOPK_MODE_B 0         /* top-k of logits, softmax over the k        */
+#define MOE_TOPK_MODE_A 1         /* softmax over N, pick k, no renormalisation */
+#define MOE_TOPK_MODE_A_RENORM 2  /* as A, then scores / sum(scores)            */
+
+/* epilogue of the expert GEMM */
+#define MOE_GEMM_PLAIN 0          /* Y[dst(r)] = A[r] . B[e]^T              (bf16) */
+#define MOE_GEMM_SILU_GATE 1      /* Y[r] = silu(A[r].Bg[e]^T) * (A[r].Bu[e]^T)    */
+#define MOE_GEMM_SCALE_SCATTER 2  /* Y[dst(r)] = w[r] * (A[r] . B[e]^T)            */
+#define MOE_GEMM_PLAIN_F32 3      /* as PLAIN, fp32 output                         */
+
+const char* moe_last_error(void);
+int moe_abi_version(void);
+
+/* Device properties the host side needs (SM count, sm_100 check). host out. */
+int moe_device_info(int device, int* sm_count, int* cc_major, int* cc_minor);
+
+/* ---- router: fused top-k + softmax -------------------------------------------
+ * Replaces kernels/topk_softmax_baseline.py:39-66 (mode B), :15-36 (mode A),
+ * :223-236 (mode A_RENORM) and the GPU op kernels/topk_softmax_tilelang.py:1103-1135.
+ * logits fp32 [M,N] with row stride ld (elements).  scores fp32 [M,k]; indices
+ * int64 [M,k] and/or indices32 int32 [M,k] (either may be NULL, not both).
+ * Output is sorted by value descending; equal values come lowest index first;
+ * -0.0 == +0.0; NaN ranks above every number.  No workspace.
+ * N <= 1024 and k <= 64: one warp per row.  Otherwise (N <= 131072, k <= 4096):
+ * radix select by a cluster of CTAs per row.
+ */
+int moe_topk_softmax(const float* logits, int64_t M, int64_t N, int64_t ld, int k, int mode,
+                     float* scores, int64_t* indices, int32_t* indices32, int32_t* status,
+                     void* stream);
+
+/* ---- permutation / histogram ---------------------------------------------------
+ * Replaces the argsort / bincount / cumsum of kernels/fusedmoe_baseline.py:123-134
+ * and the host loops of kernels/fusedmoe_tilelang.py:338-372 (no D2H sync).
+ * topk_idx: n = T*k expert ids, int64 (idx_is_int64 != 0) or int32, flattened
+ * row-major.  counts int32 [E]; offsets int32 [E+1] exclusive prefix (offsets[E]=n);
+ * perm int32 [n]: perm[p] = flat entry at expert-sorted position p (stable);
+ * inv int32 [n]: inverse of perm.  perm / inv may be NULL.  Ids outside [0,E)
+ * set status[0] and are skipped.
+ */
+size_t moe_route_histogram_workspace(int64_t n, int E);
+int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E, int32_t* counts,
+                        int32_t* offsets, int32_t* perm, int32_t* inv, void* ws, size_t ws_bytes,
+                        int32_t* status, void* stream);
+
+/* ---- row gather -----------------------------------------------------------------
+ * dst[p, :] = src[perm[p] / div, :] for p < n_rows (rows of `cols` bf16, 16-byte
+ * aligned, cols % 8 == 0).  Replaces the expert-stacking copy loops of
+ * kernels/fusedmoe_tilelang.py:346-355 and X[sorted] in grouped_gemm_tilelang.py:700.
+ * If w_src != NULL also w_dst[p] = w_src[perm[p]] (fp32 routing weights).
+ * n_rows_dev (device int32, may be NULL) overrides n_rows when it is smaller.
+ */
+int moe_gather_rows(const void* src, const int32_t* perm, int div, int64_t n_rows, int64_t cols,
+                    void* dst, const float* w_src, float* w_dst, void* stream);
+
+/* ---- expert grouped GEMM (tcgen05 / TMEM / TMA) -----------------------------------
+ * Replaces kernels/grouped_gemm_baseline.py:14-57, kernels/grouped_gemm_tilelang.py:119-214
+ * and the expert matmuls of kernels/fusedmoe_baseline.py:93-103,148-158 /
+ * kernels/fusedmoe_tilelang.py:123-238.
+ *   A        bf16 [rows, K] row-major, rows sorted by expert (expert e owns rows
+ *            offsets[e] .. offsets[e+1]-1)
+ *   B, B2    bf16 [E, N, K] (the reference's (E,I,H) layout: K contiguous);
+ *            B2 is the "up" weight for MOE_GEMM_SILU_GATE, else NULL
+ *   offsets  int32 [E+1] on the device (output of moe_route_histogram)
+ *   dst_rows int32 [rows] or NULL: output row of sorted row r (PLAIN, SCALE_SCATTER)
+ *   row_w    fp32 [rows]: routing weight of sorted row r (SCALE_SCATTER)
+ *   Y        bf16 [*, N] row stride ldy (fp32 for MOE_GEMM_PLAIN_F32)
+ *   max_rows upper bound of offsets[E] known on the host (sizes the TMA map and
+ *            the tile bound); rows beyond offsets[E] are never written
+ * K % 8 == 0, N % 8 == 0.  Workspace: none.
+ */
+int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2,
+                     const int32_t* offsets, const int32_t* dst_rows, const float* row_w, void* Y,
+                     int64_t ldy, int64_t max_rows, int K, int N, int E, int32_t* status,
+                     void* stream);
+
+/* ---- combine ----------------------------------------------------------------------
+ * out[t,:] = (shared ? shared[t,:] : 0) + sum_{s<k} Yk[t*k+s,:], fp32 sum in slot
+ * order, rounded once to bf16.  Replaces scatter_reduce_ + add of
+ * kernels/fusedmoe_baseline.py:90,161-166.  H % 8 == 0.
+ */
+int moe_combine(const void* Yk, const void* shared, int64_t T, int k, int64_t H, void* out,
+                void* stream);
+
+/* ---- router logits ------------------------------------------------------------------
+ * logits[t,e] = sum_h x[t,h] * Wr[e,h], bf16 inputs, fp32 accumulate and output.
+ * Replaces kernels/fusedmoe_baseline.py:72.  H % 8 == 0.
+ */
+int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, float* logits,
+                      int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H_ */

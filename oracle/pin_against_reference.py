@@ -1,0 +1,171 @@
+"""Pin the oracle to the reference and (re)generate ``tests/golden/*.npz``.
+
+Runs only where the reference checkout is available (argument or $MOE_REFERENCE_DIR).
+It loads the reference's own ``kernels/*_baseline.py`` by file path (they need only
+torch), runs them on CPU on seeded inputs, asserts that ``oracle/moe_oracle.py``
+reproduces them (bit-exact for routing, exact-or-tolerance for float outputs),
+and stores the reference's outputs as fixtures.  The fixtures are what travels:
+tests replay them without the reference present.
+
+    python oracle/pin_against_reference.py /path/to/reference
+"""
+from __future__ import annotations
+
+import hashlib
+import importlib.util
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent
+sys.path.insert(0, str(ROOT))
+from oracle import moe_oracle as O  # noqa: E402
+
+GOLDEN = ROOT / "tests" / "golden"
+
+
+def _load(ref_dir: Path, name: str):
+    spec = importlib.util.spec_from_file_location("ref_" + name, ref_dir / "kernels" / (name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _sha(t: torch.Tensor) -> str:
+    return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def _bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy().copy()
+
+
+def pin_topk(ref):
+    # config 1: 320 x 128, k=6, seed 0
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(320, 128, generator=g)
+    out = {"logits": logits.numpy()}
+    for name, fn, mode in (("B", ref.topk_softmax_fused, "B"), ("A", ref.topk_softmax_separate, "A"),
+                           ("AR", ref.topk_softmax_conv_a_renorm, "A_renorm")):
+        rs, ri = fn(logits, 6)
+        os_, oi = O.topk_softmax(logits, 6, mode)
+        ties = O.rows_with_ties(logits, 6)
+        assert not ties.any(), "seed 0 config-1 input is expected to be tie-free"
+        assert torch.equal(ri, oi), f"mode {name}: index mismatch vs reference"
+        assert torch.allclose(rs, os_, rtol=1e-6, atol=0), f"mode {name}: score mismatch"
+        out["scores_" + name] = rs.numpy()
+        out["idx_" + name] = ri.numpy().astype(np.int32)
+    assert O.selection_is_score_stable(logits, 6).all()
+    np.savez_compressed(GOLDEN / "topk_c1.npz", **out)
+
+    # config 4: 64 x 32768, k=2048, seed 0; fixture keeps the first 8 rows of output
+    g = torch.Generator().manual_seed(0)
+    big = torch.randn(64, 32768, generator=g)
+    rs, ri = ref.topk_softmax_fused(big, 2048)
+    os_, oi = O.topk_softmax(big, 2048, "B")
+    # values are tie-independent: gathered logits must be bit-equal
+    assert torch.equal(torch.gather(big, 1, ri), torch.gather(big, 1, oi))
+    assert torch.allclose(rs, os_, rtol=1e-6, atol=0)
+    # indices: equal as sets on every row, equal in order wherever the reference's
+    # order is already lowest-index-first inside equal-value runs
+    assert torch.equal(torch.sort(ri, 1).values, torch.sort(oi, 1).values)
+    differs = (ri != oi).any(1)
+    vals = torch.gather(big, 1, oi)
+    has_tie = (vals[:, 1:] == vals[:, :-1]).any(1)
+    assert not (differs & ~has_tie).any(), "order differs on a row without equal values"
+    np.savez_compressed(GOLDEN / "topk_c4_rows8.npz", sha256_logits=_sha(big), seed=0,
+                        scores_ref=rs[:8].numpy(), idx_ref=ri[:8].numpy().astype(np.int32),
+                        idx_stable=oi[:8].numpy().astype(np.int32),
+                        rows_where_ref_order_differs=differs.nonzero().flatten().numpy())
+
+    # a tie-heavy case: quantised logits, every row full of equal values
+    g = torch.Generator().manual_seed(3)
+    q = torch.round(torch.randn(64, 96, generator=g) * 2) / 2
+    rs, ri = ref.topk_softmax_fused(q, 8)
+    os_, oi = O.topk_softmax(q, 8, "B")
+    assert torch.equal(torch.gather(q, 1, ri), torch.gather(q, 1, oi))
+    assert torch.allclose(rs, os_, rtol=1e-6, atol=0)
+    np.savez_compressed(GOLDEN / "topk_ties.npz", logits=q.numpy(), scores_ref=rs.numpy(),
+                        idx_stable=oi.numpy().astype(np.int32))
+
+
+def pin_histogram():
+    # the call sites of kernels/fusedmoe_baseline.py:123-134 on a seeded routing table
+    g = torch.Generator().manual_seed(7)
+    T, k, E = 200, 4, 16
+    idx = torch.argsort(torch.rand(T, E, generator=g), dim=1)[:, :k].contiguous()
+    idx = torch.where(idx == 11, torch.full_like(idx, 3), idx)  # expert 11 empty, 3 doubled
+    flat = idx.view(-1)
+    sorted_idx = flat.argsort()
+    counts = flat.bincount(minlength=E).cpu().numpy()
+    offsets = counts.cumsum()
+    c, o, perm, inv = O.route_histogram(idx, E)
+    assert np.array_equal(c.numpy(), counts)
+    assert np.array_equal(o.numpy()[1:], offsets)
+    # the reference's argsort is unstable: same experts in the same segments
+    assert torch.equal(flat[sorted_idx], flat[perm.long()])
+    for e in range(E):
+        s, t = int(o[e]), int(o[e + 1])
+        assert torch.equal(torch.sort(sorted_idx[s:t]).values, perm[s:t].long())
+    np.savez_compressed(GOLDEN / "histogram.npz", topk_idx=idx.numpy().astype(np.int32), E=E,
+                        counts=counts.astype(np.int32), offsets_inclusive=offsets.astype(np.int32),
+                        perm_stable=perm.numpy(), inv=inv.numpy())
+
+
+def pin_grouped_gemm(ref):
+    g = torch.Generator().manual_seed(11)
+    T, H, I, E = 96, 128, 64, 5
+    X = torch.randn(T, H, generator=g).bfloat16()
+    W = (torch.randn(E, I, H, generator=g) * 0.02).bfloat16()
+    idx = torch.randint(0, E - 1, (T,), generator=g)          # expert E-1 stays empty
+    y_bf16 = ref.grouped_gemm_loop(X, W, idx)
+    y_f32 = ref.grouped_gemm_loop(X.float(), W.float(), idx)
+    o_f32 = O.grouped_gemm(X, W, idx)
+    o_bf16 = O.grouped_gemm(X, W, idx, out_dtype=torch.bfloat16)
+    assert torch.allclose(o_f32, y_f32, rtol=1e-6, atol=1e-7)
+    assert torch.allclose(o_bf16.float(), y_bf16.float(), rtol=1e-2, atol=2e-2)
+    np.savez_compressed(GOLDEN / "grouped_gemm.npz", X=_bf16_bits(X), W=_bf16_bits(W),
+                        idx=idx.numpy().astype(np.int32), y_ref_f32=y_f32.numpy(),
+                        y_ref_bf16=_bf16_bits(y_bf16))
+
+
+def pin_fusedmoe(ref):
+    cfg = dict(batch_size=1, seq_len=48, d_hidden=128, d_expert=64, n_routed_experts=6,
+               n_shared_experts=1, n_experts_per_token=2)
+    x, w = ref.generate_fusedmoe_inputs(**cfg, dtype=torch.bfloat16, device="cpu", seed=42)
+    x2, w2 = O.make_fusedmoe_inputs(**cfg, dtype=torch.bfloat16, seed=42)
+    assert torch.equal(x, x2) and all(torch.equal(w[n], w2[n]) for n in w), "input generator drifted"
+    names = ["router_weight", "shared_gate", "shared_up", "shared_down", "routed_gate", "routed_up",
+             "routed_down"]
+    y_f32 = ref.fusedmoe_pytorch(x.float(), *[w[n].float() for n in names], 2)
+    y_bf16 = ref.fusedmoe_pytorch(x, *[w[n] for n in names], 2)
+    o_f32, sc, ix = O.fusedmoe(x, *[w[n] for n in names], 2, return_routing=True)
+    assert torch.allclose(o_f32, y_f32, rtol=1e-4, atol=1e-5), (o_f32 - y_f32).abs().max()
+    # the routing used inside the reference (softmax over E, topk unsorted) as a set
+    logits = x.float().view(-1, 128) @ w["router_weight"].float().T
+    rsc, rix = torch.topk(torch.softmax(logits, -1), 2, dim=-1, sorted=False)
+    assert torch.equal(torch.sort(rix, 1).values, torch.sort(ix, 1).values)
+    fix = {n: _bf16_bits(w[n]) for n in names}
+    np.savez_compressed(GOLDEN / "fusedmoe.npz", x=_bf16_bits(x), y_ref_f32=y_f32.numpy(),
+                        y_ref_bf16=_bf16_bits(y_bf16), topk_idx=ix.numpy().astype(np.int32),
+                        topk_scores=sc.numpy(), **fix)
+
+
+def main():
+    ref_dir = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MOE_REFERENCE_DIR", ""))
+    if not (ref_dir / "kernels" / "topk_softmax_baseline.py").is_file():
+        raise SystemExit("reference checkout not found: pass its path")
+    GOLDEN.mkdir(parents=True, exist_ok=True)
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    pin_topk(_load(ref_dir, "topk_softmax_baseline"))
+    pin_histogram()
+    pin_grouped_gemm(_load(ref_dir, "grouped_gemm_baseline"))
+    pin_fusedmoe(_load(ref_dir, "fusedmoe_baseline"))
+    print("oracle pinned; fixtures written to", GOLDEN)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,44 @@
+"""The C-ABI library loads and exports every symbol the header declares (no GPU needed)."""
+import ctypes
+import re
+
+from conftest import ROOT
+from tilelang_moe_b200 import _lib
+
+
+def _declared():
+    text = (ROOT / "include" / "moe_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared()
+    assert len(names) >= 9
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/moe_b200.h but not exported"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes prototypes and header disagree"
+
+
+def test_version_and_error_channel(lib):
+    assert lib.moe_abi_version() == 1
+    # argument errors are detected on the host before any CUDA call
+    rc = lib.moe_topk_softmax(None, 4, 8, 8, 2, 0, None, None, None, None, None)
+    assert rc == -1
+    assert b"null" in lib.moe_last_error()
+    rc = lib.moe_topk_softmax(ctypes.c_void_p(16), 4, 8, 8, 9, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), None, None, None)
+    assert rc == -1 and b"bad shape" in lib.moe_last_error()
+    rc = lib.moe_grouped_gemm(0, None, None, None, None, None, None, None, 8, 16, 12, 8, 1, None, None)
+    assert rc == -1 and b"multiples of 8" in lib.moe_last_error()
+    rc = lib.moe_route_histogram(None, 1, 10, 4, None, None, None, None, None, 0, None, None)
+    assert rc == -1
+    assert lib.moe_route_histogram_workspace(2048, 8) == 2 * 8 * 4
+    assert lib.moe_route_histogram_workspace(0, 8) == 0
+
+
+def test_cpu_tensors_are_rejected():
+    import pytest
+    import torch
+    from tilelang_moe_b200 import kernels
+    with pytest.raises(ValueError):
+        kernels.topk_softmax(torch.randn(4, 8), 2)

@@ -1,0 +1,96 @@
+"""tcgen05 grouped GEMM through the C ABI against the fp32-accumulated oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from oracle import moe_oracle as O
+from tilelang_moe_b200 import kernels, ops
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-2, 2e-2   # bf16 outputs vs fp32-accumulated reference
+
+
+def _bf16(a):
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+def _close(y, ref):
+    torch.testing.assert_close(y.float().cpu(), ref.float(), rtol=RTOL, atol=ATOL)
+
+
+def test_fixture(cuda, lib):
+    g = np.load(GOLDEN / "grouped_gemm.npz")
+    X, W = _bf16(g["X"]), _bf16(g["W"])
+    idx = torch.from_numpy(g["idx"].astype(np.int64))
+    y = kernels.grouped_gemm(X.to(cuda), W.to(cuda), idx.to(cuda))
+    ops.check_status(cuda)
+    assert y.shape == (96, 64) and y.dtype == torch.bfloat16
+    _close(y, torch.from_numpy(g["y_ref_f32"]))
+    _close(y, _bf16(g["y_ref_bf16"]))
+    # far tighter than the contract in practice: one rounding of an fp32 accumulation
+    assert (y.float().cpu() - torch.from_numpy(g["y_ref_f32"])).abs().max() < 4e-3
+
+
+def test_config2_top2(cuda, lib):
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(4096, 1024, generator=g).bfloat16()
+    W = (torch.randn(8, 256, 1024, generator=g) * 0.02).bfloat16()
+    idx = torch.argsort(torch.rand(4096, 8, generator=g), dim=1)[:, :2].contiguous()
+    y = kernels.grouped_gemm(X.to(cuda), W.to(cuda), idx.to(cuda))
+    ops.check_status(cuda)
+    assert y.shape == (4096, 2, 256)
+    _close(y, O.grouped_gemm(X, W, idx))
+    # the reference-equivalent flattened call gives the same rows
+    y1 = kernels.grouped_gemm(X.repeat_interleave(2, 0).to(cuda), W.to(cuda), idx.reshape(-1).to(cuda))
+    assert torch.equal(y1.view(4096, 2, 256), y)
+    # (E,H,I) layout option
+    y2 = kernels.grouped_gemm(X.to(cuda), W.transpose(1, 2).contiguous().to(cuda), idx.to(cuda), w_layout="EHI")
+    assert torch.equal(y2, y)
+
+
+@pytest.mark.parametrize("T,H,I,E", [(1, 64, 8, 1), (130, 72, 24, 3), (257, 128, 136, 4), (1000, 200, 264, 7),
+                                     (64, 4096, 128, 2), (3000, 512, 512, 16), (5, 64, 64, 32), (2048, 1024, 768, 5)])
+def test_ragged_shapes(cuda, lib, T, H, I, E):
+    g = torch.Generator().manual_seed(T + H + I)
+    X = torch.randn(T, H, generator=g).bfloat16()
+    W = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16()
+    idx = torch.randint(0, E, (T,), generator=g)
+    y = kernels.grouped_gemm(X.to(cuda), W.to(cuda), idx.to(cuda))
+    ops.check_status(cuda)
+    _close(y, O.grouped_gemm(X, W, idx))
+
+
+def test_all_rows_one_expert_and_empty_experts(cuda, lib):
+    g = torch.Generator().manual_seed(4)
+    X = torch.randn(700, 256, generator=g).bfloat16()
+    W = (torch.randn(6, 256, 256, generator=g) * 0.05).bfloat16()
+    idx = torch.full((700,), 4, dtype=torch.int64)
+    _close(kernels.grouped_gemm(X.to(cuda), W.to(cuda), idx.to(cuda)), O.grouped_gemm(X, W, idx))
+    ops.check_status(cuda)
+
+
+def test_epilogues(cuda, lib):
+    g = torch.Generator().manual_seed(6)
+    T, k, H, I, E = 500, 2, 256, 384, 6
+    x = torch.randn(T, H, generator=g).bfloat16()
+    Wg = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16()
+    Wu = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16()
+    Wd = (torch.randn(E, H, I, generator=g) * 0.06).bfloat16()
+    idx = torch.argsort(torch.rand(T, E, generator=g), dim=1)[:, :k].contiguous()
+    sc = torch.rand(T, k, generator=g)
+    _, offs, perm, _ = O.route_histogram(idx, E)
+    xs = x[perm.long() // k]
+    eid = torch.repeat_interleave(torch.arange(E), (offs[1:] - offs[:-1]).long())
+    act_ref = torch.nn.functional.silu(O.grouped_gemm(xs, Wg, eid)) * O.grouped_gemm(xs, Wu, eid)
+    act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, xs.to(cuda), Wg.to(cuda), offs.to(cuda), B2=Wu.to(cuda))
+    _close(act, act_ref)
+    w_sorted = sc.view(-1)[perm.long()]
+    yk = ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, act, Wd.to(cuda), offs.to(cuda), dst_rows=perm.to(cuda),
+                                 row_w=w_sorted.to(cuda))
+    yk_ref = torch.empty(T * k, H)
+    yk_ref[perm.long()] = O.grouped_gemm(act.cpu(), Wd, eid) * w_sorted[:, None]
+    _close(yk, yk_ref)
+    f32 = ops.grouped_gemm_sorted(ops.GEMM_PLAIN_F32, xs.to(cuda), Wg.to(cuda), offs.to(cuda))
+    torch.testing.assert_close(f32.cpu(), O.grouped_gemm(xs, Wg, eid), rtol=1e-4, atol=1e-4)
+    ops.check_status(cuda)

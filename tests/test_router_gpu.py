@@ -1,0 +1,120 @@
+"""TopK+softmax on the GPU through the C ABI, against the oracle and the reference fixtures."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from oracle import moe_oracle as O
+from tilelang_moe_b200 import kernels, ops
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-6  # fp32 softmax scores, relative
+
+
+def _check(logits_cpu, k, mode, dev, rtol=RTOL):
+    s_ref, i_ref = O.topk_softmax(logits_cpu, k, mode)
+    s, i = ops.topk_softmax(logits_cpu.to(dev), k, mode=mode)
+    ops.check_status(dev)
+    assert i.dtype == torch.int64 and s.dtype == torch.float32
+    assert torch.equal(i.cpu(), i_ref), f"indices differ (mode {mode}, shape {tuple(logits_cpu.shape)}, k={k})"
+    torch.testing.assert_close(s.cpu(), s_ref, rtol=rtol, atol=1e-30)
+    return s, i
+
+
+def test_config1_fixture(cuda, lib):
+    g = np.load(GOLDEN / "topk_c1.npz")
+    logits = torch.from_numpy(g["logits"]).to(cuda)
+    for tag, mode in (("B", "B"), ("A", "A"), ("AR", "A_renorm")):
+        s, i = kernels.topk_softmax(logits, 6, mode=mode)
+        assert np.array_equal(i.cpu().numpy(), g["idx_" + tag].astype(np.int64))
+        torch.testing.assert_close(s.cpu(), torch.from_numpy(g["scores_" + tag]), rtol=RTOL, atol=1e-30)
+
+
+def test_config4_radix_full(cuda, lib):
+    big = torch.randn(64, 32768, generator=torch.Generator().manual_seed(0))
+    s, i = _check(big, 2048, "B", cuda)
+    g = np.load(GOLDEN / "topk_c4_rows8.npz")
+    assert np.array_equal(i[:8].cpu().numpy(), g["idx_stable"].astype(np.int64))
+    torch.testing.assert_close(s[:8].cpu(), torch.from_numpy(g["scores_ref"]), rtol=RTOL, atol=1e-30)
+    # against an fp64 softmax of the selected values as well
+    v = torch.gather(big, 1, i.cpu()).double()
+    torch.testing.assert_close(s.cpu().double(), torch.softmax(v, -1), rtol=RTOL, atol=1e-30)
+
+
+def test_ties_fixture(cuda, lib):
+    g = np.load(GOLDEN / "topk_ties.npz")
+    s, i = kernels.topk_softmax(torch.from_numpy(g["logits"]).to(cuda), 8)
+    assert np.array_equal(i.cpu().numpy(), g["idx_stable"].astype(np.int64))
+    torch.testing.assert_close(s.cpu(), torch.from_numpy(g["scores_ref"]), rtol=RTOL, atol=1e-30)
+
+
+@pytest.mark.parametrize("M,N,k", [(1, 8, 2), (7, 16, 4), (33, 31, 5), (64, 64, 8), (512, 128, 8), (100, 160, 6),
+                                   (256, 256, 8), (50, 500, 32), (40, 512, 64), (16, 1000, 33), (9, 1024, 64),
+                                   (512, 8, 8), (3, 1, 1)])
+@pytest.mark.parametrize("mode", ["B", "A", "A_renorm"])
+def test_warp_path_shapes(cuda, lib, M, N, k, mode):
+    lg = torch.randn(M, N, generator=torch.Generator().manual_seed(M * 131 + N))
+    _check(lg, k, mode, cuda)
+
+
+@pytest.mark.parametrize("M,N,k", [(4, 2048, 2048), (5, 1025, 7), (3, 4096, 100), (2, 32768, 1), (6, 3000, 65),
+                                   (8, 512, 128), (2, 65536, 4096), (130, 8192, 256), (1, 131072, 2048),
+                                   (300, 2048, 96)])
+@pytest.mark.parametrize("mode", ["B", "A", "A_renorm"])
+def test_radix_path_shapes(cuda, lib, M, N, k, mode):
+    lg = torch.randn(M, N, generator=torch.Generator().manual_seed(M * 7 + N + k))
+    _check(lg, k, mode, cuda)
+
+
+def test_radix_ties_straddling_the_threshold(cuda, lib):
+    # heavy quantisation: many equal values exactly at the k-th place, spread over all slices
+    g = torch.Generator().manual_seed(5)
+    q = torch.round(torch.randn(16, 16384, generator=g) * 4) / 4
+    _check(q, 1000, "B", cuda)
+    _check(q, 77, "B", cuda)
+    const = torch.zeros(3, 5000)
+    _check(const, 1234, "B", cuda)
+
+
+def test_row_stride_and_unaligned(cuda, lib):
+    base = torch.randn(20, 300, generator=torch.Generator().manual_seed(2)).to(cuda)
+    view = base[:, 3:203]                      # ld=300, offset 3 floats: not 16-byte aligned
+    s, i = ops.topk_softmax(view, 5)
+    s_ref, i_ref = O.topk_softmax(view.cpu(), 5)
+    assert torch.equal(i.cpu(), i_ref)
+    big = torch.randn(4, 9001, generator=torch.Generator().manual_seed(3)).to(cuda)
+    s, i = ops.topk_softmax(big[:, 1:], 300)
+    s_ref, i_ref = O.topk_softmax(big[:, 1:].cpu(), 300)
+    assert torch.equal(i.cpu(), i_ref)
+
+
+def test_signed_zero_nan_and_inf(cuda, lib):
+    x = torch.tensor([[0.0, -0.0, 1.0, float("nan"), -0.0, 0.0, float("-inf"), float("inf")]])
+    _, i = ops.topk_softmax(x.to(cuda), 8)
+    assert i.cpu().tolist() == O.stable_topk(x, 8)[1].tolist() == [[3, 7, 2, 0, 1, 4, 5, 6]]
+    wide = torch.zeros(2, 4096)
+    wide[0, 100] = float("nan")
+    wide[1, 7] = -0.0
+    wide[1, 9] = 1.0
+    _, i = ops.topk_softmax(wide.to(cuda), 70)
+    assert torch.equal(i.cpu(), O.stable_topk(wide, 70)[1])
+
+
+def test_int32_indices_and_large_m(cuda, lib):
+    lg = torch.randn(70000, 128, generator=torch.Generator().manual_seed(9))
+    s_ref, i_ref = O.topk_softmax(lg, 6)
+    s, i64, i32 = ops.topk_softmax(lg.to(cuda), 6, also_int32=True)
+    assert torch.equal(i64.cpu(), i_ref) and torch.equal(i32.cpu().long(), i_ref)
+    torch.testing.assert_close(s.cpu(), s_ref, rtol=RTOL, atol=1e-30)
+
+
+def test_conventions_agree_like_the_reference_test(cuda, lib):
+    # reference tests/test_topk_softmax_conventions.py: same expert sets, A-renorm == B to fp32 rounding
+    for E, K in ((8, 2), (16, 4), (128, 8), (160, 6), (64, 8)):
+        lg = torch.randn(512, E, generator=torch.Generator().manual_seed(42)).to(cuda)
+        sb, ib = kernels.topk_softmax(lg, K, mode="B")
+        sa, ia = kernels.topk_softmax(lg, K, mode="A")
+        sr, ir = kernels.topk_softmax(lg, K, mode="A_renorm")
+        assert torch.equal(ib, ia) and torch.equal(ib, ir)
+        assert (sb - sr).abs().max().item() < 5e-7
+        assert (sa.sum(-1) < 1.0 + 1e-6).all()

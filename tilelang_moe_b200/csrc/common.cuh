@@ -1,0 +1,71 @@
+// Shared host/device helpers for the moe_b200 library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/moe_b200.h"
+
+namespace moe {
+
+// Thread-local message for the last failing call (returned by moe_last_error()).
+char* last_error_buffer();
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define MOE_CUDA_CHECK(expr)                                  \
+  do {                                                        \
+    cudaError_t _e = (expr);                                  \
+    if (_e != cudaSuccess) return ::moe::cuda_fail(_e, #expr); \
+  } while (0)
+
+#define MOE_CHECK_LAUNCH(name)                                       \
+  do {                                                               \
+    cudaError_t _e = cudaGetLastError();                             \
+    if (_e != cudaSuccess) return ::moe::cuda_fail(_e, name);        \
+  } while (0)
+
+// Cached per-device attributes.
+struct DeviceInfo {
+  int sm_count;
+  int cc_major;
+  int cc_minor;
+  int max_smem_optin;
+};
+int current_device_info(DeviceInfo* out);
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Device status codes written to status[0]; status[1..3] carry detail.
+enum : int {
+  ST_OK = 0,
+  ST_BAD_EXPERT_ID = 1,     // an expert id outside [0,E) was seen
+  ST_WAIT_TIMEOUT = 2,      // a bounded barrier wait gave up; status[1] = site
+  ST_INTERNAL = 3,
+};
+
+// ---- order-preserving float <-> uint32 key -----------------------------------
+// Larger float -> larger key.  -0.0 is folded into +0.0 and every NaN maps to the
+// top key, so that key equality is exactly "compares equal in a descending sort
+// that ranks NaN first".
+__device__ __forceinline__ uint32_t float_to_key(float x) {
+  if (x != x) return 0xFFFFFFFFu;
+  if (x == 0.0f) x = 0.0f;
+  uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  uint32_t b = (k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k;
+  return __uint_as_float(b);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+}  // namespace moe

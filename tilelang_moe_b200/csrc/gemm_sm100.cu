@@ -1,0 +1,564 @@
+// Ragged expert grouped GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM.
+//
+//   Y[rows of expert e] = A[rows of expert e] . B[e]^T          (A: [rows,K], B: [E,N,K], K contiguous)
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer: per k-block one A box (128 rows x 64) and the B box(es) (BN rows x 64),
+//               128-byte swizzled, into a ring of shared-memory stages guarded by mbarriers;
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) four times per
+//               k-block; tcgen05.commit releases the stage and, after the last k-block, publishes
+//               the accumulator.  Also owns the TMEM allocation;
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (two TMEM buffers, so the next tile's
+//               main loop overlaps), apply the fused epilogue, store 16-byte vectors with row masks.
+//
+// Tiles are enumerated on the device from the expert offsets (no host sync): expert-major, then
+// N tile, then M tile, so that CTAs running side by side share one B tile through L2.
+//
+// Epilogues: plain bf16 / fp32, SiLU(gate)*up with gate and up accumulated side by side in TMEM
+// by one N=256 instruction, and routing-weight scale + scatter to the (token, slot) row.
+//
+// Every barrier wait is bounded in time; on expiry the kernel records a status code, lets the
+// copies it issued land, frees its TMEM and returns.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+
+namespace moe {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_E = 1024;
+constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per barrier wait
+constexpr uint64_t DRAIN_LIMIT_NS = 20ull * 1000ull * 1000ull;    // 20 ms when draining after a failure
+
+template <int BN>
+struct Cfg {
+  static constexpr int STAGES = BN == 256 ? 4 : 6;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;   // 256 or 512: both powers of two >= 32
+  // layout: [stages][barriers 256 B][tile tables]
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
+  static constexpr int SMEM_BYTES = TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 1024;  // + alignment slack
+};
+
+struct Params {
+  const int32_t* offsets;
+  const int32_t* dst_rows;
+  const float* row_w;
+  void* Y;
+  int64_t ldy;
+  int K, N, E;
+  int num_n_tiles;
+  int num_k_blocks;
+  int32_t* status;
+};
+
+// ------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+
+// Bounded wait.  Returns false when the limit expires or another role has already given up
+// (*abort_flag != 0); the first to give up records where in status[].
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                            int site, uint64_t limit_ns) {
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > limit_ns) {
+      if (atomicExch((int*)abort_flag, 1) == 0 && status) {
+        status[0] = ST_WAIT_TIMEOUT;
+        status[1] = site;
+        status[2] = (int32_t)blockIdx.x;
+      }
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int site, uint64_t limit_ns = WAIT_LIMIT_NS) {
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status, site, limit_ns);
+}
+
+// Short bounded wait used only while winding down after a failure: no flag, no status.
+__device__ __noinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return;
+    if (global_timer_ns() - t0 > limit_ns) return;
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T ; bf16 inputs, fp32 accumulate
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane (base_lane + i)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart (SBO), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset
+  d |= (uint64_t)1 << 46;                    // version
+  d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D fp32, A/B bf16, both K-major, M=128, N=n.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------ tile schedule
+struct Tile {
+  int e, row0, row_end, n_tile;
+};
+// tstart[e] = number of M tiles of experts < e.  Tile ids: expert-major, then N tile, then M tile.
+__device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const int32_t* offs, int E, int NT) {
+  int lo = 0, hi = E - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (tstart[mid + 1] * NT > id) hi = mid; else lo = mid + 1;
+  }
+  Tile t;
+  t.e = lo;
+  const int local = id - tstart[lo] * NT;
+  const int mt = tstart[lo + 1] - tstart[lo];
+  t.n_tile = local / mt;
+  const int m_local = local - t.n_tile * mt;
+  t.row0 = offs[lo] + m_local * BM;
+  t.row_end = offs[lo + 1];
+  return t;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+// ------------------------------------------------------------------------------ kernel
+template <int BN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmB2, const Params p) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int OUT_COLS = EPI == MOE_GEMM_SILU_GATE ? BN / 2 : BN;   // output columns per tile
+  extern __shared__ unsigned char smem_dyn[];
+  // the swizzle pattern needs 1024-byte aligned stage buffers
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFFSET + 200);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
+  int32_t* tstart = reinterpret_cast<int32_t*>(smem + C::TABLE_OFFSET);
+  int32_t* offs = tstart + (MAX_E + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+  const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
+  const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
+
+  // ---- set-up: barriers, TMEM, tile table
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    if (EPI == MOE_GEMM_SILU_GATE) prefetch_tmap(&tmB2);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets[e];
+  __syncthreads();
+  if (warp == 2) {  // prefix of M tiles per expert, one warp, chunks of consecutive experts per lane
+    const int per = (E + 31) / 32;
+    const int e_lo = lane * per, e_hi = min(E, e_lo + per);
+    int sum = 0;
+    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + BM - 1) / BM;
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    int run = inc - sum;
+    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + BM - 1) / BM; }
+    if (lane == 31) tstart[E] = inc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = tstart[E] * NT;
+
+  if (warp == 0) {
+    // ===================================================================== TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT);
+      const int n0 = t.n_tile * OUT_COLS;
+      for (int kb = 0; kb < NKB; ++kb) {
+        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+        if (lane == 0) {
+          const uint32_t full = full0 + 8 * stage;
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+          mbar_arrive_expect_tx(full, C::STAGE_BYTES);
+          tma_load_2d(sa, &tmA, full, kb * BK, t.row0);
+          if (EPI == MOE_GEMM_SILU_GATE) {
+            tma_load_3d(sb, &tmB, full, kb * BK, n0, t.e);
+            tma_load_3d(sb + C::B_BYTES / 2, &tmB2, full, kb * BK, n0, t.e);
+          } else {
+            tma_load_3d(sb, &tmB, full, kb * BK, n0, t.e);
+          }
+        }
+        __syncwarp();
+        ++issued;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (!ok) {
+      // let the copies already issued land before the CTA retires its shared memory
+      const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+      for (uint32_t j = first; j < issued; ++j)
+        mbar_wait_drain(full0 + 8 * (j % STAGES), (j / STAGES) & 1, DRAIN_LIMIT_NS);
+    }
+  } else if (warp == 1) {
+    // ===================================================================== MMA issuer
+    constexpr uint32_t idesc = make_idesc(BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+      for (int kb = 0; kb < NKB; ++kb) {
+        if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 3)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint64_t adesc = make_smem_desc(sa);
+          const uint64_t bdesc = make_smem_desc(sa + C::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (addr >> 4) field
+            umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * stage);
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(tfull0 + 8 * acc);
+      __syncwarp();
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok) {
+      // wait (bounded) until the tensor-core work issued so far has retired, so TMEM can be freed
+      if (lane == 0) umma_commit(drain_bar);
+      __syncwarp();
+      mbar_wait_drain(drain_bar, 0, DRAIN_LIMIT_NS);
+    }
+  } else {
+    // ===================================================================== epilogue (warps 2..5)
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT);
+      if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int grow = t.row0 + q * 32 + lane;   // sorted row handled by this thread
+      const bool row_ok = grow < t.row_end;
+      const int n0 = t.n_tile * OUT_COLS;
+      int64_t out_row = grow;
+      float w = 1.0f;
+      if (row_ok) {
+        if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
+        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[grow];
+      }
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < OUT_COLS / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c * 32, v);
+        if (EPI == MOE_GEMM_SILU_GATE) {
+          uint32_t u[32];
+          tmem_ld32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+        } else {
+          tmem_ld_wait();
+          if (EPI == MOE_GEMM_SCALE_SCATTER) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * w);
+          }
+        }
+        const int col = n0 + c * 32;
+        if (row_ok && col < p.N) {
+          if (EPI == MOE_GEMM_PLAIN_F32) {
+            float* dst = reinterpret_cast<float*>(p.Y) + out_row * p.ldy + col;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col + j * 4 < p.N)
+                *reinterpret_cast<uint4*>(dst + j * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.Y) + out_row * p.ldy + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + j * 8 < p.N) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                o.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                o.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                o.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                *reinterpret_cast<uint4*>(dst + j * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// bf16 tensor [d2][d1][d0] (d0 contiguous), box [1][box1][64], 128-byte swizzle, zero fill out of bounds
+static int make_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box1) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(MOE_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint32_t box[3] = {(cuuint32_t)BK, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const cuuint32_t rank = d2 > 0 ? 3 : 2;
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MOE_ERR_ARG, "cuTensorMapEncodeTiled failed with %d (dims %llu,%llu,%llu box1 %u)", (int)r,
+                                     (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2, box1);
+  return MOE_OK;
+}
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
+                  cudaStream_t st) {
+  using C = Cfg<BN>;
+  static bool attr_set = false;   // per instantiation; the attribute is idempotent
+  if (!attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    attr_set = true;
+  }
+  grouped_gemm_kernel<BN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tA, tB, tB2, p);
+  MOE_CHECK_LAUNCH("grouped_gemm_kernel");
+  return MOE_OK;
+}
+
+}  // namespace gemm
+}  // namespace moe
+
+extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
+                                const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
+                                int K, int N, int E, int32_t* status, void* stream) {
+  using namespace moe;
+  using namespace moe::gemm;
+  if (epilogue < 0 || epilogue > 3) return fail(MOE_ERR_ARG, "grouped_gemm: unknown epilogue %d", epilogue);
+  if (max_rows < 0 || K < 8 || N < 8 || (K % 8) || (N % 8) || E < 1)
+    return fail(MOE_ERR_ARG, "grouped_gemm: bad shape rows=%lld K=%d N=%d E=%d (K, N multiples of 8)", (long long)max_rows, K, N, E);
+  if (E > MAX_E) return fail(MOE_ERR_UNSUPPORTED, "grouped_gemm: E=%d exceeds %d", E, MAX_E);
+  if (max_rows == 0) return MOE_OK;
+  if (max_rows > 0x7FFFFF00ll) return fail(MOE_ERR_UNSUPPORTED, "grouped_gemm: too many rows");
+  if (!A || !B || !offsets || !Y) return fail(MOE_ERR_ARG, "grouped_gemm: null pointer");
+  if (epilogue == MOE_GEMM_SILU_GATE && !B2) return fail(MOE_ERR_ARG, "grouped_gemm: SILU_GATE needs the up weight");
+  if (epilogue == MOE_GEMM_SCALE_SCATTER && !row_w) return fail(MOE_ERR_ARG, "grouped_gemm: SCALE_SCATTER needs row weights");
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(B2) |
+       reinterpret_cast<uintptr_t>(Y)) & 15)
+    return fail(MOE_ERR_ARG, "grouped_gemm: pointers must be 16-byte aligned");
+  const int out_elem = epilogue == MOE_GEMM_PLAIN_F32 ? 4 : 2;
+  if (ldy < N || (ldy * out_elem) % 16) return fail(MOE_ERR_ARG, "grouped_gemm: ldy=%lld must be >= N and 16-byte aligned", (long long)ldy);
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+
+  // tile width: 256 accumulator columns when that still fills the machine, else 128
+  const int64_t m_tiles_bound = max_rows / BM + E;
+  int BN;
+  if (epilogue == MOE_GEMM_SILU_GATE) {
+    BN = 256;  // 128 gate + 128 up columns
+  } else {
+    BN = (N % 256 == 0 && m_tiles_bound * (N / 256) >= dev.sm_count) ? 256 : 128;
+  }
+  const int out_cols = epilogue == MOE_GEMM_SILU_GATE ? BN / 2 : BN;
+
+  Params p;
+  p.offsets = offsets; p.dst_rows = dst_rows; p.row_w = row_w; p.Y = Y; p.ldy = ldy;
+  p.K = K; p.N = N; p.E = E;
+  p.num_n_tiles = (N + out_cols - 1) / out_cols;
+  p.num_k_blocks = (K + BK - 1) / BK;
+  p.status = status;
+
+  CUtensorMap tA, tB, tB2;
+  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)max_rows, 0, BM);
+  if (rc) return rc;
+  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, (uint32_t)out_cols);
+  if (rc) return rc;
+  tB2 = tB;
+  if (epilogue == MOE_GEMM_SILU_GATE) {
+    rc = make_tmap(&tB2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, (uint32_t)out_cols);
+    if (rc) return rc;
+  }
+  int64_t tiles_bound = m_tiles_bound * p.num_n_tiles;
+  int grid = (int)(tiles_bound < dev.sm_count ? tiles_bound : dev.sm_count);
+  if (grid < 1) grid = 1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (epilogue) {
+    case MOE_GEMM_PLAIN:
+      return BN == 256 ? launch<256, MOE_GEMM_PLAIN>(tA, tB, tB2, p, grid, st) : launch<128, MOE_GEMM_PLAIN>(tA, tB, tB2, p, grid, st);
+    case MOE_GEMM_SILU_GATE:
+      return launch<256, MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, grid, st);
+    case MOE_GEMM_SCALE_SCATTER:
+      return BN == 256 ? launch<256, MOE_GEMM_SCALE_SCATTER>(tA, tB, tB2, p, grid, st)
+                       : launch<128, MOE_GEMM_SCALE_SCATTER>(tA, tB, tB2, p, grid, st);
+    default:
+      return BN == 256 ? launch<256, MOE_GEMM_PLAIN_F32>(tA, tB, tB2, p, grid, st)
+                       : launch<128, MOE_GEMM_PLAIN_F32>(tA, tB, tB2, p, grid, st);
+  }
+}

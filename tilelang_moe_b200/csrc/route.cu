@@ -1,0 +1,324 @@
+// Token permutation / histogram stage, row gather, combine and the small-E router GEMV.
+// All of it is HBM- or latency-bound integer / copy work: coalesced 16-byte accesses,
+// warp-private shared-memory histograms, no host round trip.
+#include "common.cuh"
+
+namespace moe {
+
+// ------------------------------------------------------------------------------------
+// histogram / offsets / stable permutation
+//
+// The flat list of n = T*k expert ids is cut into units of RUNIT consecutive entries,
+// one warp per unit.  (1) every warp counts its unit into unit_counts[u][e];
+// (2) one CTA turns the table into start positions: offsets[e] + entries of expert e in
+// earlier units; (3) every warp walks its unit again in order and hands out positions,
+// which makes the permutation the stable argsort of the ids.
+// ------------------------------------------------------------------------------------
+constexpr int RUNIT = 1024;        // entries per warp
+constexpr int RWPB = 8;            // warps per CTA in the count / scatter kernels
+
+__device__ __forceinline__ int load_id(const void* ids, int is64, int64_t i) {
+  if (is64) {
+    const long long v = reinterpret_cast<const long long*>(ids)[i];
+    return (v < 0 || v > 0x7FFFFFFFll) ? -1 : (int)v;
+  }
+  return reinterpret_cast<const int*>(ids)[i];
+}
+
+__global__ void __launch_bounds__(RWPB * 32)
+route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, int32_t* __restrict__ unit_counts,
+                   int32_t* __restrict__ status) {
+  extern __shared__ int32_t sh[];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  int32_t* wh = sh + (size_t)w * E;
+  const int64_t u = (int64_t)blockIdx.x * RWPB + w;
+  const int64_t first = u * RUNIT;
+  if (first >= n) return;
+  for (int e = lane; e < E; e += 32) wh[e] = 0;
+  __syncwarp();
+  const int64_t last = first + RUNIT < n ? first + RUNIT : n;
+  for (int64_t i = first + lane; i < last; i += 32) {
+    const int e = load_id(ids, is64, i);
+    if (e >= 0 && e < E) atomicAdd(&wh[e], 1);
+    else if (status) status[0] = ST_BAD_EXPERT_ID;
+  }
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) unit_counts[u * E + e] = wh[e];
+}
+
+__global__ void __launch_bounds__(1024)
+route_scan_kernel(int32_t* __restrict__ unit_counts, int64_t n_units, int E, int32_t* __restrict__ counts,
+                  int32_t* __restrict__ offsets) {
+  __shared__ int32_t warp_tot[32];
+  __shared__ int32_t carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base < E; base += 1024) {
+    const int e = base + tid;
+    int32_t total = 0;
+    if (e < E)
+      for (int64_t u = 0; u < n_units; ++u) total += unit_counts[u * E + e];
+    // exclusive scan of `total` over this chunk of experts
+    int32_t inc = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    if (lane == 31) warp_tot[wid] = inc;
+    __syncthreads();
+    int32_t before = carry_s;
+    for (int w2 = 0; w2 < wid; ++w2) before += warp_tot[w2];
+    const int32_t start = before + inc - total;
+    if (e < E) {
+      counts[e] = total;
+      offsets[e] = start;
+      int32_t run = start;
+      for (int64_t u = 0; u < n_units; ++u) {
+        const int32_t c = unit_counts[u * E + e];
+        unit_counts[u * E + e] = run;
+        run += c;
+      }
+    }
+    __syncthreads();
+    if (tid == 1023) carry_s = before + inc;
+    __syncthreads();
+  }
+  if (tid == 0) offsets[E] = carry_s;
+}
+
+__global__ void __launch_bounds__(RWPB * 32)
+route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ unit_base,
+                     int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+  extern __shared__ int32_t sh[];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const unsigned lt_mask = (1u << lane) - 1u;
+  int32_t* wh = sh + (size_t)w * E;
+  const int64_t u = (int64_t)blockIdx.x * RWPB + w;
+  const int64_t first = u * RUNIT;
+  if (first >= n) return;
+  for (int e = lane; e < E; e += 32) wh[e] = unit_base[u * E + e];
+  __syncwarp();
+  const int64_t last = first + RUNIT < n ? first + RUNIT : n;
+  for (int64_t i0 = first; i0 < last; i0 += 32) {
+    const int64_t i = i0 + lane;
+    int e = i < last ? load_id(ids, is64, i) : -1;
+    const bool valid = e >= 0 && e < E;
+    // lanes without a valid id get a private group so that they match nobody
+    const unsigned grp = __match_any_sync(0xFFFFFFFFu, valid ? (unsigned)e : (0x80000000u | (unsigned)lane));
+    const int r = __popc(grp & lt_mask);
+    int32_t base = 0;
+    if (valid) base = wh[e];
+    __syncwarp();
+    if (valid && r == 0) wh[e] = base + __popc(grp);
+    __syncwarp();
+    if (valid) {
+      const int32_t pos = base + r;
+      if (perm) perm[pos] = (int32_t)i;
+      if (inv) inv[i] = pos;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// row gather: dst[p,:] = src[perm[p] / div, :]
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ perm, int div, int64_t n_rows,
+                   int vec_per_row, uint4* __restrict__ dst, const float* __restrict__ w_src,
+                   float* __restrict__ w_dst) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = (int64_t)gridDim.x * 8;
+  for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < n_rows; p += nwarps) {
+    const int32_t f = perm ? perm[p] : (int32_t)p;
+    const int64_t srow = div > 1 ? f / div : f;
+    const uint4* s = src + srow * vec_per_row;
+    uint4* d = dst + p * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) d[v] = __ldg(s + v);
+    if (w_src && lane == 0) w_dst[p] = w_src[f];
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// combine: out[t,:] = shared[t,:] + sum_s Yk[t*k+s,:]   (fp32 sum in slot order, one rounding)
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ void add_bf16x8(float* acc, const uint4& v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h[j]);
+    acc[2 * j] += f.x;
+    acc[2 * j + 1] += f.y;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, int64_t T, int k, int vec_per_row,
+               uint4* __restrict__ out) {
+  const int64_t total = T * vec_per_row;
+  for (int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x; g < total; g += (int64_t)gridDim.x * 256) {
+    const int64_t t = g / vec_per_row;
+    const int v = (int)(g - t * vec_per_row);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < k; ++s) add_bf16x8(acc, __ldg(Yk + (t * k + s) * vec_per_row + v));
+    if (shared) add_bf16x8(acc, __ldg(shared + g));
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    out[g] = o;
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// router logits for a small expert count: one warp per token, 8 experts per pass
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, int64_t T, int vec_per_row, int E,
+                     float* __restrict__ logits) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = (int64_t)gridDim.x * 8;
+  for (int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); t < T; t += nwarps) {
+    const uint4* xr = x + t * vec_per_row;
+    for (int e0 = 0; e0 < E; e0 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int v = lane; v < vec_per_row; v += 32) {
+        const uint4 xv = __ldg(xr + v);
+        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        float xf[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(xh[j]);
+          xf[2 * j] = f.x; xf[2 * j + 1] = f.y;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (e0 + j < E) {
+            const uint4 wv = __ldg(Wr + (int64_t)(e0 + j) * vec_per_row + v);
+            const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = __bfloat1622float2(wh[q]);
+              acc[j] = fmaf(xf[2 * q], f.x, acc[j]);
+              acc[j] = fmaf(xf[2 * q + 1], f.y, acc[j]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float s = warp_sum(acc[j]);
+        if (lane == 0 && e0 + j < E) logits[t * E + e0 + j] = s;
+      }
+    }
+  }
+}
+
+}  // namespace moe
+
+// ====================================================================================
+extern "C" size_t moe_route_histogram_workspace(int64_t n, int E) {
+  if (n <= 0 || E <= 0) return 0;
+  const int64_t units = moe::ceil_div64(n, moe::RUNIT);
+  return (size_t)units * (size_t)E * sizeof(int32_t);
+}
+
+extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E, int32_t* counts,
+                                   int32_t* offsets, int32_t* perm, int32_t* inv, void* ws, size_t ws_bytes,
+                                   int32_t* status, void* stream) {
+  using namespace moe;
+  if (n < 0 || E < 1) return fail(MOE_ERR_ARG, "route_histogram: bad size n=%lld E=%d", (long long)n, E);
+  if (!counts || !offsets) return fail(MOE_ERR_ARG, "route_histogram: null counts/offsets");
+  if (n > 0 && !topk_idx) return fail(MOE_ERR_ARG, "route_histogram: null ids");
+  if (n > 0x7FFFFFFFll) return fail(MOE_ERR_UNSUPPORTED, "route_histogram: n exceeds int32 positions");
+  if ((size_t)RWPB * E * 4 > 160 * 1024) return fail(MOE_ERR_UNSUPPORTED, "route_histogram: E=%d too large", E);
+  const size_t need = moe_route_histogram_workspace(n, E);
+  if (need > 0 && (!ws || ws_bytes < need)) return fail(MOE_ERR_WORKSPACE, "route_histogram: workspace %zu < %zu", ws_bytes, need);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t units = ceil_div64(n, RUNIT);
+  const size_t smem = (size_t)RWPB * E * 4;
+  int32_t* unit_counts = reinterpret_cast<int32_t*>(ws);
+  if (smem > 48 * 1024) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  const unsigned blocks = (unsigned)ceil_div64(units, RWPB);
+  if (units > 0) {
+    route_count_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, unit_counts, status);
+    MOE_CHECK_LAUNCH("route_count_kernel");
+  }
+  route_scan_kernel<<<1, 1024, 0, st>>>(unit_counts, units, E, counts, offsets);
+  MOE_CHECK_LAUNCH("route_scan_kernel");
+  if (units > 0 && (perm || inv)) {
+    route_scatter_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, unit_counts, perm, inv);
+    MOE_CHECK_LAUNCH("route_scatter_kernel");
+  }
+  return MOE_OK;
+}
+
+extern "C" int moe_gather_rows(const void* src, const int32_t* perm, int div, int64_t n_rows, int64_t cols, void* dst,
+                               const float* w_src, float* w_dst, void* stream) {
+  using namespace moe;
+  if (n_rows < 0 || cols < 8 || cols % 8) return fail(MOE_ERR_ARG, "gather_rows: cols=%lld must be a positive multiple of 8", (long long)cols);
+  if (n_rows == 0) return MOE_OK;
+  if (!src || !dst) return fail(MOE_ERR_ARG, "gather_rows: null pointer");
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) return fail(MOE_ERR_ARG, "gather_rows: pointers must be 16-byte aligned");
+  if (w_src && !w_dst) return fail(MOE_ERR_ARG, "gather_rows: w_src without w_dst");
+  if (div < 1) div = 1;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  int64_t blocks = ceil_div64(n_rows, 8);
+  const int64_t cap = (int64_t)dev.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  gather_rows_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(src), perm, div, n_rows, (int)(cols / 8), reinterpret_cast<uint4*>(dst), w_src, w_dst);
+  MOE_CHECK_LAUNCH("gather_rows_kernel");
+  return MOE_OK;
+}
+
+extern "C" int moe_combine(const void* Yk, const void* shared, int64_t T, int k, int64_t H, void* out, void* stream) {
+  using namespace moe;
+  if (T < 0 || k < 0 || H < 8 || H % 8) return fail(MOE_ERR_ARG, "combine: bad shape T=%lld k=%d H=%lld", (long long)T, k, (long long)H);
+  if (T == 0) return MOE_OK;
+  if ((k > 0 && !Yk) || !out) return fail(MOE_ERR_ARG, "combine: null pointer");
+  if ((reinterpret_cast<uintptr_t>(Yk) | reinterpret_cast<uintptr_t>(shared) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(MOE_ERR_ARG, "combine: pointers must be 16-byte aligned");
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  const int64_t total = T * (H / 8);
+  int64_t blocks = ceil_div64(total, 256);
+  const int64_t cap = (int64_t)dev.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  combine_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(Yk), reinterpret_cast<const uint4*>(shared), T, k, (int)(H / 8),
+      reinterpret_cast<uint4*>(out));
+  MOE_CHECK_LAUNCH("combine_kernel");
+  return MOE_OK;
+}
+
+extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, float* logits, int32_t* status,
+                                 void* stream) {
+  using namespace moe;
+  (void)status;
+  if (T < 0 || H < 8 || H % 8 || E < 1) return fail(MOE_ERR_ARG, "router_logits: bad shape T=%lld H=%d E=%d", (long long)T, H, E);
+  if (T == 0) return MOE_OK;
+  if (!x || !Wr || !logits) return fail(MOE_ERR_ARG, "router_logits: null pointer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(Wr)) & 15) return fail(MOE_ERR_ARG, "router_logits: pointers must be 16-byte aligned");
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  int64_t blocks = ceil_div64(T, 8);
+  const int64_t cap = (int64_t)dev.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  router_logits_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);
+  MOE_CHECK_LAUNCH("router_logits_kernel");
+  return MOE_OK;
+}

@@ -1,0 +1,158 @@
+"""Drop-in for the hot path of the reference's ``kernels`` package.
+
+Same names, argument order and return types as the reference's public API
+(reference kernels/__init__.py:4-101) for the MoE-layer path:
+
+    topk_softmax(logits, k)                       kernels/topk_softmax_tilelang.py:1103-1135
+    grouped_gemm(X, W, expert_indices)            kernels/grouped_gemm_tilelang.py:859-895
+    fusedmoe_tilelang(x, router_weight, ...)      kernels/fusedmoe_tilelang.py:605-647
+    FusedMoETileLang(...).forward(...)            kernels/fusedmoe_tilelang.py:241-417
+    generate_fusedmoe_inputs(...)                 kernels/fusedmoe_baseline.py:311-375
+
+Everything runs on the CUDA library behind ``include/moe_b200.h``; there is no
+strategy auto-selection between back ends and no CPU path.  Deliberate
+differences from the reference's GPU path, all towards its PyTorch baseline:
+indices are int64 and sorted (value descending, ties lowest index first), the
+router of the fused layer accumulates logits in fp32, and the compute dtype is
+bfloat16.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import layer as _layer
+from .. import ops as _ops
+
+__all__ = [
+    "topk_softmax", "topk_softmax_best", "grouped_gemm", "grouped_gemm_best", "fusedmoe_tilelang", "fusedmoe",
+    "FusedMoETileLang", "FusedMoE", "generate_fusedmoe_inputs", "route_histogram",
+]
+
+
+def topk_softmax(logits: torch.Tensor, k: int, mode: str = "B") -> Tuple[torch.Tensor, torch.Tensor]:
+    """Top-k of the logits, softmax over the k selected (convention B).
+
+    logits (num_tokens, num_experts) float32 -> (scores float32 (num_tokens, k),
+    indices int64 (num_tokens, k)).  ``mode`` "A" / "A_renorm" give the other two
+    conventions of the reference baseline (softmax over all experts first).
+    """
+    return _ops.topk_softmax(logits, k, mode=mode, index_dtype=torch.int64)
+
+
+topk_softmax_best = topk_softmax
+
+
+def route_histogram(topk_indices: torch.Tensor, n_experts: int):
+    """counts, exclusive offsets, stable permutation and inverse of the flattened expert ids."""
+    return _ops.route_histogram(topk_indices, n_experts)
+
+
+def grouped_gemm(X: torch.Tensor, W: torch.Tensor, expert_indices: torch.Tensor,
+                 w_layout: str = "EIH") -> torch.Tensor:
+    """Y[i] = X[i] @ W[expert_indices[i]].T.
+
+    X (total_tokens, H) bfloat16; W (E, I, H); expert_indices (total_tokens,) int64
+    -> Y (total_tokens, I).  With 2-D expert_indices (T, k) every token row is used
+    by its k experts and Y is (T, k, I), without materialising a repeated X on the
+    host side.  ``w_layout="EHI"`` accepts the kernel-level layout the reference's
+    benchmark allocates (it is transposed once here).
+    """
+    if w_layout == "EHI":
+        W = W.transpose(1, 2).contiguous()
+    elif w_layout != "EIH":
+        raise ValueError("w_layout must be 'EIH' or 'EHI'")
+    if X.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
+        raise ValueError("grouped_gemm computes in bfloat16")
+    if expert_indices.dim() not in (1, 2) or expert_indices.shape[0] != X.shape[0]:
+        raise ValueError("expert_indices must be (total_tokens,) or (total_tokens, k)")
+    E, I, H = W.shape
+    k = expert_indices.shape[1] if expert_indices.dim() == 2 else 1
+    n = X.shape[0] * k
+    _, offsets, perm, _ = _ops.route_histogram(expert_indices, E, want_inv=False)
+    xs = _ops.gather_rows(X.contiguous(), perm, div=k)
+    Y = torch.empty(n, I, dtype=X.dtype, device=X.device)
+    _ops.grouped_gemm_sorted(_ops.GEMM_PLAIN, xs, W.contiguous(), offsets, dst_rows=perm, out=Y)
+    return Y.view(X.shape[0], k, I) if expert_indices.dim() == 2 else Y
+
+
+grouped_gemm_best = grouped_gemm
+
+
+class FusedMoETileLang:
+    """Shared + routed SiLU-gated MoE layer with persistent scratch for one shape.
+
+    Constructor arguments as in the reference (kernels/fusedmoe_tilelang.py:248-260);
+    ``block_token`` is accepted and ignored (the tile shape is fixed by the kernel).
+    """
+
+    def __init__(self, d_hidden: int, d_expert: int, n_routed_experts: int, n_shared_experts: int,
+                 n_experts_per_token: int, batch_size: int, seq_len: int, dtype: torch.dtype = torch.bfloat16,
+                 block_token: int = 128, device: Optional[torch.device] = None):
+        if dtype != torch.bfloat16:
+            raise ValueError("moe_b200 computes in bfloat16")
+        self.d_hidden, self.d_expert = d_hidden, d_expert
+        self.n_routed_experts, self.n_shared_experts = n_routed_experts, n_shared_experts
+        self.n_experts_per_token = n_experts_per_token
+        self.batch_size, self.seq_len = batch_size, seq_len
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.ws = _layer.MoEWorkspace(batch_size * seq_len, n_experts_per_token, d_hidden, d_expert,
+                                      n_routed_experts, d_expert * n_shared_experts, dev)
+
+    def forward(self, x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down,
+                logits: Optional[torch.Tensor] = None):
+        return _layer.moe_forward(x, router_weight, shared_gate if self.n_shared_experts else None, shared_up,
+                                  shared_down, routed_gate, routed_up, routed_down, self.n_experts_per_token,
+                                  ws=self.ws, logits=logits)
+
+    __call__ = forward
+
+
+FusedMoE = FusedMoETileLang
+_layer_cache: Dict[tuple, FusedMoETileLang] = {}
+
+
+def fusedmoe_tilelang(x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down,
+                      n_experts_per_token: int) -> torch.Tensor:
+    """Functional form; caches one layer object per shape like the reference
+    (kernels/fusedmoe_tilelang.py:628-640).  Output: shape of x."""
+    B, S, H = x.shape
+    E, I, _ = routed_gate.shape
+    n_shared = shared_gate.shape[0] // I if shared_gate is not None else 0
+    key = (H, I, E, n_shared, n_experts_per_token, B, S, x.dtype, x.device)
+    m = _layer_cache.get(key)
+    if m is None:
+        m = FusedMoETileLang(H, I, E, n_shared, n_experts_per_token, B, S, x.dtype, device=x.device)
+        _layer_cache[key] = m
+    return m.forward(x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down)
+
+
+fusedmoe = fusedmoe_tilelang
+
+
+def generate_fusedmoe_inputs(batch_size: int, seq_len: int, d_hidden: int, d_expert: int, n_routed_experts: int,
+                             n_shared_experts: int, n_experts_per_token: int, dtype: torch.dtype = torch.float16,
+                             device: str = "cuda", seed: int = 42):
+    """Seeded layer inputs: x ~ N(0,1) and weights ~ N(0, 1/fan_in), drawn in the order x,
+    router, shared gate/up/down, routed gate/up/down from one generator on ``device``
+    (same contract as reference kernels/fusedmoe_baseline.py:311-375)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+
+    def draw(*shape):
+        return torch.randn(*shape, device=device, dtype=dtype, generator=gen)
+
+    x = draw(batch_size, seq_len, d_hidden).contiguous()
+    sd = d_expert * n_shared_experts
+    weights = {
+        "router_weight": draw(n_routed_experts, d_hidden) / math.sqrt(d_hidden),
+        "shared_gate": draw(sd, d_hidden) / math.sqrt(d_hidden),
+        "shared_up": draw(sd, d_hidden) / math.sqrt(d_hidden),
+        "shared_down": draw(d_hidden, sd) / math.sqrt(max(sd, 1)),
+        "routed_gate": draw(n_routed_experts, d_expert, d_hidden) / math.sqrt(d_hidden),
+        "routed_up": draw(n_routed_experts, d_expert, d_hidden) / math.sqrt(d_hidden),
+        "routed_down": draw(n_routed_experts, d_hidden, d_expert) / math.sqrt(d_expert),
+    }
+    return x, weights

@@ -1,0 +1,101 @@
+"""The MoE layer forward as a fixed sequence of launches on one stream.
+
+    logits -> top-k + softmax -> histogram / offsets / permutation -> row gather
+           -> up GEMM (SiLU gate fused) -> down GEMM (weight scale + scatter fused)
+           -> combine (k-way sum + shared expert)
+
+No step reads anything back to the host: tile tables are derived on the device
+from the expert offsets, and scratch is sized from T, k, H, I alone, so one
+``MoEWorkspace`` serves every routing pattern of a given shape.
+
+Mirrors ``FusedMoEPyTorch.forward`` (reference kernels/fusedmoe_baseline.py:46-91)
+and ``FusedMoETileLang.forward`` (reference kernels/fusedmoe_tilelang.py:309-417).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib, ops
+
+
+@dataclass
+class MoEWorkspace:
+    """Persistent scratch for one (T, k, H, I, E) shape on one device."""
+    T: int
+    k: int
+    H: int
+    I: int
+    E: int
+    SI: int
+    device: torch.device
+
+    def __post_init__(self):
+        dev, bf16 = self.device, torch.bfloat16
+        n = self.T * self.k
+        self.logits = torch.empty(self.T, self.E, dtype=torch.float32, device=dev)
+        self.xs = torch.empty(n, self.H, dtype=bf16, device=dev)          # expert-sorted activations
+        self.ws = torch.empty(n, dtype=torch.float32, device=dev)         # routing weight per sorted row
+        self.act = torch.empty(n, self.I, dtype=bf16, device=dev)         # SiLU(gate)*up per sorted row
+        self.yk = torch.empty(n, self.H, dtype=bf16, device=dev)          # scaled expert output per (token, slot)
+        need = _lib.load().moe_route_histogram_workspace(n, self.E)
+        self.hist_ws = torch.empty(max(need, 4), dtype=torch.uint8, device=dev)
+        if self.SI > 0:
+            self.act_s = torch.empty(self.T, self.SI, dtype=bf16, device=dev)
+            self.y_s = torch.empty(self.T, self.H, dtype=bf16, device=dev)
+            self.offs_s = torch.tensor([0, self.T], dtype=torch.int32, device=dev)
+        self.out = torch.empty(self.T, self.H, dtype=bf16, device=dev)
+
+
+def routed_forward(x_flat: torch.Tensor, scores: torch.Tensor, idx32: torch.Tensor, routed_gate: torch.Tensor,
+                   routed_up: torch.Tensor, routed_down: torch.Tensor, ws: MoEWorkspace,
+                   shared_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routed experts + combine for routing already decided (scores fp32 [T,k], idx32 int32 [T,k])."""
+    E = routed_gate.shape[0]
+    k = idx32.shape[1]
+    counts, offsets, perm, _ = ops.route_histogram(idx32, E, want_inv=False, workspace=ws.hist_ws)
+    ops.gather_rows(x_flat, perm, div=k, out=ws.xs, w_src=scores, w_out=ws.ws)
+    ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, ws.xs, routed_gate, offsets, B2=routed_up, out=ws.act)
+    ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, ws.act, routed_down, offsets, dst_rows=perm, row_w=ws.ws,
+                            out=ws.yk)
+    return ops.combine(ws.yk, k, shared=shared_out, out=ws.out if out is None else out)
+
+
+def shared_forward(x_flat: torch.Tensor, shared_gate: torch.Tensor, shared_up: torch.Tensor,
+                   shared_down: torch.Tensor, ws: MoEWorkspace) -> torch.Tensor:
+    """The shared experts as one dense SiLU-gated FFN of width S*I (reference fusedmoe_baseline.py:93-103)."""
+    ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, x_flat, shared_gate.unsqueeze(0), ws.offs_s,
+                            B2=shared_up.unsqueeze(0), out=ws.act_s)
+    return ops.grouped_gemm_sorted(ops.GEMM_PLAIN, ws.act_s, shared_down.unsqueeze(0), ws.offs_s, out=ws.y_s)
+
+
+def moe_forward(x: torch.Tensor, router_weight: Optional[torch.Tensor], shared_gate, shared_up, shared_down,
+                routed_gate: torch.Tensor, routed_up: torch.Tensor, routed_down: torch.Tensor, k: int,
+                ws: Optional[MoEWorkspace] = None, logits: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, return_routing: bool = False):
+    """Full layer.  x [..., H] bf16.  Router: fp32 logits (given, or x.Wr^T), softmax over all
+    experts, top-k without renormalisation (reference fusedmoe_baseline.py:72-76)."""
+    if x.dtype != torch.bfloat16:
+        raise ValueError("moe_b200 computes in bfloat16; cast the activations and weights")
+    shape = x.shape
+    H = shape[-1]
+    x_flat = x.reshape(-1, H)
+    if not x_flat.is_contiguous():
+        x_flat = x_flat.contiguous()
+    T = x_flat.shape[0]
+    E, I, _ = routed_gate.shape
+    SI = 0 if shared_gate is None else shared_gate.shape[0]
+    if ws is None or (ws.T, ws.k, ws.H, ws.I, ws.E, ws.SI) != (T, k, H, I, E, SI) or ws.device != x.device:
+        ws = MoEWorkspace(T, k, H, I, E, SI, x.device)
+    if logits is None:
+        logits = ops.router_logits(x_flat, router_weight, out=ws.logits)
+    scores, idx32 = ops.topk_softmax(logits, k, mode="A", index_dtype=torch.int32)
+    shared_out = shared_forward(x_flat, shared_gate, shared_up, shared_down, ws) if SI > 0 else None
+    y = routed_forward(x_flat, scores, idx32, routed_gate, routed_up, routed_down, ws, shared_out=shared_out,
+                       out=None if out is None else out.view(T, H))
+    y = y.view(*shape)
+    if return_routing:
+        return y, scores, idx32
+    return y

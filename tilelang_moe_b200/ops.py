@@ -1,0 +1,211 @@
+"""Torch-tensor front end of the C ABI: argument checks, output allocation, launch.
+
+PyTorch is used here for device memory and streams only.  Every function enqueues
+on the current CUDA stream and returns without synchronising.  Kernels report
+device-side give-ups (a bounded wait that expired, an expert id out of range)
+in a per-device status word; ``check_status()`` reads it (one D2H sync), and it is
+read after every call when ``MOE_B200_DEBUG=1``.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+MODE_B, MODE_A, MODE_A_RENORM = 0, 1, 2
+GEMM_PLAIN, GEMM_SILU_GATE, GEMM_SCALE_SCATTER, GEMM_PLAIN_F32 = 0, 1, 2, 3
+_MODES = {"B": MODE_B, "A": MODE_A, "A_norenorm": MODE_A, "A_renorm": MODE_A_RENORM,
+          0: MODE_B, 1: MODE_A, 2: MODE_A_RENORM}
+
+_DEBUG = os.environ.get("MOE_B200_DEBUG", "0") not in ("", "0")
+_status = {}
+_STATUS_TEXT = {1: "expert id outside [0,E)", 2: "a bounded barrier wait expired", 3: "internal selection count mismatch"}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("moe_b200 operates on CUDA tensors only (no CPU path)")
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    buf = _status.get(key)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
+        _status[key] = buf
+    return buf
+
+
+def check_status(device=None, reset: bool = True) -> None:
+    """Raise if a kernel recorded a device-side failure since the last check."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    buf = status_buffer(dev)
+    vals = buf.tolist()
+    if vals[0] != 0:
+        if reset:
+            buf.zero_()
+        raise _lib.MoeLibraryError(
+            f"device status {vals}: {_STATUS_TEXT.get(vals[0], 'unknown')}")
+
+
+def _after(dev) -> None:
+    if _DEBUG:
+        check_status(dev)
+
+
+# ----------------------------------------------------------------------------- router
+def topk_softmax(logits: torch.Tensor, k: int, mode="B", index_dtype: torch.dtype = torch.int64,
+                 also_int32: bool = False):
+    """Fused top-k + softmax.  Returns (scores fp32 [M,k], indices [M,k]) sorted by value
+    descending, ties lowest index first.  With ``also_int32`` a third tensor carries the
+    same indices as int32 (feeds route_histogram without a cast)."""
+    _need_cuda(logits)
+    if logits.dim() != 2 or logits.dtype != torch.float32:
+        raise ValueError("logits must be a 2-D float32 tensor")
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    M, N = logits.shape
+    if not (1 <= k <= N):
+        raise ValueError(f"k={k} must be in [1, N={N}]")
+    if index_dtype not in (torch.int64, torch.int32):
+        raise ValueError("index_dtype must be int64 or int32")
+    lib = _lib.load()
+    scores = torch.empty(M, k, dtype=torch.float32, device=logits.device)
+    idx64 = torch.empty(M, k, dtype=torch.int64, device=logits.device) if index_dtype == torch.int64 else None
+    idx32 = torch.empty(M, k, dtype=torch.int32, device=logits.device) if (also_int32 or idx64 is None) else None
+    with torch.cuda.device(logits.device):
+        rc = lib.moe_topk_softmax(_ptr(logits), M, N, logits.stride(0), k, _MODES[mode], _ptr(scores), _ptr(idx64),
+                                  _ptr(idx32), _ptr(status_buffer(logits.device)), _stream())
+    _lib.check(rc, "moe_topk_softmax")
+    _after(logits.device)
+    if idx64 is None:
+        return scores, idx32
+    if also_int32:
+        return scores, idx64, idx32
+    return scores, idx64
+
+
+# ----------------------------------------------------------------------------- permutation
+def route_histogram(topk_idx: torch.Tensor, n_experts: int, want_perm: bool = True, want_inv: bool = True,
+                    workspace: Optional[torch.Tensor] = None):
+    """counts [E], exclusive offsets [E+1], stable permutation perm [n] and its inverse inv [n]
+    (all int32) of the flattened expert ids."""
+    _need_cuda(topk_idx)
+    if topk_idx.dtype not in (torch.int64, torch.int32):
+        raise ValueError("expert ids must be int64 or int32")
+    ids = topk_idx.contiguous().view(-1)
+    n = ids.numel()
+    dev = ids.device
+    lib = _lib.load()
+    counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    perm = torch.empty(n, dtype=torch.int32, device=dev) if want_perm else None
+    inv = torch.empty(n, dtype=torch.int32, device=dev) if want_inv else None
+    need = lib.moe_route_histogram_workspace(n, n_experts)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(need, 4), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.moe_route_histogram(_ptr(ids), int(ids.dtype == torch.int64), n, n_experts, _ptr(counts),
+                                     _ptr(offsets), _ptr(perm), _ptr(inv), _ptr(workspace),
+                                     workspace.numel() * workspace.element_size(), _ptr(status_buffer(dev)), _stream())
+    _lib.check(rc, "moe_route_histogram")
+    _after(dev)
+    return counts, offsets, perm, inv
+
+
+def gather_rows(src: torch.Tensor, perm: Optional[torch.Tensor], div: int = 1, out: Optional[torch.Tensor] = None,
+                w_src: Optional[torch.Tensor] = None, w_out: Optional[torch.Tensor] = None, n_rows: Optional[int] = None):
+    """out[p] = src[perm[p] // div]; optionally w_out[p] = w_src[perm[p]]."""
+    _need_cuda(src, perm)
+    if src.dim() != 2 or src.dtype != torch.bfloat16 or not src.is_contiguous():
+        raise ValueError("src must be a contiguous 2-D bfloat16 tensor")
+    n = (perm.numel() if perm is not None else src.shape[0]) if n_rows is None else n_rows
+    cols = src.shape[1]
+    if out is None:
+        out = torch.empty(n, cols, dtype=src.dtype, device=src.device)
+    if w_src is not None:
+        if w_src.dtype != torch.float32:
+            raise ValueError("routing weights must be float32")
+        w_src = w_src.contiguous().view(-1)
+        if w_out is None:
+            w_out = torch.empty(n, dtype=torch.float32, device=src.device)
+    with torch.cuda.device(src.device):
+        rc = _lib.load().moe_gather_rows(_ptr(src), _ptr(perm), div, n, cols, _ptr(out), _ptr(w_src), _ptr(w_out), _stream())
+    _lib.check(rc, "moe_gather_rows")
+    return (out, w_out) if w_src is not None else out
+
+
+# ----------------------------------------------------------------------------- expert GEMM
+def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets: torch.Tensor,
+                        B2: Optional[torch.Tensor] = None, dst_rows: Optional[torch.Tensor] = None,
+                        row_w: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                        out_rows: Optional[int] = None, max_rows: Optional[int] = None) -> torch.Tensor:
+    """Expert GEMM over expert-sorted rows.  A [rows,K] bf16, B (and B2) [E,N,K] bf16,
+    offsets int32 [E+1] on the device.  See include/moe_b200.h for the epilogues."""
+    _need_cuda(A, B, offsets)
+    if A.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
+        raise ValueError("A and B must be bfloat16")
+    if A.dim() != 2 or B.dim() != 3 or not A.is_contiguous() or not B.is_contiguous():
+        raise ValueError("A must be contiguous [rows,K], B contiguous [E,N,K]")
+    rows, K = A.shape
+    E, N, K2 = B.shape
+    if K2 != K:
+        raise ValueError(f"inner dimensions differ: A has K={K}, B has K={K2}")
+    if B2 is not None and (B2.shape != B.shape or B2.dtype != B.dtype or not B2.is_contiguous()):
+        raise ValueError("B2 must match B")
+    if offsets.dtype != torch.int32 or offsets.numel() != E + 1:
+        raise ValueError("offsets must be int32 [E+1]")
+    if max_rows is None:
+        max_rows = rows
+    if out is None:
+        odt = torch.float32 if epilogue == GEMM_PLAIN_F32 else torch.bfloat16
+        out = torch.empty(rows if out_rows is None else out_rows, N, dtype=odt, device=A.device)
+    with torch.cuda.device(A.device):
+        rc = _lib.load().moe_grouped_gemm(epilogue, _ptr(A), _ptr(B), _ptr(B2), _ptr(offsets), _ptr(dst_rows),
+                                          _ptr(row_w), _ptr(out), out.stride(0), max_rows, K, N, E,
+                                          _ptr(status_buffer(A.device)), _stream())
+    _lib.check(rc, "moe_grouped_gemm")
+    _after(A.device)
+    return out
+
+
+def combine(Yk: torch.Tensor, k: int, shared: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = shared[t] + sum over the k slot rows Yk[t*k : t*k+k] (fp32 sum, one bf16 rounding)."""
+    _need_cuda(Yk, shared)
+    n, H = Yk.shape
+    T = n // k
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=Yk.device)
+    with torch.cuda.device(Yk.device):
+        rc = _lib.load().moe_combine(_ptr(Yk), _ptr(shared), T, k, H, _ptr(out), _stream())
+    _lib.check(rc, "moe_combine")
+    return out
+
+
+def router_logits(x: torch.Tensor, router_weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 logits [T,E] = x [T,H] . Wr[E,H]^T from bf16 inputs, fp32 accumulate."""
+    _need_cuda(x, router_weight)
+    if x.dtype != torch.bfloat16 or router_weight.dtype != torch.bfloat16:
+        raise ValueError("router inputs must be bfloat16")
+    T, H = x.shape
+    E = router_weight.shape[0]
+    if out is None:
+        out = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().moe_router_logits(_ptr(x.contiguous()), _ptr(router_weight.contiguous()), T, H, E, _ptr(out),
+                                           _ptr(status_buffer(x.device)), _stream())
+    _lib.check(rc, "moe_router_logits")
+    return out
