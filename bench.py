@@ -1,0 +1,367 @@
+"""Benchmark of the MoE-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c5|c3]
+
+One "step" is one forward pass of the routed MoE layer over one batch of synthetic
+tokens: top-k + softmax routing of the given fp32 logits, histogram / permutation,
+row gather, up GEMM with fused SiLU gate, down GEMM with fused weight scale + scatter,
+k-way combine.  The default workload is the DeepSeek-V3-shaped layer of the benchmark
+contract (T=8192, H=7168, I=2048, E=256, top-8, Zipf(1.1) expert load); with N > 1 the
+256 experts are sharded N ways and tokens travel by all-to-all (expert parallelism).
+
+Prints ONE JSON line (rank 0).  `value` is tokens/s with inputs resident in HBM;
+`e2e` times the public API with pinned host buffers (H2D of x and logits, D2H of the
+output inside the timed region); `roofline` is for the dominant kernel (the up GEMM)
+from CUDA events recorded around it in every timed step; `cpu_baseline` is the oracle
+(a port of the reference's PyTorch path) on the host cores over a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: T, H, I, E, k, shared experts
+    "c5": dict(T=8192, H=7168, I=2048, E=256, k=8, S=0, desc="DeepSeek-V3-shaped routed MoE layer, Zipf(1.1) load"),
+    "c3": dict(T=1024, H=2048, I=512, E=8, k=2, S=1, desc="FusedMoE small, 8 routed top-2 + 1 shared"),
+}
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        # the busiest samples are the ones under load: median of the upper half by power would need power;
+        # clocks rise under load on this part, so report the median of all samples taken in the region
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------- inputs
+def make_inputs(cfg, seed=0):
+    """x bf16 [T,H] ~ N(0,1) and fp32 router logits [T,E] (Zipf(1.1) popularity + Gumbel noise),
+    both drawn on the CPU from `seed` (so that the CPU baseline sees the same batch)."""
+    from tilelang_moe_b200 import inputs
+    return inputs.activations(cfg["T"], cfg["H"], seed), inputs.zipf_logits(cfg["T"], cfg["E"], 1.1, seed=seed)
+
+
+def make_weights(cfg, device, experts=None, seed=1234):
+    """bf16 weights ~ N(0, 0.02) generated on the device, expert by expert from seed+e
+    (so any shard, or the CPU sample, can regenerate exactly the experts it owns)."""
+    E = cfg["E"] if experts is None else len(experts)
+    ids = range(cfg["E"]) if experts is None else experts
+    H, I = cfg["H"], cfg["I"]
+    Wg = torch.empty(E, I, H, dtype=torch.bfloat16, device=device)
+    Wu = torch.empty(E, I, H, dtype=torch.bfloat16, device=device)
+    Wd = torch.empty(E, H, I, dtype=torch.bfloat16, device=device)
+    g = torch.Generator(device=device)
+    for j, e in enumerate(ids):
+        g.manual_seed(seed + int(e))
+        Wg[j] = torch.randn(I, H, generator=g, device=device, dtype=torch.float32).mul_(0.02)
+        Wu[j] = torch.randn(I, H, generator=g, device=device, dtype=torch.float32).mul_(0.02)
+        Wd[j] = torch.randn(H, I, generator=g, device=device, dtype=torch.float32).mul_(0.02)
+    return Wg, Wu, Wd
+
+
+# --------------------------------------------------------------------------------------- CPU arm
+def cpu_sample(cfg, x, logits, weights_for, target_rows=4096):
+    """Time the oracle's routed-expert loop (port of the reference's PyTorch CPU path, bf16)
+    on the experts of this batch in ascending id until about `target_rows` routed rows are
+    covered; scale to the whole batch by routed rows.  Returns (tokens_per_s, description)."""
+    from oracle import moe_oracle as O
+    T, k, E = cfg["T"], cfg["k"], cfg["E"]
+    t0 = time.perf_counter()
+    scores, idx = O.topk_softmax(logits, k, "A")
+    counts, offsets, perm, _ = O.route_histogram(idx, E)
+    t_route = time.perf_counter() - t0
+    token_of = perm.long() // k
+    flat_scores = scores.reshape(-1, 1).bfloat16()
+    cache = torch.zeros(T, cfg["H"], dtype=torch.bfloat16)
+    rows_done, n_exp, t_ffn = 0, 0, 0.0
+    for e in range(E):
+        s, t = int(offsets[e]), int(offsets[e + 1])
+        if s == t:
+            continue
+        Wg, Wu, Wd = weights_for(e)
+        tok = token_of[s:t]
+        t1 = time.perf_counter()
+        out = O.expert_ffn(x[tok], Wg, Wu, Wd) * flat_scores[perm.long()[s:t]]
+        cache.index_add_(0, tok, out)
+        t_ffn += time.perf_counter() - t1
+        rows_done += t - s
+        n_exp += 1
+        if rows_done >= target_rows:
+            break
+    total_rows = T * k
+    est = t_route + t_ffn * total_rows / max(rows_done, 1)
+    desc = (f"oracle port (torch CPU, bf16), routing of all {T} tokens + first {n_exp} non-empty experts "
+            f"({rows_done} of {total_rows} routed rows, {t_ffn:.2f} s), scaled by routed rows")
+    return T / est, desc
+
+
+def run_reference_arm(args, cfg):
+    """The reference's CPU path (the oracle port: the reference checkout is not on the GPU box)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    x, logits = make_inputs(cfg)
+    cache = {}
+
+    def weights_for(e):
+        if e not in cache:
+            g = torch.Generator().manual_seed(1234 + e)
+            H, I = cfg["H"], cfg["I"]
+            cache[e] = tuple((torch.randn(*s, generator=g) * 0.02).bfloat16() for s in ((I, H), (I, H), (H, I)))
+        return cache[e]
+
+    target = max(512, min(4096, cfg["T"] * cfg["k"]))
+    for _ in range(args.warmup):
+        cpu_sample(cfg, x, logits, weights_for, target_rows=256)
+    vals, desc = [], ""
+    for _ in range(args.steps):
+        v, desc = cpu_sample(cfg, x, logits, weights_for, target_rows=target)
+        vals.append(v)
+    v = statistics.median(vals)
+    cores = torch.get_num_threads()
+    line = {"metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": cfg["T"] / v * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, **{k_: cfg[k_] for k_ in ("T", "H", "I", "E", "k")}},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------- GPU arm
+def run_ours(args, cfg):
+    import torch.distributed as dist
+    from tilelang_moe_b200 import _lib, ep, layer, ops
+    _lib.load()   # fails loudly if the CUDA library is missing
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    T, H, I, E, k = (cfg[n] for n in ("T", "H", "I", "E", "k"))
+    x_cpu, logits_cpu = make_inputs(cfg)
+    peaks = _peaks()
+
+    if world == 1:
+        Wg, Wu, Wd = make_weights(cfg, dev)
+        ws = layer.MoEWorkspace(T, k, H, I, E, 0, dev)
+        x = x_cpu.to(dev)
+        logits = logits_cpu.to(dev)
+        ev = {}
+
+        def step(timers=None):
+            scores, idx32 = ops.topk_softmax(logits, k, mode="A", index_dtype=torch.int32)
+            return layer.routed_forward(x, scores, idx32, Wg, Wu, Wd, ws, timers=timers)
+
+        launches_per_step = 8
+        x_pin = x_cpu.pin_memory()
+        lg_pin = logits_cpu.pin_memory()
+        out_pin = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+        x_dev = torch.empty_like(x)
+        lg_dev = torch.empty_like(logits)
+
+        def step_e2e():
+            x_dev.copy_(x_pin, non_blocking=True)
+            lg_dev.copy_(lg_pin, non_blocking=True)
+            scores, idx32 = ops.topk_softmax(lg_dev, k, mode="A", index_dtype=torch.int32)
+            y = layer.routed_forward(x_dev, scores, idx32, Wg, Wu, Wd, ws)
+            out_pin.copy_(y, non_blocking=True)
+
+        tokens_per_step = T
+        h2d = x_pin.numel() * 2 + lg_pin.numel() * 4
+        d2h = out_pin.numel() * 2
+        parallelism = "1 GPU, 256 experts resident"
+        imbalance = None
+    else:
+        runner = ep.EPRunner(cfg, rank, world, dev, make_weights)
+        step, step_e2e, launches_per_step, h2d, d2h = runner.bench_closures(x_cpu, logits_cpu)
+        tokens_per_step = T
+        parallelism = f"ep{world}: {E // world} experts per GPU, tokens split {T // world} per rank, NCCL all-to-all"
+        imbalance = runner.imbalance
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps, with_timers=False):
+        sync_all()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stage_events = []
+        e0.record()
+        for _ in range(steps):
+            if with_timers:
+                tm = {}
+                fn(timers=tm)
+                stage_events.append(tm)
+            else:
+                fn()
+        e1.record()
+        sync_all()
+        clocks = sampler.stop() if rank == 0 else None
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, stage_events, clocks
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ms, stage_events, clocks = timed(step, args.steps, with_timers=True)
+    ops.check_status(dev)
+    for _ in range(2):
+        step_e2e()
+    ms_e2e, _, _ = timed(step_e2e, args.steps)
+
+    # per-stage device time from the events recorded inside the timed steps
+    stages = {}
+    for tm in stage_events:
+        for name, ev in tm.items():
+            if not name.startswith("_"):
+                stages.setdefault(name, []).append(ev[0].elapsed_time(ev[1]))
+    stage_ms = {n: sum(v) / len(v) for n, v in stages.items()}
+
+    roofline = None
+    if "up_gemm" in stage_ms:
+        rows = T * k if world == 1 else sum(tm.get("_n_recv", 0) for tm in stage_events) / max(len(stage_events), 1)
+        flops = 2.0 * rows * H * (2 * I)
+        achieved = flops / (stage_ms["up_gemm"] * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        roofline = {"kernel": "grouped_gemm_kernel<256,SILU_GATE> (up GEMM, tcgen05)", "bound": "tensor",
+                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "traffic": None,
+                    "ms_per_launch": stage_ms["up_gemm"]}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu_v, cpu_desc = None, None
+    if world == 1 and not args.no_cpu:
+        torch.set_num_threads(os.cpu_count() or 1)
+
+        def weights_for(e):
+            return Wg[e].cpu(), Wu[e].cpu(), Wd[e].cpu()
+
+        cpu_v, cpu_desc = cpu_sample(cfg, x_cpu, logits_cpu, weights_for, target_rows=2048 if T * k > 4096 else T * k)
+
+    value = tokens_per_step * args.steps / (ms * 1e-3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {cfg['desc']}", "T": T, "H": H, "I": I, "E": E, "k": k,
+                   "parallelism": parallelism, "l2": "per-step inputs (weights) exceed L2 many times over; no flush",
+                   "load_imbalance_max_over_mean": imbalance},
+        "e2e": {"value": tokens_per_step * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "stage_ms": stage_ms,
+        "roofline": roofline,
+        "clocks": clocks,
+    }
+    if cpu_v is not None:
+        line["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": cpu_desc}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

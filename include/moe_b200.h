@@ -12,7 +12,7 @@
  *     unless the parameter comment says "host";
  *   - the library never allocates or frees memory on behalf of these calls:
  *     scratch is passed in as (ws, ws_bytes), sized by the matching *_workspace
- *     query (the one exception is declared at the end of this file);
+ *     query;
  *   - every call only enqueues work on `stream` (a cudaStream_t passed as void*)
  *     and returns without synchronising;
  *   - return value: 0 ok; negative = argument / shape error found on the host
@@ -78,19 +78,19 @@ int moe_topk_softmax(const float* logits, int64_t M, int64_t N, int64_t ld, int 
  * row-major.  counts int32 [E]; offsets int32 [E+1] exclusive prefix (offsets[E]=n);
  * perm int32 [n]: perm[p] = flat entry at expert-sorted position p (stable);
  * inv int32 [n]: inverse of perm.  perm / inv may be NULL.  Ids outside [0,E)
- * set status[0] and are skipped.
+ * set status[0] and are skipped.  id_map (int32 [E], may be NULL) renumbers the
+ * ids before counting (expert parallelism sorts by destination rank first).
  */
 size_t moe_route_histogram_workspace(int64_t n, int E);
-int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E, int32_t* counts,
-                        int32_t* offsets, int32_t* perm, int32_t* inv, void* ws, size_t ws_bytes,
-                        int32_t* status, void* stream);
+int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E, const int32_t* id_map,
+                        int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv, void* ws,
+                        size_t ws_bytes, int32_t* status, void* stream);
 
 /* ---- row gather -----------------------------------------------------------------
  * dst[p, :] = src[perm[p] / div, :] for p < n_rows (rows of `cols` bf16, 16-byte
  * aligned, cols % 8 == 0).  Replaces the expert-stacking copy loops of
  * kernels/fusedmoe_tilelang.py:346-355 and X[sorted] in grouped_gemm_tilelang.py:700.
  * If w_src != NULL also w_dst[p] = w_src[perm[p]] (fp32 routing weights).
- * n_rows_dev (device int32, may be NULL) overrides n_rows when it is smaller.
  */
 int moe_gather_rows(const void* src, const int32_t* perm, int div, int64_t n_rows, int64_t cols,
                     void* dst, const float* w_src, float* w_dst, void* stream);
@@ -117,12 +117,14 @@ int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2,
                      void* stream);
 
 /* ---- combine ----------------------------------------------------------------------
- * out[t,:] = (shared ? shared[t,:] : 0) + sum_{s<k} Yk[t*k+s,:], fp32 sum in slot
- * order, rounded once to bf16.  Replaces scatter_reduce_ + add of
- * kernels/fusedmoe_baseline.py:90,161-166.  H % 8 == 0.
+ * out[t,:] = (shared ? shared[t,:] : 0) + sum_{s<k} c(t,s) * Yk[r(t,s),:], fp32 sum in
+ * slot order, rounded once to bf16, with f = t*k+s, r = row_of ? row_of[f] : f and
+ * c = scale ? scale[f] : 1.  Replaces scatter_reduce_ + add of
+ * kernels/fusedmoe_baseline.py:90,161-166 (and, with scale, the weighting of :156-158
+ * when expert outputs come back unscaled from other ranks).  H % 8 == 0.
  */
-int moe_combine(const void* Yk, const void* shared, int64_t T, int k, int64_t H, void* out,
-                void* stream);
+int moe_combine(const void* Yk, const void* shared, const int32_t* row_of, const float* scale,
+                int64_t T, int k, int64_t H, void* out, void* stream);
 
 /* ---- router logits ------------------------------------------------------------------
  * logits[t,e] = sum_h x[t,h] * Wr[e,h], bf16 inputs, fp32 accumulate and output.
@@ -130,6 +132,17 @@ int moe_combine(const void* Yk, const void* shared, int64_t T, int k, int64_t H,
  */
 int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, float* logits,
                       int32_t* status, void* stream);
+
+/* ---- expert-parallel regroup table -----------------------------------------------------
+ * No counterpart in the reference (it has no multi-GPU code).  recv_counts int32
+ * [G][E_local]: rows received from source rank s for local expert j, laid out
+ * source-major in the receive buffer.  Writes offsets int32 [E_local+1] (expert-major
+ * exclusive prefix, the `offsets` of moe_grouped_gemm) and src_row int32 [n_recv]:
+ * the receive-buffer row held at expert-major position p (gather list before the up
+ * GEMM, dst_rows of the down GEMM).  G * E_local <= 20000.
+ */
+int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets,
+                   int32_t* src_row, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,92 @@
+"""Expert-parallel host protocol on two (and four) gloo ranks with CPU stand-in ops: the sharded layer
+must return what the single-process oracle returns, for contiguous and load-balanced placements."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import moe_oracle as O
+from tilelang_moe_b200 import ep, inputs
+
+
+def test_balanced_placement_properties():
+    load = [1000, 10, 10, 10, 900, 20, 20, 20]
+    e2r = ep.balanced_placement(load, 2)
+    assert sorted(e2r.count(r) for r in range(2)) == [4, 4]
+    assert e2r[0] != e2r[4]                       # the two heavy experts are split up
+    plan = ep.EPPlan(8, 2, e2r)
+    assert sorted(plan.id_map) == list(range(8))
+    assert plan.imbalance(load) < ep.EPPlan(8, 2, ep.contiguous_placement(8, 2)).imbalance([1000, 900, 10, 10, 10, 20, 20, 20])
+    for r in range(2):
+        for slot, e in enumerate(plan.local_experts[r]):
+            assert plan.id_map[e] == r * 4 + slot
+    with pytest.raises(ValueError):
+        ep.EPPlan(8, 2, [0] * 8)
+
+
+def test_zipf_placement_reduces_imbalance():
+    lg = inputs.zipf_logits(4096, 256, 1.1, seed=0)
+    _, idx = O.topk_softmax(lg, 8, "A")
+    counts = O.route_histogram(idx, 256)[0].tolist()
+    calib = inputs.zipf_logits(4096, 256, 1.1, seed=0, noise_seed=77)
+    ccounts = O.route_histogram(O.topk_softmax(calib, 8, "A")[1], 256)[0].tolist()
+    bal = ep.EPPlan(256, 8, ep.balanced_placement(ccounts, 8)).imbalance(counts)
+    con = ep.EPPlan(256, 8, ep.contiguous_placement(256, 8)).imbalance(counts)
+    assert bal < 1.15 and bal < con
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, placement, q):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import cpu_ops
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        T, H, I, E, k = 64, 32, 16, 8, 3
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(T, H, generator=g)
+        Wg = torch.randn(E, I, H, generator=g) * 0.2
+        Wu = torch.randn(E, I, H, generator=g) * 0.2
+        Wd = torch.randn(E, H, I, generator=g) * 0.2
+        logits = inputs.zipf_logits(T, E, 1.1, seed=1)
+        _, idx = O.topk_softmax(logits, k, "A")
+        load = O.route_histogram(idx, E)[0].tolist()
+        e2r = ep.balanced_placement(load, world) if placement == "balanced" else ep.contiguous_placement(E, world)
+        plan = ep.EPPlan(E, world, e2r)
+        mine = plan.local_experts[rank]
+        Tl = T // world
+        out = ep.ep_forward(x[rank * Tl:(rank + 1) * Tl], logits[rank * Tl:(rank + 1) * Tl], k, plan,
+                            torch.tensor(plan.id_map, dtype=torch.int32), Wg[mine], Wu[mine], Wd[mine], cpu_ops)
+        ref = O.fusedmoe(x, None, None, None, None, Wg, Wu, Wd, k, logits=logits)[rank * Tl:(rank + 1) * Tl]
+        q.put((rank, float((out - ref).abs().max()), None))
+    except Exception as e:  # surfaced in the parent
+        q.put((rank, None, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,placement", [(2, "contiguous"), (2, "balanced"), (4, "balanced")])
+def test_ep_protocol_matches_single_process(world, placement):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, placement, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, err, exc in res:
+        assert exc is None, f"rank {rank}: {exc}"
+        assert err < 1e-4, f"rank {rank}: max abs error {err}"

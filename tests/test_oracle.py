@@ -108,3 +108,8 @@ def test_zipf_logits_are_skewed():
     c = c.sort(descending=True).values.float()
     assert c[0] > 4 * c[32]
     assert (idx.sort(1).values[:, 1:] != idx.sort(1).values[:, :-1]).all()
+
+
+def test_benchmark_input_recipe_matches_the_oracle_copy():
+    from tilelang_moe_b200 import inputs
+    assert torch.equal(inputs.zipf_logits(300, 64, 1.1, seed=5), O.zipf_logits(300, 64, 1.1, seed=5))

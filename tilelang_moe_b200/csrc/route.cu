@@ -17,17 +17,23 @@ namespace moe {
 constexpr int RUNIT = 1024;        // entries per warp
 constexpr int RWPB = 8;            // warps per CTA in the count / scatter kernels
 
-__device__ __forceinline__ int load_id(const void* ids, int is64, int64_t i) {
+// Expert id of flat entry i; with an id_map (int32 [E]) the id is translated, e.g. to the
+// destination-major numbering used by expert parallelism.  Out-of-range ids come back as -1.
+__device__ __forceinline__ int load_id(const void* ids, int is64, int64_t i, const int32_t* id_map, int E) {
+  int e;
   if (is64) {
     const long long v = reinterpret_cast<const long long*>(ids)[i];
-    return (v < 0 || v > 0x7FFFFFFFll) ? -1 : (int)v;
+    e = (v < 0 || v > 0x7FFFFFFFll) ? -1 : (int)v;
+  } else {
+    e = reinterpret_cast<const int*>(ids)[i];
   }
-  return reinterpret_cast<const int*>(ids)[i];
+  if (e < 0 || e >= E) return -1;
+  return id_map ? id_map[e] : e;
 }
 
 __global__ void __launch_bounds__(RWPB * 32)
-route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, int32_t* __restrict__ unit_counts,
-                   int32_t* __restrict__ status) {
+route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ id_map,
+                   int32_t* __restrict__ unit_counts, int32_t* __restrict__ status) {
   extern __shared__ int32_t sh[];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   int32_t* wh = sh + (size_t)w * E;
@@ -38,7 +44,7 @@ route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, int
   __syncwarp();
   const int64_t last = first + RUNIT < n ? first + RUNIT : n;
   for (int64_t i = first + lane; i < last; i += 32) {
-    const int e = load_id(ids, is64, i);
+    const int e = load_id(ids, is64, i, id_map, E);
     if (e >= 0 && e < E) atomicAdd(&wh[e], 1);
     else if (status) status[0] = ST_BAD_EXPERT_ID;
   }
@@ -89,8 +95,8 @@ route_scan_kernel(int32_t* __restrict__ unit_counts, int64_t n_units, int E, int
 }
 
 __global__ void __launch_bounds__(RWPB * 32)
-route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ unit_base,
-                     int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ id_map,
+                     const int32_t* __restrict__ unit_base, int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
   extern __shared__ int32_t sh[];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const unsigned lt_mask = (1u << lane) - 1u;
@@ -103,7 +109,7 @@ route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, c
   const int64_t last = first + RUNIT < n ? first + RUNIT : n;
   for (int64_t i0 = first; i0 < last; i0 += 32) {
     const int64_t i = i0 + lane;
-    int e = i < last ? load_id(ids, is64, i) : -1;
+    int e = i < last ? load_id(ids, is64, i, id_map, E) : -1;
     const bool valid = e >= 0 && e < E;
     // lanes without a valid id get a private group so that they match nobody
     const unsigned grp = __match_any_sync(0xFFFFFFFFu, valid ? (unsigned)e : (0x80000000u | (unsigned)lane));
@@ -153,9 +159,19 @@ __device__ __forceinline__ void add_bf16x8(float* acc, const uint4& v) {
   }
 }
 
+__device__ __forceinline__ void fma_bf16x8(float* acc, const uint4& v, float w) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(h[j]);
+    acc[2 * j] = fmaf(f.x, w, acc[2 * j]);
+    acc[2 * j + 1] = fmaf(f.y, w, acc[2 * j + 1]);
+  }
+}
+
 __global__ void __launch_bounds__(256)
-combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, int64_t T, int k, int vec_per_row,
-               uint4* __restrict__ out) {
+combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, const int32_t* __restrict__ row_of,
+               const float* __restrict__ scale, int64_t T, int k, int vec_per_row, uint4* __restrict__ out) {
   const int64_t total = T * vec_per_row;
   for (int64_t g = (int64_t)blockIdx.x * 256 + threadIdx.x; g < total; g += (int64_t)gridDim.x * 256) {
     const int64_t t = g / vec_per_row;
@@ -163,7 +179,12 @@ combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, i
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int s = 0; s < k; ++s) add_bf16x8(acc, __ldg(Yk + (t * k + s) * vec_per_row + v));
+    for (int s = 0; s < k; ++s) {
+      const int64_t f = t * k + s;
+      const int64_t r = row_of ? (int64_t)row_of[f] : f;
+      const uint4 y = __ldg(Yk + r * vec_per_row + v);
+      if (scale) fma_bf16x8(acc, y, scale[f]); else add_bf16x8(acc, y);
+    }
     if (shared) add_bf16x8(acc, __ldg(shared + g));
     uint4 o;
     __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -219,6 +240,89 @@ router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, 
   }
 }
 
+
+// ------------------------------------------------------------------------------------
+// expert-parallel regroup table
+//
+// After the dispatch all-to-all a rank holds rows in source-major order: for each source
+// rank s, for each local expert j, cnt[s][j] rows.  The expert GEMM wants them expert-major.
+// This kernel turns cnt (int32 [G][El]) into offsets[El+1] (expert-major exclusive prefix) and
+// src_row[p] = source-major row held at expert-major position p.  src_row serves both as the
+// gather list before the up GEMM and as the scatter list of the down GEMM's epilogue.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+ep_regroup_kernel(const int32_t* __restrict__ cnt, int G, int El, int32_t* __restrict__ offsets,
+                  int32_t* __restrict__ src_row) {
+  extern __shared__ int32_t sh[];
+  int32_t* in_start = sh;               // [G*El] source-major exclusive prefix
+  int32_t* out_start = sh + G * El;     // [G*El] expert-major start of segment (s, j), stored at [s*El + j]
+  __shared__ int32_t part[1024];
+  const int tid = threadIdx.x;
+  const int n = G * El;
+  const int per = (n + 1023) / 1024;
+
+  // pass 1: source-major exclusive scan
+  {
+    const int lo = tid * per, hi = min(n, lo + per);
+    int32_t sum = 0;
+    for (int q = lo; q < hi; ++q) sum += cnt[q];
+    part[tid] = sum;
+    __syncthreads();
+    if (tid < 32) {  // one warp scans the 1024 partial sums, 32 per lane
+      int32_t loc = 0;
+      for (int i = 0; i < 32; ++i) loc += part[tid * 32 + i];
+      int32_t inc = loc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int32_t v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (tid >= o) inc += v;
+      }
+      int32_t run = inc - loc;
+      for (int i = 0; i < 32; ++i) { const int32_t v = part[tid * 32 + i]; part[tid * 32 + i] = run; run += v; }
+    }
+    __syncthreads();
+    int32_t run = part[tid];
+    for (int q = lo; q < hi; ++q) { in_start[q] = run; run += cnt[q]; }
+    __syncthreads();
+  }
+  // pass 2: expert-major order = flattened index q' = j*G + s
+  {
+    const int lo = tid * per, hi = min(n, lo + per);
+    int32_t sum = 0;
+    for (int q = lo; q < hi; ++q) { const int j = q / G, s = q - j * G; sum += cnt[s * El + j]; }
+    part[tid] = sum;
+    __syncthreads();
+    if (tid < 32) {
+      int32_t loc = 0;
+      for (int i = 0; i < 32; ++i) loc += part[tid * 32 + i];
+      int32_t inc = loc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int32_t v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (tid >= o) inc += v;
+      }
+      int32_t run = inc - loc;
+      for (int i = 0; i < 32; ++i) { const int32_t v = part[tid * 32 + i]; part[tid * 32 + i] = run; run += v; }
+      if (tid == 31) offsets[El] = inc;
+    }
+    __syncthreads();
+    int32_t run = part[tid];
+    for (int q = lo; q < hi; ++q) {
+      const int j = q / G, s = q - j * G;
+      out_start[s * El + j] = run;
+      if (s == 0) offsets[j] = run;
+      run += cnt[s * El + j];
+    }
+    __syncthreads();
+  }
+  // fill: one warp per segment
+  const int lane = tid & 31;
+  for (int q = tid >> 5; q < n; q += 32) {
+    const int32_t c = cnt[q], a = in_start[q], b = out_start[q];
+    for (int i = lane; i < c; i += 32) src_row[b + i] = a + i;
+  }
+}
+
 }  // namespace moe
 
 // ====================================================================================
@@ -228,9 +332,9 @@ extern "C" size_t moe_route_histogram_workspace(int64_t n, int E) {
   return (size_t)units * (size_t)E * sizeof(int32_t);
 }
 
-extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E, int32_t* counts,
-                                   int32_t* offsets, int32_t* perm, int32_t* inv, void* ws, size_t ws_bytes,
-                                   int32_t* status, void* stream) {
+extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E, const int32_t* id_map,
+                                   int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv, void* ws,
+                                   size_t ws_bytes, int32_t* status, void* stream) {
   using namespace moe;
   if (n < 0 || E < 1) return fail(MOE_ERR_ARG, "route_histogram: bad size n=%lld E=%d", (long long)n, E);
   if (!counts || !offsets) return fail(MOE_ERR_ARG, "route_histogram: null counts/offsets");
@@ -249,13 +353,13 @@ extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64
   }
   const unsigned blocks = (unsigned)ceil_div64(units, RWPB);
   if (units > 0) {
-    route_count_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, unit_counts, status);
+    route_count_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
     MOE_CHECK_LAUNCH("route_count_kernel");
   }
   route_scan_kernel<<<1, 1024, 0, st>>>(unit_counts, units, E, counts, offsets);
   MOE_CHECK_LAUNCH("route_scan_kernel");
   if (units > 0 && (perm || inv)) {
-    route_scatter_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, unit_counts, perm, inv);
+    route_scatter_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
     MOE_CHECK_LAUNCH("route_scatter_kernel");
   }
   return MOE_OK;
@@ -282,7 +386,8 @@ extern "C" int moe_gather_rows(const void* src, const int32_t* perm, int div, in
   return MOE_OK;
 }
 
-extern "C" int moe_combine(const void* Yk, const void* shared, int64_t T, int k, int64_t H, void* out, void* stream) {
+extern "C" int moe_combine(const void* Yk, const void* shared, const int32_t* row_of, const float* scale, int64_t T,
+                           int k, int64_t H, void* out, void* stream) {
   using namespace moe;
   if (T < 0 || k < 0 || H < 8 || H % 8) return fail(MOE_ERR_ARG, "combine: bad shape T=%lld k=%d H=%lld", (long long)T, k, (long long)H);
   if (T == 0) return MOE_OK;
@@ -297,7 +402,7 @@ extern "C" int moe_combine(const void* Yk, const void* shared, int64_t T, int k,
   const int64_t cap = (int64_t)dev.sm_count * 8;
   if (blocks > cap) blocks = cap;
   combine_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint4*>(Yk), reinterpret_cast<const uint4*>(shared), T, k, (int)(H / 8),
+      reinterpret_cast<const uint4*>(Yk), reinterpret_cast<const uint4*>(shared), row_of, scale, T, k, (int)(H / 8),
       reinterpret_cast<uint4*>(out));
   MOE_CHECK_LAUNCH("combine_kernel");
   return MOE_OK;
@@ -320,5 +425,17 @@ extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H
   router_logits_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);
   MOE_CHECK_LAUNCH("router_logits_kernel");
+  return MOE_OK;
+}
+
+extern "C" int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets, int32_t* src_row,
+                              void* stream) {
+  using namespace moe;
+  if (!recv_counts || !offsets || !src_row) return fail(MOE_ERR_ARG, "ep_regroup: null pointer");
+  if (G < 1 || E_local < 1 || (int64_t)G * E_local > 20000) return fail(MOE_ERR_UNSUPPORTED, "ep_regroup: G*E_local=%lld out of range", (long long)G * E_local);
+  const size_t smem = (size_t)2 * G * E_local * sizeof(int32_t);
+  if (smem > 48 * 1024) MOE_CUDA_CHECK(cudaFuncSetAttribute(ep_regroup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  ep_regroup_kernel<<<1, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(recv_counts, G, E_local, offsets, src_row);
+  MOE_CHECK_LAUNCH("ep_regroup_kernel");
   return MOE_OK;
 }

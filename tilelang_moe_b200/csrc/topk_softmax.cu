@@ -148,12 +148,12 @@ constexpr int RMAX_KPAD = 4096;
 
 struct RadixCtrl {
   uint32_t warp_tot[RWARPS];
-  float warp_f[RWARPS];
+  double warp_d[RWARPS];
   uint32_t sel_bin;
   uint32_t k_rem;
   uint32_t sel_count;
   uint32_t blk_maxkey;
-  float blk_sum;
+  double blk_sum;
 };
 static_assert(sizeof(RadixCtrl) <= RCTRL_BYTES, "control block too large");
 
@@ -161,15 +161,18 @@ __device__ __forceinline__ uint64_t pack_entry(uint32_t key, uint32_t col) {
   return ((uint64_t)key << 32) | (uint64_t)(0xFFFFFFFFu - col);
 }
 
-// Sum of one float per thread over the CTA in a fixed order; result valid in every thread.
-__device__ __forceinline__ float block_sum_ordered(float v, RadixCtrl* ctrl, int lane, int wid) {
-  v = warp_sum(v);
-  __syncthreads();
-  if (lane == 0) ctrl->warp_f[wid] = v;
-  __syncthreads();
-  float t = 0.f;
+// Sum of one value per thread over the CTA in a fixed order; result valid in every thread.
+// Softmax denominators over thousands of terms are accumulated in fp64 so that the only
+// rounding left in a score is that of expf and of the final division.
+__device__ __forceinline__ double block_sum_ordered(double v, RadixCtrl* ctrl, int lane, int wid) {
 #pragma unroll
-  for (int w = 0; w < RWARPS; ++w) t += ctrl->warp_f[w];
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  __syncthreads();
+  if (lane == 0) ctrl->warp_d[wid] = v;
+  __syncthreads();
+  double t = 0.0;
+#pragma unroll
+  for (int w = 0; w < RWARPS; ++w) t += ctrl->warp_d[w];
   return t;
 }
 
@@ -196,7 +199,7 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
   if (len > slice) len = slice;
   if (len < 0) len = 0;
 
-  if (tid == 0) { ctrl->sel_count = 0u; ctrl->blk_maxkey = 0u; ctrl->blk_sum = 0.f; ctrl->sel_bin = 0u; ctrl->k_rem = 0u; }
+  if (tid == 0) { ctrl->sel_count = 0u; ctrl->blk_maxkey = 0u; ctrl->blk_sum = 0.0; ctrl->sel_bin = 0u; ctrl->k_rem = 0u; }
   for (int i = tid; i < 2 * RBINS; i += RT) hist[i] = 0u;
   if (crank == 0)
     for (int i = k + tid; i < kpad; i += RT) sbuf[i] = 0ull;
@@ -227,7 +230,7 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
 
   // ---- radix select: after three passes `prefix` is the key of the k-th largest value
   uint32_t prefix = 0u, pmask = 0u, k_rem = (uint32_t)k, bin = 0u;
-  float rowsum = 0.f;
+  double rowsum = 0.0;
   uint32_t* h = hist;
   for (int pass = 0; pass < 3; ++pass) {
     const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
@@ -278,8 +281,8 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
       uint32_t gmax = 0u;
       for (unsigned c = 0; c < C; ++c) gmax = max(gmax, cluster.map_shared_rank(ctrl, c)->blk_maxkey);
       const float vmax = key_to_float(gmax);
-      float part = 0.f;
-      for (int i = tid; i < len; i += RT) part += expf(key_to_float(keys[i]) - vmax);
+      double part = 0.0;
+      for (int i = tid; i < len; i += RT) part += (double)expf(key_to_float(keys[i]) - vmax);
       part = block_sum_ordered(part, ctrl, lane, wid);
       if (tid == 0) ctrl->blk_sum = part;  // published by the next cluster barrier
     }
@@ -361,17 +364,17 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
   const float vmax = key_to_float((uint32_t)(sbuf[0] >> 32));
   float denom;
   if (mode == MOE_TOPK_MODE_B) {
-    float part = 0.f;
-    for (int r = tid; r < k; r += RT) part += expf(key_to_float((uint32_t)(sbuf[r] >> 32)) - vmax);
-    denom = block_sum_ordered(part, ctrl, lane, wid);
+    double part = 0.0;
+    for (int r = tid; r < k; r += RT) part += (double)expf(key_to_float((uint32_t)(sbuf[r] >> 32)) - vmax);
+    denom = (float)block_sum_ordered(part, ctrl, lane, wid);
   } else {
-    denom = rowsum;
+    denom = (float)rowsum;
   }
   float renorm = 1.f;
   if (mode == MOE_TOPK_MODE_A_RENORM) {
-    float part = 0.f;
-    for (int r = tid; r < k; r += RT) part += expf(key_to_float((uint32_t)(sbuf[r] >> 32)) - vmax) / denom;
-    renorm = block_sum_ordered(part, ctrl, lane, wid);
+    double part = 0.0;
+    for (int r = tid; r < k; r += RT) part += (double)(expf(key_to_float((uint32_t)(sbuf[r] >> 32)) - vmax) / denom);
+    renorm = (float)block_sum_ordered(part, ctrl, lane, wid);
   }
   const int64_t o = row * (int64_t)k;
   for (int r = tid; r < k; r += RT) {

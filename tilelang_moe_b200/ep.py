@@ -1,0 +1,211 @@
+"""Expert parallelism for the routed MoE layer: one process per GPU, experts sharded, tokens
+data-parallel, one exchange each way.
+
+    rank r owns T/G tokens and E/G experts (placement table expert -> rank).
+    route locally -> sort rows by (destination rank, local expert) -> counts all-to-all
+    -> dispatch all-to-all-v of bf16 rows -> regroup expert-major -> up / down GEMMs
+    -> combine all-to-all-v back -> weighted k-way sum on the owner.
+
+The reference has no distributed code (its benchmark only shrinks the expert count,
+benchmarks/benchmark_grouped_gemm.py:85-109); the contract here is that the sharded
+layer returns what the single-GPU layer returns.  Received rows always sit in this
+GPU's own memory before a kernel touches them.
+
+The protocol is written against a small ops namespace (``tilelang_moe_b200.ops`` in
+production) so that its host logic - placement, split sizes, the two permutations and
+their inverses - can be exercised on CPU ranks over gloo with stand-in ops.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+# --------------------------------------------------------------------------- placement
+def contiguous_placement(n_experts: int, world: int) -> List[int]:
+    per = n_experts // world
+    return [e // per for e in range(n_experts)]
+
+
+def balanced_placement(load: Sequence[float], world: int) -> List[int]:
+    """Greedy longest-processing-time assignment with exactly E/world experts per rank:
+    heaviest expert first, to the least loaded rank that still has a free slot."""
+    E = len(load)
+    per = E // world
+    order = sorted(range(E), key=lambda e: (-float(load[e]), e))
+    tot = [0.0] * world
+    cnt = [0] * world
+    out = [0] * E
+    for e in order:
+        r = min((r for r in range(world) if cnt[r] < per), key=lambda r: (tot[r], r))
+        out[e] = r
+        tot[r] += float(load[e])
+        cnt[r] += 1
+    return out
+
+
+@dataclass
+class EPPlan:
+    """Static sharding of E experts over `world` ranks."""
+    n_experts: int
+    world: int
+    expert_to_rank: List[int]
+    local_experts: List[List[int]] = field(init=False)   # per rank: global ids in local slot order
+    id_map: List[int] = field(init=False)                 # global id -> rank * E_local + slot
+
+    def __post_init__(self):
+        E, G = self.n_experts, self.world
+        if E % G:
+            raise ValueError(f"{E} experts do not split evenly over {G} ranks")
+        self.e_local = E // G
+        self.local_experts = [[] for _ in range(G)]
+        self.id_map = [0] * E
+        for e in range(E):
+            r = self.expert_to_rank[e]
+            self.id_map[e] = r * self.e_local + len(self.local_experts[r])
+            self.local_experts[r].append(e)
+        if any(len(l) != self.e_local for l in self.local_experts):
+            raise ValueError("placement must give every rank the same number of experts")
+
+    def imbalance(self, counts_per_expert: Sequence[float]) -> float:
+        """max over ranks / mean over ranks of routed rows under this placement."""
+        tot = [0.0] * self.world
+        for e, c in enumerate(counts_per_expert):
+            tot[self.expert_to_rank[e]] += float(c)
+        mean = sum(tot) / self.world
+        return max(tot) / mean if mean > 0 else 1.0
+
+
+# --------------------------------------------------------------------------- protocol
+def ep_forward(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: EPPlan, id_map_dev: torch.Tensor,
+               Wg: torch.Tensor, Wu: torch.Tensor, Wd: torch.Tensor, ops, group=None, bufs: Optional[dict] = None,
+               timers: Optional[dict] = None, stage=None) -> torch.Tensor:
+    """One expert-parallel forward of the routed layer for this rank's tokens.
+
+    x_local bf16 [T_local,H]; logits_local fp32 [T_local,E]; Wg/Wu [E_local,I,H], Wd [E_local,H,I]
+    for this rank's experts in slot order.  Returns out bf16 [T_local,H].
+    """
+    G, El, E = plan.world, plan.e_local, plan.n_experts
+    Tl, H = x_local.shape
+    n = Tl * k
+    st = stage if stage is not None else (lambda name: _null)
+    bufs = {} if bufs is None else bufs
+
+    with st("route"):
+        scores, idx32 = ops.topk_softmax(logits_local, k, mode="A", index_dtype=torch.int32)
+        counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map_dev, workspace=bufs.get("hist_ws"))
+        xs = ops.gather_rows(x_local, perm, div=k, out=bufs.get("xs"))
+    with st("counts_a2a"):
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=group)      # equal splits of E_local ints
+        sizes = torch.stack([counts.view(G, El).sum(1), recv_counts.view(G, El).sum(1)]).cpu()   # one D2H sync
+        in_splits, out_splits = sizes[0].tolist(), sizes[1].tolist()
+        n_recv = int(sum(out_splits))
+    with st("dispatch_a2a"):
+        recv = _take(bufs, "recv", n_recv, H, x_local)
+        dist.all_to_all_single(recv, xs, out_splits, in_splits, group=group)
+    with st("regroup"):
+        offs_local, src_row = ops.ep_regroup(recv_counts.view(G, El), max(n_recv, 1))
+        xl = ops.gather_rows(recv, src_row, out=_take(bufs, "xl", n_recv, H, x_local), n_rows=n_recv)
+    with st("up_gemm"):
+        act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, xl, Wg, offs_local, B2=Wu,
+                                      out=_take(bufs, "act", n_recv, Wg.shape[1], x_local))
+    with st("down_gemm"):
+        yb = ops.grouped_gemm_sorted(ops.GEMM_PLAIN, act, Wd, offs_local, dst_rows=src_row,
+                                     out=_take(bufs, "yb", n_recv, H, x_local))
+    with st("combine_a2a"):
+        yret = _take(bufs, "yret", n, H, x_local)
+        dist.all_to_all_single(yret, yb, in_splits, out_splits, group=group)
+    with st("combine"):
+        out = ops.combine(yret, k, row_of=inv, scale=scores.reshape(-1), T=Tl, out=bufs.get("out"))
+    if timers is not None:
+        timers["_n_recv"] = n_recv
+    return out
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+_null = _Null()
+
+
+def _take(bufs: dict, name: str, rows: int, cols: int, like: torch.Tensor) -> torch.Tensor:
+    """A [rows, cols] view of a persistent buffer (grown on demand), or a fresh tensor."""
+    buf = bufs.get(name)
+    if buf is None or buf.shape[0] < rows or buf.shape[1] != cols:
+        buf = torch.empty(max(rows, 1), cols, dtype=like.dtype, device=like.device)
+        bufs[name] = buf
+    return buf[:rows]
+
+
+# --------------------------------------------------------------------------- bench runner
+class EPRunner:
+    """Holds one rank's shard (weights of its experts, buffers) for the benchmark workload."""
+
+    def __init__(self, cfg: dict, rank: int, world: int, device: torch.device, make_weights: Callable,
+                 placement: str = "balanced", calib_seed: int = 1):
+        from . import _lib, ops
+        from .layer import _Stage
+        self.ops, self._Stage = ops, _Stage
+        self.cfg, self.rank, self.world, self.dev = cfg, rank, world, device
+        T, E, k = cfg["T"], cfg["E"], cfg["k"]
+        if T % world:
+            raise ValueError("tokens must split evenly over the ranks")
+        self.Tl = T // world
+        # placement from the expert loads of a calibration batch with the same popularity law
+        # (a different noise draw than the timed batch): what a serving system knows in advance
+        load = self._calibration_load(cfg, calib_seed)
+        e2r = balanced_placement(load, world) if placement == "balanced" else contiguous_placement(E, world)
+        self.plan = EPPlan(E, world, e2r)
+        self.id_map_dev = torch.tensor(self.plan.id_map, dtype=torch.int32, device=device)
+        self.Wg, self.Wu, self.Wd = make_weights(cfg, device, experts=self.plan.local_experts[rank])
+        need = _lib.load().moe_route_histogram_workspace(self.Tl * k, E)
+        self.bufs = {"hist_ws": torch.empty(max(need, 4), dtype=torch.uint8, device=device)}
+        self.imbalance = None
+
+    def _routed_counts(self, logits_cpu: torch.Tensor) -> List[int]:
+        """Rows per expert when `logits_cpu` is routed top-k (through the router and histogram kernels)."""
+        _, idx32 = self.ops.topk_softmax(logits_cpu.to(self.dev), self.cfg["k"], mode="A", index_dtype=torch.int32)
+        counts, _, _, _ = self.ops.route_histogram(idx32, self.cfg["E"], want_perm=False, want_inv=False)
+        return counts.cpu().tolist()
+
+    def _calibration_load(self, cfg, seed):
+        from .inputs import zipf_logits
+        return self._routed_counts(zipf_logits(cfg["T"], cfg["E"], 1.1, seed=0, noise_seed=seed + 1000))
+
+    def forward(self, x_local, logits_local, timers=None):
+        stage = (lambda name: self._Stage(timers, name)) if timers is not None else None
+        return ep_forward(x_local, logits_local, self.cfg["k"], self.plan, self.id_map_dev, self.Wg, self.Wu,
+                          self.Wd, self.ops, bufs=self.bufs, timers=timers, stage=stage)
+
+    def bench_closures(self, x_cpu, logits_cpu):
+        """(step, step_e2e, launches per step, h2d bytes, d2h bytes) for this rank's share of the batch."""
+        Tl, r, dev = self.Tl, self.rank, self.dev
+        self.imbalance = self.plan.imbalance(self._routed_counts(logits_cpu))
+        x_l = x_cpu[r * Tl:(r + 1) * Tl].contiguous()
+        lg_l = logits_cpu[r * Tl:(r + 1) * Tl].contiguous()
+        x, lg = x_l.to(dev), lg_l.to(dev)
+        x_pin, lg_pin = x_l.pin_memory(), lg_l.pin_memory()
+        out_pin = torch.empty(Tl, x_l.shape[1], dtype=torch.bfloat16).pin_memory()
+        x_dev, lg_dev = torch.empty_like(x), torch.empty_like(lg)
+
+        def step(timers=None):
+            return self.forward(x, lg, timers=timers)
+
+        def step_e2e():
+            x_dev.copy_(x_pin, non_blocking=True)
+            lg_dev.copy_(lg_pin, non_blocking=True)
+            out_pin.copy_(self.forward(x_dev, lg_dev), non_blocking=True)
+
+        # kernels of this library per step: topk, 3 x histogram, gather, regroup, gather, up, down, combine
+        h2d = (x_pin.numel() * 2 + lg_pin.numel() * 4) * self.world
+        d2h = out_pin.numel() * 2 * self.world
+        return step, step_e2e, 10, h2d, d2h

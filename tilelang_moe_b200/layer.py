@@ -49,18 +49,44 @@ class MoEWorkspace:
         self.out = torch.empty(self.T, self.H, dtype=bf16, device=dev)
 
 
+class _Stage:
+    """Records a CUDA event pair around a stage when a timers dict is given (else does nothing)."""
+
+    def __init__(self, timers, name):
+        self.timers, self.name = timers, name
+
+    def __enter__(self):
+        if self.timers is not None:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+    def __exit__(self, *exc):
+        if self.timers is not None:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            self.timers[self.name] = (self.a, b)
+
+
 def routed_forward(x_flat: torch.Tensor, scores: torch.Tensor, idx32: torch.Tensor, routed_gate: torch.Tensor,
                    routed_up: torch.Tensor, routed_down: torch.Tensor, ws: MoEWorkspace,
-                   shared_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Routed experts + combine for routing already decided (scores fp32 [T,k], idx32 int32 [T,k])."""
+                   shared_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                   timers: Optional[dict] = None) -> torch.Tensor:
+    """Routed experts + combine for routing already decided (scores fp32 [T,k], idx32 int32 [T,k]).
+    ``timers``: optional dict that receives a CUDA event pair per stage."""
     E = routed_gate.shape[0]
     k = idx32.shape[1]
-    counts, offsets, perm, _ = ops.route_histogram(idx32, E, want_inv=False, workspace=ws.hist_ws)
-    ops.gather_rows(x_flat, perm, div=k, out=ws.xs, w_src=scores, w_out=ws.ws)
-    ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, ws.xs, routed_gate, offsets, B2=routed_up, out=ws.act)
-    ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, ws.act, routed_down, offsets, dst_rows=perm, row_w=ws.ws,
-                            out=ws.yk)
-    return ops.combine(ws.yk, k, shared=shared_out, out=ws.out if out is None else out)
+    with _Stage(timers, "histogram"):
+        counts, offsets, perm, _ = ops.route_histogram(idx32, E, want_inv=False, workspace=ws.hist_ws)
+    with _Stage(timers, "gather"):
+        ops.gather_rows(x_flat, perm, div=k, out=ws.xs, w_src=scores, w_out=ws.ws)
+    with _Stage(timers, "up_gemm"):
+        ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, ws.xs, routed_gate, offsets, B2=routed_up, out=ws.act)
+    with _Stage(timers, "down_gemm"):
+        ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, ws.act, routed_down, offsets, dst_rows=perm, row_w=ws.ws,
+                                out=ws.yk)
+    with _Stage(timers, "combine"):
+        y = ops.combine(ws.yk, k, shared=shared_out, out=ws.out if out is None else out)
+    return y
 
 
 def shared_forward(x_flat: torch.Tensor, shared_gate: torch.Tensor, shared_up: torch.Tensor,

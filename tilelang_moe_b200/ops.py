@@ -99,7 +99,7 @@ def topk_softmax(logits: torch.Tensor, k: int, mode="B", index_dtype: torch.dtyp
 
 # ----------------------------------------------------------------------------- permutation
 def route_histogram(topk_idx: torch.Tensor, n_experts: int, want_perm: bool = True, want_inv: bool = True,
-                    workspace: Optional[torch.Tensor] = None):
+                    workspace: Optional[torch.Tensor] = None, id_map: Optional[torch.Tensor] = None):
     """counts [E], exclusive offsets [E+1], stable permutation perm [n] and its inverse inv [n]
     (all int32) of the flattened expert ids."""
     _need_cuda(topk_idx)
@@ -117,7 +117,7 @@ def route_histogram(topk_idx: torch.Tensor, n_experts: int, want_perm: bool = Tr
     if workspace is None or workspace.numel() * workspace.element_size() < need:
         workspace = torch.empty(max(need, 4), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
-        rc = lib.moe_route_histogram(_ptr(ids), int(ids.dtype == torch.int64), n, n_experts, _ptr(counts),
+        rc = lib.moe_route_histogram(_ptr(ids), int(ids.dtype == torch.int64), n, n_experts, _ptr(id_map), _ptr(counts),
                                      _ptr(offsets), _ptr(perm), _ptr(inv), _ptr(workspace),
                                      workspace.numel() * workspace.element_size(), _ptr(status_buffer(dev)), _stream())
     _lib.check(rc, "moe_route_histogram")
@@ -181,16 +181,19 @@ def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets
     return out
 
 
-def combine(Yk: torch.Tensor, k: int, shared: Optional[torch.Tensor] = None,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = shared[t] + sum over the k slot rows Yk[t*k : t*k+k] (fp32 sum, one bf16 rounding)."""
+def combine(Yk: torch.Tensor, k: int, shared: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+            row_of: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
+            T: Optional[int] = None) -> torch.Tensor:
+    """out[t] = shared[t] + sum_s scale[t*k+s] * Yk[row_of[t*k+s]] (fp32 sum, one bf16 rounding);
+    row_of defaults to the identity and scale to 1."""
     _need_cuda(Yk, shared)
     n, H = Yk.shape
-    T = n // k
+    if T is None:
+        T = (row_of.numel() if row_of is not None else n) // k
     if out is None:
         out = torch.empty(T, H, dtype=torch.bfloat16, device=Yk.device)
     with torch.cuda.device(Yk.device):
-        rc = _lib.load().moe_combine(_ptr(Yk), _ptr(shared), T, k, H, _ptr(out), _stream())
+        rc = _lib.load().moe_combine(_ptr(Yk), _ptr(shared), _ptr(row_of), _ptr(scale), T, k, H, _ptr(out), _stream())
     _lib.check(rc, "moe_combine")
     return out
 
@@ -209,3 +212,16 @@ def router_logits(x: torch.Tensor, router_weight: torch.Tensor, out: Optional[to
                                            _ptr(status_buffer(x.device)), _stream())
     _lib.check(rc, "moe_router_logits")
     return out
+
+
+def ep_regroup(recv_counts: torch.Tensor, n_recv_bound: int):
+    """recv_counts int32 [G, E_local] -> (offsets int32 [E_local+1], src_row int32 [n_recv_bound])."""
+    _need_cuda(recv_counts)
+    G, El = recv_counts.shape
+    dev = recv_counts.device
+    offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+    src_row = torch.empty(max(n_recv_bound, 1), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().moe_ep_regroup(_ptr(recv_counts.contiguous()), G, El, _ptr(offsets), _ptr(src_row), _stream())
+    _lib.check(rc, "moe_ep_regroup")
+    return offsets, src_row
