@@ -11,12 +11,19 @@ pytestmark = pytest.mark.gpu
 RTOL = 1e-6  # fp32 softmax scores, relative
 
 
-def _check(logits_cpu, k, mode, dev, rtol=RTOL):
+def _check(logits_cpu, k, mode, dev, rtol=RTOL, oracle_slack=False):
     s_ref, i_ref = O.topk_softmax(logits_cpu, k, mode)
     s, i = ops.topk_softmax(logits_cpu.to(dev), k, mode=mode)
     ops.check_status(dev)
     assert i.dtype == torch.int64 and s.dtype == torch.float32
     assert torch.equal(i.cpu(), i_ref), f"indices differ (mode {mode}, shape {tuple(logits_cpu.shape)}, k={k})"
+    if oracle_slack:
+        # quantised inputs repeat the same addend thousands of times, which biases an fp32 running sum:
+        # the fp32 oracle itself is then ~1e-6 away from the exact softmax.  Hold the kernel to 1e-6 of the
+        # exact (fp64) value, and to 1e-6 plus the oracle's own measured error against the oracle.
+        exact = torch.softmax(torch.gather(logits_cpu, 1, i_ref).double(), -1)
+        torch.testing.assert_close(s.cpu().double(), exact, rtol=rtol, atol=1e-30)
+        rtol = rtol + float(((s_ref.double() - exact).abs() / exact).max())
     torch.testing.assert_close(s.cpu(), s_ref, rtol=rtol, atol=1e-30)
     return s, i
 
@@ -70,10 +77,10 @@ def test_radix_ties_straddling_the_threshold(cuda, lib):
     # heavy quantisation: many equal values exactly at the k-th place, spread over all slices
     g = torch.Generator().manual_seed(5)
     q = torch.round(torch.randn(16, 16384, generator=g) * 4) / 4
-    _check(q, 1000, "B", cuda)
-    _check(q, 77, "B", cuda)
+    _check(q, 1000, "B", cuda, oracle_slack=True)
+    _check(q, 77, "B", cuda, oracle_slack=True)
     const = torch.zeros(3, 5000)
-    _check(const, 1234, "B", cuda)
+    _check(const, 1234, "B", cuda, oracle_slack=True)
 
 
 def test_row_stride_and_unaligned(cuda, lib):
