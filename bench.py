@@ -36,6 +36,8 @@ import torch  # noqa: E402
 WORKLOADS = {
     # name: T, H, I, E, k, shared experts
     "c5": dict(T=8192, H=7168, I=2048, E=256, k=8, S=0, desc="DeepSeek-V3-shaped routed MoE layer, Zipf(1.1) load"),
+    # the per-GPU share of c5 under 8-way expert parallelism (32 experts, 8192 routed rows): small enough to profile
+    "c5_shard8": dict(T=1024, H=7168, I=2048, E=32, k=8, S=0, desc="one rank's share of c5 at 8-way expert parallelism"),
     "c3": dict(T=1024, H=2048, I=512, E=8, k=2, S=1, desc="FusedMoE small, 8 routed top-2 + 1 shared"),
 }
 METRIC = "moe_layer_tokens_per_s"
