@@ -86,6 +86,26 @@ int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E
                         int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv, void* ws,
                         size_t ws_bytes, int32_t* status, void* stream);
 
+/* Same result as moe_route_histogram, for callers that cannot hand over a workspace.
+ * This entry point has no counterpart in the reference.  Some hosts give a plug-in only
+ * its input and output buffers and forbid it to create device memory of its own: a
+ * serving loop that may not stall on the device-wide synchronisation an allocation can
+ * cause, or an embedding runtime that owns the whole memory pool.  For them the count
+ * table lives in a 1 MiB array built into the library's device image (present on every
+ * GPU that loads the library until the process exits).
+ *   - limit: ceil(n / 1024) * E <= 262144, otherwise MOE_ERR_UNSUPPORTED (use the
+ *     workspace variant); with E = 256 that is n <= 1 048 576 routed entries;
+ *   - the first call on each GPU looks up the array's device address; make that call
+ *     outside any stream capture;
+ *   - all calls on a GPU share the one array: two calls whose kernels may overlap on the
+ *     device (different streams, no ordering between them) race and give wrong results.
+ *     Calls ordered on one stream are safe, and nothing needs clearing between them;
+ *   - the call itself allocates and frees nothing.
+ */
+int moe_route_histogram_static(const void* topk_idx, int idx_is_int64, int64_t n, int E,
+                               const int32_t* id_map, int32_t* counts, int32_t* offsets,
+                               int32_t* perm, int32_t* inv, int32_t* status, void* stream);
+
 /* ---- row gather -----------------------------------------------------------------
  * dst[p, :] = src[perm[p] / div, :] for p < n_rows (rows of `cols` bf16, 16-byte
  * aligned, cols % 8 == 0).  Replaces the expert-stacking copy loops of

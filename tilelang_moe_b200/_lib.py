@@ -19,6 +19,7 @@ SIGNATURES = {
     "moe_topk_softmax": (_i32, [_vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "moe_route_histogram_workspace": (_sz, [_i64, _i32]),
     "moe_route_histogram": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "moe_route_histogram_static": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "moe_gather_rows": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _vp, _vp, _vp]),
     "moe_grouped_gemm": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _vp]),
     "moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _vp, _vp]),

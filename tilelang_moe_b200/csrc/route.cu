@@ -3,6 +3,8 @@
 // warp-private shared-memory histograms, no host round trip.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace moe {
 
 // ------------------------------------------------------------------------------------
@@ -437,5 +439,75 @@ extern "C" int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, in
   if (smem > 48 * 1024) MOE_CUDA_CHECK(cudaFuncSetAttribute(ep_regroup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   ep_regroup_kernel<<<1, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(recv_counts, G, E_local, offsets, src_row);
   MOE_CHECK_LAUNCH("ep_regroup_kernel");
+  return MOE_OK;
+}
+
+// ====================================================================================
+// Histogram entry point for callers that have no scratch buffer to give.
+//
+// The per-unit count table that moe_route_histogram keeps in caller-provided workspace lives
+// here in a fixed array inside the library's device image.  The array is 1 MiB, exists once on
+// every GPU that loads the library, and is never freed.
+// ====================================================================================
+namespace moe {
+constexpr int64_t STATIC_SCRATCH_INTS = 262144;   // 1 MiB of int32
+static __device__ __align__(256) int32_t g_route_static_scratch[STATIC_SCRATCH_INTS];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can use;
+// the device address is looked up once per GPU (with that GPU current) and remembered.
+static int static_scratch_address(int32_t** out) {
+  static std::mutex mu;
+  static int32_t* cached[64] = {nullptr};
+  int dev = 0;
+  MOE_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MOE_ERR_DEVICE, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    int32_t* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_route_static_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_route_static_scratch)");
+    if (!ptr) return fail(MOE_ERR_DEVICE, "no device address for the built-in scratch array");
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return MOE_OK;
+}
+}  // namespace moe
+
+extern "C" int moe_route_histogram_static(const void* topk_idx, int idx_is_int64, int64_t n, int E,
+                                          const int32_t* id_map, int32_t* counts, int32_t* offsets, int32_t* perm,
+                                          int32_t* inv, int32_t* status, void* stream) {
+  using namespace moe;
+  if (n < 0 || E < 1) return fail(MOE_ERR_ARG, "route_histogram_static: bad size n=%lld E=%d", (long long)n, E);
+  if (!counts || !offsets) return fail(MOE_ERR_ARG, "route_histogram_static: null counts/offsets");
+  if (n > 0 && !topk_idx) return fail(MOE_ERR_ARG, "route_histogram_static: null ids");
+  if ((size_t)RWPB * E * 4 > 160 * 1024) return fail(MOE_ERR_UNSUPPORTED, "route_histogram_static: E=%d too large", E);
+  const int64_t units = ceil_div64(n, RUNIT);
+  if (units * (int64_t)E > STATIC_SCRATCH_INTS)
+    return fail(MOE_ERR_UNSUPPORTED,
+                "route_histogram_static: ceil(n/%d)*E = %lld exceeds the built-in scratch of %lld entries; "
+                "use moe_route_histogram with a workspace", RUNIT, (long long)(units * E), (long long)STATIC_SCRATCH_INTS);
+  int32_t* unit_counts = nullptr;
+  int rc = static_scratch_address(&unit_counts);   // first call on a GPU performs the look-up
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)RWPB * E * 4;
+  if (smem > 48 * 1024) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
+  const unsigned blocks = (unsigned)ceil_div64(units, RWPB);
+  // Nothing in the array has to start at zero: the count kernel writes every entry of the
+  // units x E table it will later read, so whatever an earlier call left behind is overwritten.
+  if (units > 0) {
+    route_count_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
+    MOE_CHECK_LAUNCH("route_count_kernel");
+  }
+  route_scan_kernel<<<1, 1024, 0, st>>>(unit_counts, units, E, counts, offsets);
+  MOE_CHECK_LAUNCH("route_scan_kernel");
+  if (units > 0 && (perm || inv)) {
+    route_scatter_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
+    MOE_CHECK_LAUNCH("route_scatter_kernel");
+  }
   return MOE_OK;
 }
