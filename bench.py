@@ -100,10 +100,16 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------- inputs
+BALANCED = False   # --balanced: N(0,1) logits (uniform expert load) instead of the Zipf law; a diagnostic, not the metric
+
+
 def make_inputs(cfg, seed=0):
     """x bf16 [T,H] ~ N(0,1) and fp32 router logits [T,E] (Zipf(1.1) popularity + Gumbel noise),
     both drawn on the CPU from `seed` (so that the CPU baseline sees the same batch)."""
     from tilelang_moe_b200 import inputs
+    if BALANCED:
+        g = torch.Generator().manual_seed(seed)
+        return inputs.activations(cfg["T"], cfg["H"], seed), torch.randn(cfg["T"], cfg["E"], generator=g)
     return inputs.activations(cfg["T"], cfg["H"], seed), inputs.zipf_logits(cfg["T"], cfg["E"], 1.1, seed=seed)
 
 
@@ -331,7 +337,7 @@ def run_ours(args, cfg):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {cfg['desc']}", "T": T, "H": H, "I": I, "E": E, "k": k,
+        "config": {"workload": f"{args.workload}: {cfg['desc']}" + (" [diagnostic: balanced load]" if BALANCED else ""), "T": T, "H": H, "I": I, "E": E, "k": k,
                    "parallelism": parallelism, "l2": "per-step inputs (weights) exceed L2 many times over; no flush",
                    "load_imbalance_max_over_mean": imbalance},
         "e2e": {"value": tokens_per_step * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
@@ -357,7 +363,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--balanced", action="store_true", help="diagnostic: uniform expert load instead of Zipf(1.1)")
     args = ap.parse_args()
+    global BALANCED
+    BALANCED = args.balanced
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, cfg)

@@ -94,3 +94,33 @@ def test_epilogues(cuda, lib):
     f32 = ops.grouped_gemm_sorted(ops.GEMM_PLAIN_F32, xs.to(cuda), Wg.to(cuda), offs.to(cuda))
     torch.testing.assert_close(f32.cpu(), O.grouped_gemm(xs, Wg, eid), rtol=1e-4, atol=1e-4)
     ops.check_status(cuda)
+
+
+@pytest.mark.parametrize("tile_rows", ["128", "256", "pair"])
+def test_both_tile_shapes_on_ragged_groups(cuda, lib, tile_rows, monkeypatch):
+    """128-row tiles, 256-row tiles (two MMAs sharing one B tile) and CTA-pair tiles (cta_group::2) on the same ragged problem: experts with
+    0, 1, 127, 128, 129, 255, 256, 257, 300 and 1000 rows exercise every tail case of both shapes."""
+    monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)
+    g = torch.Generator().manual_seed(8)
+    sizes = [0, 1, 127, 128, 129, 255, 256, 257, 300, 1000, 0, 513]
+    E, H, I = len(sizes), 256, 256
+    idx = torch.cat([torch.full((n,), e, dtype=torch.int64) for e, n in enumerate(sizes)])
+    idx = idx[torch.randperm(idx.numel(), generator=g)]
+    T = idx.numel()
+    x = torch.randn(T, H, generator=g).bfloat16()
+    Wg = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16()
+    Wu = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16()
+    Wd = (torch.randn(E, H, I, generator=g) * 0.06).bfloat16()
+    _close(kernels.grouped_gemm(x.to(cuda), Wg.to(cuda), idx.to(cuda)), O.grouped_gemm(x, Wg, idx))
+    _, offs, perm, _ = O.route_histogram(idx, E)
+    xs = x[perm.long()]
+    eid = idx[perm.long()]
+    act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, xs.to(cuda), Wg.to(cuda), offs.to(cuda), B2=Wu.to(cuda))
+    _close(act, torch.nn.functional.silu(O.grouped_gemm(xs, Wg, eid)) * O.grouped_gemm(xs, Wu, eid))
+    w = torch.rand(T, generator=g)
+    yk = ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, act, Wd.to(cuda), offs.to(cuda), dst_rows=perm.to(cuda),
+                                 row_w=w.to(cuda))
+    ref = torch.empty(T, H)
+    ref[perm.long()] = O.grouped_gemm(act.cpu(), Wd, eid) * w[:, None]
+    _close(yk, ref)
+    ops.check_status(cuda)

@@ -8,8 +8,14 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) four times per
 //               k-block; tcgen05.commit releases the stage and, after the last k-block, publishes
 //               the accumulator.  Also owns the TMEM allocation;
-//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (two TMEM buffers, so the next tile's
-//               main loop overlaps), apply the fused epilogue, store 16-byte vectors with row masks.
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator, apply the fused epilogue, store 16-byte
+//               vectors with row masks.
+//
+// Two tile shapes.  MT=1: 128 rows x BN columns, accumulator double-buffered in TMEM so that the next
+// tile's main loop overlaps the epilogue.  MT=2: 256 rows x 256 columns as two M=128 MMAs per K step
+// that share one B tile in shared memory - a third less operand traffic into the SM per flop, which is
+// what limits the MT=1 shape (all 512 TMEM columns hold one tile, so the epilogue is not overlapped).
+// A tile whose expert has no more than 128 rows left issues only the first of the two MMAs.
 //
 // Tiles are enumerated on the device from the expert offsets (no host sync): expert-major, then
 // N tile, then M tile, so that CTAs running side by side share one B tile through L2.
@@ -23,6 +29,7 @@
 
 #include <cuda.h>
 #include <mutex>
+#include <stdlib.h>
 
 namespace moe {
 namespace gemm {
@@ -35,13 +42,15 @@ constexpr int MAX_E = 1024;
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per barrier wait
 constexpr uint64_t DRAIN_LIMIT_NS = 20ull * 1000ull * 1000ull;    // 20 ms when draining after a failure
 
-template <int BN>
+template <int MT, int BN>
 struct Cfg {
-  static constexpr int STAGES = BN == 256 ? 4 : 6;
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_HALF_BYTES = BM * BK * 2;         // one 128-row A tile
+  static constexpr int A_BYTES = MT * A_HALF_BYTES;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TMEM_COLS = 2 * BN;   // 256 or 512: both powers of two >= 32
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;  // 6, 4 or 3
+  static constexpr int ACC_BUFS = (MT * BN * 2 <= 512) ? 2 : 1;
+  static constexpr int TMEM_COLS = ACC_BUFS * MT * BN;       // 256 or 512: powers of two >= 32
   // layout: [stages][barriers 256 B][tile tables]
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
@@ -141,6 +150,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// Pull a box into L2 only (no shared-memory destination, no barrier): runs ahead of the operand ring so
+// that the ring's own loads find their data in L2 instead of waiting on HBM.
+__device__ __forceinline__ void tma_prefetch_2d(const void* tmap, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(tmap), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_3d(const void* tmap, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -206,7 +224,8 @@ struct Tile {
   int e, row0, row_end, n_tile;
 };
 // tstart[e] = number of M tiles of experts < e.  Tile ids: expert-major, then N tile, then M tile.
-__device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const int32_t* offs, int E, int NT) {
+__device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const int32_t* offs, int E, int NT,
+                                            int tile_rows) {
   int lo = 0, hi = E - 1;
   while (lo < hi) {
     const int mid = (lo + hi) >> 1;
@@ -218,7 +237,7 @@ __device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const
   const int mt = tstart[lo + 1] - tstart[lo];
   t.n_tile = local / mt;
   const int m_local = local - t.n_tile * mt;
-  t.row0 = offs[lo] + m_local * BM;
+  t.row0 = offs[lo] + m_local * tile_rows;
   t.row_end = offs[lo + 1];
   return t;
 }
@@ -230,12 +249,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 
 // ------------------------------------------------------------------------------ kernel
-template <int BN, int EPI>
+template <int MT, int BN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmB2, const Params p) {
-  using C = Cfg<BN>;
+  using C = Cfg<MT, BN>;
   constexpr int STAGES = C::STAGES;
+  constexpr int ACC_BUFS = C::ACC_BUFS;
+  constexpr int TILE_ROWS = MT * BM;
   constexpr int OUT_COLS = EPI == MOE_GEMM_SILU_GATE ? BN / 2 : BN;   // output columns per tile
   extern __shared__ unsigned char smem_dyn[];
   // the swizzle pattern needs 1024-byte aligned stage buffers
@@ -274,7 +295,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int per = (E + 31) / 32;
     const int e_lo = lane * per, e_hi = min(E, e_lo + per);
     int sum = 0;
-    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + BM - 1) / BM;
+    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS;
     int inc = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -282,7 +303,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (lane >= o) inc += v;
     }
     int run = inc - sum;
-    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + BM - 1) / BM; }
+    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS; }
     if (lane == 31) tstart[E] = inc;
   }
   tc_fence_before();
@@ -298,7 +319,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t issued = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT);
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
       const int n0 = t.n_tile * OUT_COLS;
       for (int kb = 0; kb < NKB; ++kb) {
         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
@@ -335,9 +356,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      const bool second_half = MT == 2 && (t.row_end - t.row0) > BM;   // rows beyond the first 128 exist
       if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+      const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MT * BN);
       for (int kb = 0; kb < NKB; ++kb) {
         if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 3)) { ok = false; break; }
         tc_fence_after();
@@ -349,6 +372,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (addr >> 4) field
             umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            if (second_half)   // rows 128..255 of the tile: next A half (16 KB further), same B, next accumulator
+              umma_bf16(d_tmem + BN, adesc + (uint64_t)(C::A_HALF_BYTES >> 4) + (uint64_t)(2 * k),
+                        bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty0 + 8 * stage);
         }
@@ -358,7 +384,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!ok) break;
       if (lane == 0) umma_commit(tfull0 + 8 * acc);
       __syncwarp();
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
     }
     if (!ok) {
       // wait (bounded) until the tensor-core work issued so far has retired, so TMEM can be freed
@@ -373,10 +399,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT);
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
       tc_fence_after();
-      const int grow = t.row0 + q * 32 + lane;   // sorted row handled by this thread
+#pragma unroll 1
+      for (int half = 0; half < MT; ++half) {
+      if (half == 1 && t.row0 + BM >= t.row_end) break;   // nothing was accumulated for rows 128..255
+      const int grow = t.row0 + half * BM + q * 32 + lane;   // sorted row handled by this thread
       const bool row_ok = grow < t.row_end;
       const int n0 = t.n_tile * OUT_COLS;
       int64_t out_row = grow;
@@ -385,7 +414,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
         if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[grow];
       }
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * MT * BN + half * BN);
 #pragma unroll 1
       for (int c = 0; c < OUT_COLS / 32; ++c) {
         uint32_t v[32];
@@ -427,10 +456,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       }
+      }  // halves
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
     }
   }
 
@@ -440,6 +470,313 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------------------------------ CTA-pair kernel
+// The same pipeline on a cluster of two CTAs driving tcgen05 in cta_group::2 mode: one MMA covers a
+// 256-row x 256-column tile, 128 rows per CTA.  Each CTA stages only its own 128 rows of A and its own
+// half of the B tile (128 of the 256 N rows; for the SiLU-gate epilogue CTA 0 holds the gate rows and
+// CTA 1 the up rows), 32 KB per k-block instead of 48 KB.  Operand staging and operand reads share the
+// SM's shared-memory bandwidth, which is what caps the single-CTA shape; halving the B traffic lifts it.
+//
+//   full[s]    lives in CTA 0: its producer posts the byte count of both CTAs, both CTAs' TMA loads
+//              complete on it (cta_group::2 loads may signal the peer's barrier);
+//   empty[s]   one per CTA, released by the leader's tcgen05.commit (one commit per CTA's barrier);
+//   tfull[b]   one per CTA, same way; tempty[b] lives in CTA 0 and collects the epilogue warps of both.
+// No multicast load anywhere: every CTA fetches its own boxes.
+struct PairCfg {
+  static constexpr int BN = 256;
+  static constexpr int A_BYTES = BM * BK * 2;            // 16 KB: this CTA's 128 rows
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;      // 16 KB: this CTA's half of the N rows
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
+  static constexpr int SMEM_BYTES = TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, uint32_t bar_cluster, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// arrive on a barrier (shared::cluster address, either CTA's) once the pair's MMAs issued so far retire
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_pair(int n) {   // M = 256 across the pair
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmB2, const Params p) {
+  using C = PairCfg;
+  constexpr int STAGES = C::STAGES;
+  constexpr int BN = C::BN;
+  constexpr int TILE_ROWS = 2 * BM;
+  constexpr int OUT_COLS = EPI == MOE_GEMM_SILU_GATE ? BN / 2 : BN;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFFSET + 200);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
+  int32_t* tstart = reinterpret_cast<int32_t*>(smem + C::TABLE_OFFSET);
+  int32_t* offs = tstart + (MAX_E + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+  const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
+  const uint32_t lead_full0 = map_to_cta(full0, 0), lead_tempty0 = map_to_cta(tempty0, 0);
+  const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    if (EPI == MOE_GEMM_SILU_GATE) prefetch_tmap(&tmB2);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets[e];
+  __syncthreads();
+  if (warp == 2) {
+    const int per = (E + 31) / 32;
+    const int e_lo = lane * per, e_hi = min(E, e_lo + per);
+    int sum = 0;
+    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS;
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    int run = inc - sum;
+    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS; }
+    if (lane == 31) tstart[E] = inc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_barrier();   // both CTAs' barriers are initialised before anything remote touches them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = tstart[E] * NT;
+
+  if (warp == 0) {
+    // ===================================================================== TMA producer (both CTAs)
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t issued = 0;
+    bool ok = true;
+    for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      const int n0 = t.n_tile * OUT_COLS;
+      for (int kb = 0; kb < NKB; ++kb) {
+        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
+        if (lane == 0) {
+          const uint32_t lead_full = lead_full0 + 8 * stage;
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+          if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, 2 * C::STAGE_BYTES);
+          tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, t.row0 + (int)rank * BM);
+          if (EPI == MOE_GEMM_SILU_GATE)   // CTA 0 stages the gate rows, CTA 1 the up rows of the same columns
+            tma_load_3d_pair(sb, leader ? &tmB : &tmB2, lead_full, kb * BK, n0, t.e);
+          else
+            tma_load_3d_pair(sb, &tmB, lead_full, kb * BK, n0 + (int)rank * (BN / 2), t.e);
+        }
+        __syncwarp();
+        ++issued;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (ok) {
+      // tail: the leader's tcgen05.commit arrives on this CTA's empty barriers from the other SM; let the
+      // last of those arrivals land before this CTA may retire (bounded like every other wait)
+      const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+      for (uint32_t j = first; j < issued && ok; ++j)
+        ok = mbar_wait(empty0 + 8 * (j % STAGES), (j / STAGES) & 1, abort_flag, p.status, 15);
+    }
+    if (!ok && leader) {
+      // the leader's full barriers count the copies of both CTAs: wait (bounded) for the outstanding ones
+      const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+      for (uint32_t j = first; j < issued; ++j)
+        mbar_wait_drain(full0 + 8 * (j % STAGES), (j / STAGES) & 1, DRAIN_LIMIT_NS);
+    }
+  } else if (warp == 1) {
+    // ===================================================================== MMA issuer (leader CTA only)
+    if (leader) {
+      constexpr uint32_t idesc = make_idesc_pair(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
+        if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < NKB; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 13)) { ok = false; break; }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+            const uint64_t adesc = make_smem_desc(sa);
+            const uint64_t bdesc = make_smem_desc(sa + C::A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit_pair(empty0 + 8 * stage);                  // this CTA's stage
+            umma_commit_pair(map_to_cta(empty0 + 8 * stage, 1));   // the peer's stage
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (lane == 0) {
+          umma_commit_pair(tfull0 + 8 * acc);
+          umma_commit_pair(map_to_cta(tfull0 + 8 * acc, 1));
+        }
+        __syncwarp();
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) {
+        if (lane == 0) umma_commit_pair(drain_bar);
+        __syncwarp();
+        mbar_wait_drain(drain_bar, 0, DRAIN_LIMIT_NS);
+      }
+    }
+  } else {
+    // ===================================================================== epilogue (both CTAs)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
+      tc_fence_after();
+      const int grow = t.row0 + (int)rank * BM + q * 32 + lane;
+      const bool row_ok = grow < t.row_end;
+      const int n0 = t.n_tile * OUT_COLS;
+      int64_t out_row = grow;
+      float w = 1.0f;
+      if (row_ok) {
+        if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
+        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[grow];
+      }
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      const bool any_rows = t.row0 + (int)rank * BM < t.row_end;   // warp-uniform: this CTA's half holds rows
+#pragma unroll 1
+      for (int c = 0; any_rows && c < OUT_COLS / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(taddr + c * 32, v);
+        if (EPI == MOE_GEMM_SILU_GATE) {
+          uint32_t u[32];
+          tmem_ld32(taddr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+        } else {
+          tmem_ld_wait();
+          if (EPI == MOE_GEMM_SCALE_SCATTER) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * w);
+          }
+        }
+        const int col = n0 + c * 32;
+        if (row_ok && col < p.N) {
+          if (EPI == MOE_GEMM_PLAIN_F32) {
+            float* dst = reinterpret_cast<float*>(p.Y) + out_row * p.ldy + col;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (col + j * 4 < p.N)
+                *reinterpret_cast<uint4*>(dst + j * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.Y) + out_row * p.ldy + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + j * 8 < p.N) {
+                uint4 o;
+                o.x = pack_bf16(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+                o.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+                o.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+                o.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                *reinterpret_cast<uint4*>(dst + j * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---- teardown: neither CTA may retire its shared memory or TMEM while the other still uses them
+  tc_fence_before();
+  __syncthreads();
+  cluster_barrier();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -478,17 +815,31 @@ static int make_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1,
   return MOE_OK;
 }
 
-template <int BN, int EPI>
+template <int MT, int BN, int EPI>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
                   cudaStream_t st) {
-  using C = Cfg<BN>;
+  using C = Cfg<MT, BN>;
   static bool attr_set = false;   // per instantiation; the attribute is idempotent
   if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<MT, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
-  grouped_gemm_kernel<BN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tA, tB, tB2, p);
+  grouped_gemm_kernel<MT, BN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tA, tB, tB2, p);
   MOE_CHECK_LAUNCH("grouped_gemm_kernel");
+  return MOE_OK;
+}
+
+template <int EPI>
+static int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
+                       cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        PairCfg::SMEM_BYTES));
+    attr_set = true;
+  }
+  grouped_gemm_pair_kernel<EPI><<<grid, NUM_THREADS, PairCfg::SMEM_BYTES, st>>>(tA, tB, tB2, p);
+  MOE_CHECK_LAUNCH("grouped_gemm_pair_kernel");
   return MOE_OK;
 }
 
@@ -518,15 +869,25 @@ extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, cons
   int rc = current_device_info(&dev);
   if (rc) return rc;
 
-  // tile width: 256 accumulator columns when that still fills the machine, else 128
-  const int64_t m_tiles_bound = max_rows / BM + E;
-  int BN;
-  if (epilogue == MOE_GEMM_SILU_GATE) {
-    BN = 256;  // 128 gate + 128 up columns
-  } else {
-    BN = (N % 256 == 0 && m_tiles_bound * (N / 256) >= dev.sm_count) ? 256 : 128;
+  // Tile shape: a fixed rule on the problem size.  Ragged groups pay for row padding at the tile height, so
+  // the 128-row tile is the default; the CTA-pair kernel (256 rows over two SMs, half the B staging per SM)
+  // takes over when groups are large (>= 512 rows on average) and there are enough pair tiles for every SM.
+  // The single-CTA 256-row shape is kept for measurement (override below).
+  const bool gate = epilogue == MOE_GEMM_SILU_GATE;
+  const int n_tiles_256 = gate ? (N + 127) / 128 : (N + 255) / 256;
+  const int64_t m_tiles_128 = max_rows / BM + E, m_tiles_256 = max_rows / (2 * BM) + E;
+  int MT = 1, BN = 128;
+  if (gate || (N % 256 == 0 && m_tiles_128 * n_tiles_256 >= dev.sm_count)) BN = 256;
+  bool pair = (gate || N % 256 == 0) && max_rows / E >= 512 &&
+              (max_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
+  if (pair) { MT = 2; BN = 256; }
+  if (const char* force = getenv("MOE_B200_GEMM_TILE_ROWS")) {   // test / measurement override: "128", "256", "pair"
+    if (force[0] == 'p' && (gate || N % 256 == 0)) { MT = 2; BN = 256; pair = true; }
+    else if (atoi(force) == 256 && (gate || N % 256 == 0)) { MT = 2; BN = 256; }
+    else if (atoi(force) == 128) { MT = 1; pair = false; if (gate) BN = 256; }
   }
-  const int out_cols = epilogue == MOE_GEMM_SILU_GATE ? BN / 2 : BN;
+  const int64_t m_tiles_bound = MT == 2 ? m_tiles_256 : m_tiles_128;
+  const int out_cols = gate ? BN / 2 : BN;
 
   Params p;
   p.offsets = offsets; p.dst_rows = dst_rows; p.row_w = row_w; p.Y = Y; p.ldy = ldy;
@@ -536,29 +897,41 @@ extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, cons
   p.status = status;
 
   CUtensorMap tA, tB, tB2;
-  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)max_rows, 0, BM);
+  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)max_rows, 0, (uint32_t)(pair ? BM : MT * BM));
   if (rc) return rc;
-  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, (uint32_t)out_cols);
+  const uint32_t b_box_rows = pair ? 128u : (uint32_t)out_cols;   // a CTA of a pair stages 128 N rows
+  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows);
   if (rc) return rc;
   tB2 = tB;
   if (epilogue == MOE_GEMM_SILU_GATE) {
-    rc = make_tmap(&tB2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, (uint32_t)out_cols);
+    rc = make_tmap(&tB2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows);
     if (rc) return rc;
   }
   int64_t tiles_bound = m_tiles_bound * p.num_n_tiles;
   int grid = (int)(tiles_bound < dev.sm_count ? tiles_bound : dev.sm_count);
   if (grid < 1) grid = 1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  switch (epilogue) {
-    case MOE_GEMM_PLAIN:
-      return BN == 256 ? launch<256, MOE_GEMM_PLAIN>(tA, tB, tB2, p, grid, st) : launch<128, MOE_GEMM_PLAIN>(tA, tB, tB2, p, grid, st);
-    case MOE_GEMM_SILU_GATE:
-      return launch<256, MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, grid, st);
-    case MOE_GEMM_SCALE_SCATTER:
-      return BN == 256 ? launch<256, MOE_GEMM_SCALE_SCATTER>(tA, tB, tB2, p, grid, st)
-                       : launch<128, MOE_GEMM_SCALE_SCATTER>(tA, tB, tB2, p, grid, st);
-    default:
-      return BN == 256 ? launch<256, MOE_GEMM_PLAIN_F32>(tA, tB, tB2, p, grid, st)
-                       : launch<128, MOE_GEMM_PLAIN_F32>(tA, tB, tB2, p, grid, st);
+  if (pair) {
+    int pgrid = (int)(2 * tiles_bound < dev.sm_count ? 2 * tiles_bound : dev.sm_count) & ~1;
+    if (pgrid < 2) pgrid = 2;
+    switch (epilogue) {
+      case MOE_GEMM_PLAIN: return launch_pair<MOE_GEMM_PLAIN>(tA, tB, tB2, p, pgrid, st);
+      case MOE_GEMM_SCALE_SCATTER: return launch_pair<MOE_GEMM_SCALE_SCATTER>(tA, tB, tB2, p, pgrid, st);
+      case MOE_GEMM_PLAIN_F32: return launch_pair<MOE_GEMM_PLAIN_F32>(tA, tB, tB2, p, pgrid, st);
+      default: return launch_pair<MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, pgrid, st);
+    }
   }
+#define MOE_GEMM_CASE(EPI_)                                                                  \
+  if (MT == 2) return launch<2, 256, EPI_>(tA, tB, tB2, p, grid, st);                          \
+  if (BN == 256) return launch<1, 256, EPI_>(tA, tB, tB2, p, grid, st);                        \
+  return launch<1, 128, EPI_>(tA, tB, tB2, p, grid, st)
+  switch (epilogue) {
+    case MOE_GEMM_PLAIN: MOE_GEMM_CASE(MOE_GEMM_PLAIN);
+    case MOE_GEMM_SCALE_SCATTER: MOE_GEMM_CASE(MOE_GEMM_SCALE_SCATTER);
+    case MOE_GEMM_PLAIN_F32: MOE_GEMM_CASE(MOE_GEMM_PLAIN_F32);
+    default:
+      if (MT == 2) return launch<2, 256, MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, grid, st);
+      return launch<1, 256, MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, grid, st);
+  }
+#undef MOE_GEMM_CASE
 }
