@@ -96,7 +96,7 @@ def test_epilogues(cuda, lib):
     ops.check_status(cuda)
 
 
-@pytest.mark.parametrize("tile_rows", ["128", "256", "pair"])
+@pytest.mark.parametrize("tile_rows", ["128", "256", "pair", "tn128", "tn256"])
 def test_both_tile_shapes_on_ragged_groups(cuda, lib, tile_rows, monkeypatch):
     """128-row tiles, 256-row tiles (two MMAs sharing one B tile) and CTA-pair tiles (cta_group::2) on the same ragged problem: experts with
     0, 1, 127, 128, 129, 255, 256, 257, 300 and 1000 rows exercise every tail case of both shapes."""

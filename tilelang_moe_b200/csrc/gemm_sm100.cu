@@ -780,6 +780,245 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   }
 }
 
+
+// ------------------------------------------------------------------------------ tokens-as-N kernel
+// Ragged groups waste tensor-core time when rows are padded to the 128-row M of the instruction: with a
+// Zipf expert load most experts own far fewer than 128 rows.  This kernel swaps the operands: the
+// weight tile is the M side (always 128 full rows of W[e]) and the expert's tokens are the N side, whose
+// extent may be any multiple of 16 up to TN, so padding costs at most 15 rows per group.
+//
+//   D[feature, token] (+)= W[e][feature, k] * X[token, k]^T        (both operands K-major, as stored)
+//
+// A tile = (expert, feature tile, chunk of <= TN tokens) and carries two weight tiles that share the
+// token tile: gate and up rows of the same 128 features (SiLU-gate epilogue), or features f0..f0+127 and
+// f0+128..f0+255 (plain / scale-scatter).  Accumulators are feature-major in TMEM (lane = feature,
+// column = token); the epilogue walks the token columns and stores 2-byte elements, 32 lanes covering 64
+// contiguous bytes of one output row.  TN=128 keeps two accumulator sets (epilogue overlaps the next
+// main loop), TN=256 one.
+template <int TN>
+struct TnCfg {
+  static constexpr int W_BYTES = BM * BK * 2;                 // one 128-feature weight tile, 16 KB
+  static constexpr int X_BYTES = TN * BK * 2;                 // token tile
+  static constexpr int STAGE_BYTES = 2 * W_BYTES + X_BYTES;
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;   // 4 (TN=128) or 3 (TN=256)
+  static constexpr int ACC_BUFS = TN == 128 ? 2 : 1;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
+  static constexpr int SMEM_BYTES = TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 1024;
+};
+__host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int TN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
+                       const __grid_constant__ CUtensorMap tmX, const Params p) {
+  using C = TnCfg<TN>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int ACC_BUFS = C::ACC_BUFS;
+  constexpr bool GATE = EPI == MOE_GEMM_SILU_GATE;
+  constexpr int FEAT_PER_TILE = GATE ? BM : 2 * BM;     // output features per tile
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFFSET + 200);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
+  int32_t* tstart = reinterpret_cast<int32_t*>(smem + C::TABLE_OFFSET);
+  int32_t* offs = tstart + (MAX_E + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+  const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
+  const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmW);
+    prefetch_tmap(&tmX);
+    if (GATE) prefetch_tmap(&tmW2);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets[e];
+  __syncthreads();
+  if (warp == 2) {  // prefix of token chunks per expert
+    const int per = (E + 31) / 32;
+    const int e_lo = lane * per, e_hi = min(E, e_lo + per);
+    int sum = 0;
+    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + TN - 1) / TN;
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    int run = inc - sum;
+    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + TN - 1) / TN; }
+    if (lane == 31) tstart[E] = inc;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = tstart[E] * NT;
+
+  if (warp == 0) {
+    // ===================================================================== TMA producer
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TN);
+      const int f0 = t.n_tile * FEAT_PER_TILE;
+      const bool have2 = GATE || (f0 + BM < p.N);
+      int cnt = t.row_end - t.row0;
+      if (cnt > TN) cnt = TN;
+      const int nbox = (cnt + 63) >> 6;                       // 64-token boxes actually needed
+      const uint32_t tx = (uint32_t)(C::W_BYTES * (have2 ? 2 : 1) + nbox * 64 * BK * 2);
+      for (int kb = 0; kb < NKB; ++kb) {
+        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
+        if (lane == 0) {
+          const uint32_t full = full0 + 8 * stage;
+          const uint32_t sw = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sx = sw + 2 * C::W_BYTES;
+          mbar_arrive_expect_tx(full, tx);
+          tma_load_3d(sw, &tmW, full, kb * BK, f0, t.e);
+          if (GATE) tma_load_3d(sw + C::W_BYTES, &tmW2, full, kb * BK, f0, t.e);
+          else if (have2) tma_load_3d(sw + C::W_BYTES, &tmW, full, kb * BK, f0 + BM, t.e);
+          for (int j = 0; j < nbox; ++j) tma_load_2d(sx + j * (64 * BK * 2), &tmX, full, kb * BK, t.row0 + 64 * j);
+        }
+        __syncwarp();
+        ++issued;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (!ok) {
+      const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
+      for (uint32_t j = first; j < issued; ++j)
+        mbar_wait_drain(full0 + 8 * (j % STAGES), (j / STAGES) & 1, DRAIN_LIMIT_NS);
+    }
+  } else if (warp == 1) {
+    // ===================================================================== MMA issuer
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TN);
+      const bool have2 = GATE || (t.n_tile * FEAT_PER_TILE + BM < p.N);
+      int cnt = t.row_end - t.row0;
+      if (cnt > TN) cnt = TN;
+      const int n16 = (cnt + 15) & ~15;                        // instruction N: tokens rounded up to 16
+      const uint32_t idesc = make_idesc_mn(BM, n16);
+      if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d0 = tmem_base + (uint32_t)(acc * 2 * TN);
+      for (int kb = 0; kb < NKB; ++kb) {
+        if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 23)) { ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sw = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint64_t w0 = make_smem_desc(sw), w1 = make_smem_desc(sw + C::W_BYTES);
+          const uint64_t xd = make_smem_desc(sw + 2 * C::W_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            umma_bf16(d0, w0 + (uint64_t)(2 * k), xd + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            if (have2) umma_bf16(d0 + TN, w1 + (uint64_t)(2 * k), xd + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * stage);
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (!ok) break;
+      if (lane == 0) umma_commit(tfull0 + 8 * acc);
+      __syncwarp();
+      if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok) {
+      if (lane == 0) umma_commit(drain_bar);
+      __syncwarp();
+      mbar_wait_drain(drain_bar, 0, DRAIN_LIMIT_NS);
+    }
+  } else {
+    // ===================================================================== epilogue (warps 2..5)
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const Tile t = decode_tile(tile, tstart, offs, E, NT, TN);
+      const int f0 = t.n_tile * FEAT_PER_TILE;
+      const bool have2 = GATE || (f0 + BM < p.N);
+      int cnt = t.row_end - t.row0;
+      if (cnt > TN) cnt = TN;
+      if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 24)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * TN);
+      const int n_pass = (GATE || !have2) ? 1 : 2;            // plain: second pass handles features f0+128..
+#pragma unroll 1
+      for (int pass = 0; pass < n_pass; ++pass) {
+        const int feat = f0 + pass * BM + q * 32 + lane;       // output column of this thread
+        const bool feat_ok = feat < p.N;
+#pragma unroll 1
+        for (int c = 0; c * 32 < cnt; ++c) {
+          uint32_t v[32];
+          tmem_ld32(t0 + pass * TN + c * 32, v);
+          if (GATE) {
+            uint32_t u[32];
+            tmem_ld32(t0 + TN + c * 32, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+          } else {
+            tmem_ld_wait();
+          }
+          // per-token metadata: lane j holds the output row (and weight) of token column j of this chunk
+          const int tok = t.row0 + c * 32 + lane;
+          int my_dst = -1;
+          float my_w = 1.0f;
+          if (tok < t.row0 + cnt) {
+            my_dst = (!GATE && p.dst_rows) ? p.dst_rows[tok] : tok;
+            if (EPI == MOE_GEMM_SCALE_SCATTER) my_w = p.row_w[tok];
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
+            float val = __uint_as_float(v[j]);
+            if (EPI == MOE_GEMM_SCALE_SCATTER) val *= __shfl_sync(0xFFFFFFFFu, my_w, j);
+            if (d >= 0 && feat_ok) {
+              if (EPI == MOE_GEMM_PLAIN_F32) reinterpret_cast<float*>(p.Y)[(int64_t)d * p.ldy + feat] = val;
+              else reinterpret_cast<__nv_bfloat16*>(p.Y)[(int64_t)d * p.ldy + feat] = __float2bfloat16_rn(val);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -843,6 +1082,21 @@ static int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   return MOE_OK;
 }
 
+template <int TN, int EPI>
+static int launch_tn(const CUtensorMap& tW, const CUtensorMap& tW2, const CUtensorMap& tX, const Params& p, int grid,
+                     cudaStream_t st) {
+  using C = TnCfg<TN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_tn_kernel<TN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        C::SMEM_BYTES));
+    attr_set = true;
+  }
+  grouped_gemm_tn_kernel<TN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tW, tW2, tX, p);
+  MOE_CHECK_LAUNCH("grouped_gemm_tn_kernel");
+  return MOE_OK;
+}
+
 }  // namespace gemm
 }  // namespace moe
 
@@ -881,10 +1135,48 @@ extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, cons
   bool pair = (gate || N % 256 == 0) && max_rows / E >= 512 &&
               (max_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
   if (pair) { MT = 2; BN = 256; }
-  if (const char* force = getenv("MOE_B200_GEMM_TILE_ROWS")) {   // test / measurement override: "128", "256", "pair"
+  // The tokens-as-N kernel is selected only by the override: measured on B200 it matches the rows-as-M
+  // kernel when groups are small (both stream weights at HBM speed) and loses when they are large
+  // (2-byte epilogue stores, more shared-memory reads per flop), so the default stays rows-as-M.
+  int tn = 0;
+  if (const char* force = getenv("MOE_B200_GEMM_TILE_ROWS")) {   // test / measurement override: "128", "256", "pair", "tn128", "tn256"
+    if (force[0] == 't') { tn = atoi(force + 2) == 128 ? 128 : 256; pair = false; }
+    else tn = 0;
     if (force[0] == 'p' && (gate || N % 256 == 0)) { MT = 2; BN = 256; pair = true; }
     else if (atoi(force) == 256 && (gate || N % 256 == 0)) { MT = 2; BN = 256; }
     else if (atoi(force) == 128) { MT = 1; pair = false; if (gate) BN = 256; }
+  }
+  if (tn) {
+    Params q;
+    q.offsets = offsets; q.dst_rows = dst_rows; q.row_w = row_w; q.Y = Y; q.ldy = ldy;
+    q.K = K; q.N = N; q.E = E;
+    q.num_n_tiles = gate ? (N + BM - 1) / BM : (N + 2 * BM - 1) / (2 * BM);
+    q.num_k_blocks = (K + BK - 1) / BK;
+    q.status = status;
+    CUtensorMap tW, tW2, tX;
+    rc = make_tmap(&tW, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM);
+    if (rc) return rc;
+    tW2 = tW;
+    if (gate) {
+      rc = make_tmap(&tW2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM);
+      if (rc) return rc;
+    }
+    rc = make_tmap(&tX, A, (uint64_t)K, (uint64_t)max_rows, 0, 64);
+    if (rc) return rc;
+    const int64_t tiles = (max_rows / tn + E) * q.num_n_tiles;
+    int g = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
+    if (g < 1) g = 1;
+    cudaStream_t st2 = reinterpret_cast<cudaStream_t>(stream);
+#define MOE_TN_CASE(EPI_)                                                        \
+    if (tn == 128) return launch_tn<128, EPI_>(tW, tW2, tX, q, g, st2);            \
+    return launch_tn<256, EPI_>(tW, tW2, tX, q, g, st2)
+    switch (epilogue) {
+      case MOE_GEMM_PLAIN: MOE_TN_CASE(MOE_GEMM_PLAIN);
+      case MOE_GEMM_SCALE_SCATTER: MOE_TN_CASE(MOE_GEMM_SCALE_SCATTER);
+      case MOE_GEMM_PLAIN_F32: MOE_TN_CASE(MOE_GEMM_PLAIN_F32);
+      default: MOE_TN_CASE(MOE_GEMM_SILU_GATE);
+    }
+#undef MOE_TN_CASE
   }
   const int64_t m_tiles_bound = MT == 2 ? m_tiles_256 : m_tiles_128;
   const int out_cols = gate ? BN / 2 : BN;
