@@ -254,10 +254,12 @@ def run_ours(args, cfg):
         parallelism = "1 GPU, 256 experts resident"
         imbalance = None
     else:
-        runner = ep.EPRunner(cfg, rank, world, dev, make_weights)
+        runner = ep.EPRunner(cfg, rank, world, dev, make_weights, exchange=args.exchange)
         step, step_e2e, launches_per_step, h2d, d2h = runner.bench_closures(x_cpu, logits_cpu)
         tokens_per_step = T
-        parallelism = f"ep{world}: {E // world} experts per GPU, tokens split {T // world} per rank, NCCL all-to-all"
+        how = ("dispatch kernel + down-GEMM epilogue over NVLink peer memory" if args.exchange == "peer"
+               else "NCCL all-to-all")
+        parallelism = f"ep{world}: {E // world} experts per GPU, tokens split {T // world} per rank, {how}"
         imbalance = runner.imbalance
 
     def sync_all():
@@ -309,7 +311,8 @@ def run_ours(args, cfg):
 
     roofline = None
     if "up_gemm" in stage_ms:
-        rows = T * k if world == 1 else sum(tm.get("_n_recv", 0) for tm in stage_events) / max(len(stage_events), 1)
+        rows = T * k if world == 1 else (sum(tm.get("_n_recv", 0) for tm in stage_events) / max(len(stage_events), 1)
+                                         or T * k / world)
         flops = 2.0 * rows * H * (2 * I)
         achieved = flops / (stage_ms["up_gemm"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
@@ -427,6 +430,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--only", default="", help="router workload: comma-separated point names to run")
     ap.add_argument("--balanced", action="store_true", help="diagnostic: uniform expert load instead of Zipf(1.1)")
     args = ap.parse_args()

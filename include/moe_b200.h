@@ -164,6 +164,32 @@ int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, fl
 int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets,
                    int32_t* src_row, void* stream);
 
+/* ---- expert parallelism over peer memory ---------------------------------------------
+ * No counterpart in the reference.  cnt_all int32 [G][G*E_local]: cnt_all[s][v] = rows that
+ * source rank s routes to virtual expert v = dest_rank*E_local + slot (all-gather of the
+ * per-rank histograms taken with id_map).  moe_ep_plan derives this rank's tables:
+ *   offsets  int32 [E_local+1]  expert-major start of each local expert in the receive buffer
+ *   dst_base int32 [G*E_local]  start of this rank's rows for v inside the destination's buffer
+ *   ret_rank, ret_row int32 [rows received]: source rank and row in the source's return
+ *            buffer (its sorted order) for the row held at expert-major position q.
+ * moe_ep_dispatch copies the activation row of every routed entry (this rank's sorted order,
+ * perm / topk_idx / id_map / offsets from moe_route_histogram) into peer_recv[dest] at its
+ * expert-major row: plain stores to peer memory, no collective library.  peer_recv: host
+ * array of G device pointers (one receive buffer per rank, this rank's own included).
+ * moe_grouped_gemm_peer_scatter is moe_grouped_gemm(MOE_GEMM_PLAIN) whose epilogue stores row r
+ * into peer_base[row_rank[r]] at row dst_rows[r]: the combine exchange fused into the down GEMM.
+ * Callers order the phases across ranks (a barrier after dispatch and after the scatter).
+ */
+int moe_ep_plan(const int32_t* cnt_all, int G, int E_local, int my_rank, int32_t* offsets,
+                int32_t* dst_base, int32_t* ret_rank, int32_t* ret_row, void* stream);
+int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx,
+                    const int32_t* id_map, const int32_t* offsets, const int32_t* dst_base, int k,
+                    int E_local, int64_t n, int64_t H, void* const* peer_recv, int G, void* stream);
+int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
+                                  const int32_t* row_rank, const int32_t* dst_rows,
+                                  void* const* peer_base, int n_peers, int64_t ldy, int64_t max_rows,
+                                  int K, int N, int E, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

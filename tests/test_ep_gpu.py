@@ -19,7 +19,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, placement, q):
+def _worker(rank, world, port, placement, q, exchange="nccl"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     from oracle import moe_oracle as O
     from tilelang_moe_b200 import ep, inputs, ops
@@ -42,10 +42,11 @@ def _worker(rank, world, port, placement, q):
         Tl = T // world
         sl = slice(rank * Tl, (rank + 1) * Tl)
         bufs = {}
-        for _ in range(2):   # second pass reuses the grown buffers
-            out = ep.ep_forward(x[sl].to(dev), logits[sl].to(dev), k, plan,
-                                torch.tensor(plan.id_map, dtype=torch.int32, device=dev), Wg[mine].to(dev),
-                                Wu[mine].to(dev), Wd[mine].to(dev), ops, bufs=bufs)
+        px = ep.PeerExchange(Tl, k, H, world, dev) if exchange == "peer" else None
+        for _ in range(3):   # later passes reuse the buffers (and, for the peer exchange, overwrite them)
+            args = (x[sl].to(dev), logits[sl].to(dev), k, plan, torch.tensor(plan.id_map, dtype=torch.int32, device=dev),
+                    Wg[mine].to(dev), Wu[mine].to(dev), Wd[mine].to(dev), ops)
+            out = ep.ep_forward_peer(*args, px, bufs=bufs) if px is not None else ep.ep_forward(*args, bufs=bufs)
         ops.check_status(dev)
         ref = O.fusedmoe(x, None, None, None, None, Wg, Wu, Wd, k, logits=logits)[sl]
         ok = torch.isclose(out.float().cpu(), ref, rtol=1e-2, atol=2e-2).all().item()
@@ -56,15 +57,16 @@ def _worker(rank, world, port, placement, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("placement", ["contiguous", "balanced"])
-def test_ep_two_gpus_match_oracle(lib, placement):
+@pytest.mark.parametrize("placement,exchange", [("contiguous", "nccl"), ("balanced", "nccl"), ("contiguous", "peer"),
+                                                ("balanced", "peer")])
+def test_ep_two_gpus_match_oracle(lib, placement, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, placement, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, placement, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=240) for _ in range(world)]

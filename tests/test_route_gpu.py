@@ -76,3 +76,35 @@ def test_gather_and_combine(cuda, lib):
     for s in range(k):
         acc += yk.float().view(T, k, H)[:, s]
     assert torch.equal(out2.cpu(), acc.bfloat16())
+
+
+def test_ep_plan_tables(cuda, lib):
+    """The expert-parallel plan tables against a direct restatement of their definition."""
+    g = torch.Generator().manual_seed(3)
+    G, El = 4, 6
+    E = G * El
+    cnt = torch.randint(0, 40, (G, E), generator=g, dtype=torch.int32)
+    cnt[1, 7] = 0
+    cnt[:, 13] = 0
+    for me in range(G):
+        cap = int(cnt[:, me * El:(me + 1) * El].sum()) + 5
+        offs, dst_base, ret_rank, ret_row = ops.ep_plan(cnt.to(cuda), G, El, me, cap)
+        tot = cnt.sum(0).long()
+        # expert-major start of every virtual expert on its destination
+        dbase = torch.zeros(E, dtype=torch.long)
+        for d in range(G):
+            dbase[d * El:(d + 1) * El] = torch.cumsum(tot[d * El:(d + 1) * El], 0) - tot[d * El:(d + 1) * El]
+        want_offs = torch.cat([dbase[me * El:(me + 1) * El], tot[me * El:(me + 1) * El].sum().view(1)])
+        assert torch.equal(offs.cpu().long(), want_offs)
+        want_dst = dbase + cnt[:me].sum(0).long()
+        assert torch.equal(dst_base.cpu().long(), want_dst)
+        src_off = torch.cumsum(cnt.long(), 1) - cnt.long()           # each source's own sorted order
+        rr, rw = ret_rank.cpu(), ret_row.cpu()
+        for j in range(El):
+            v = me * El + j
+            q = int(dbase[v])
+            for s_ in range(G):
+                c = int(cnt[s_, v])
+                assert (rr[q:q + c] == s_).all()
+                assert torch.equal(rw[q:q + c].long(), int(src_off[s_, v]) + torch.arange(c))
+                q += c

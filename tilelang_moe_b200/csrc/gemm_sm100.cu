@@ -67,6 +67,10 @@ struct Params {
   int num_n_tiles;
   int num_k_blocks;
   int32_t* status;
+  // optional scatter of output rows into other GPUs' buffers (expert-parallel combine): row r goes to
+  // peer_base[row_rank[r]] at row dst_rows[r]; plain stores to peer memory from the epilogue
+  const int32_t* row_rank;
+  void* peer_base[16];
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -410,9 +414,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int n0 = t.n_tile * OUT_COLS;
       int64_t out_row = grow;
       float w = 1.0f;
+      void* ybase = p.Y;
       if (row_ok) {
         if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
         if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[grow];
+        if (EPI == MOE_GEMM_PLAIN && p.row_rank) ybase = p.peer_base[p.row_rank[grow]];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * MT * BN + half * BN);
 #pragma unroll 1
@@ -441,7 +447,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               if (col + j * 4 < p.N)
                 *reinterpret_cast<uint4*>(dst + j * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.Y) + out_row * p.ldy + col;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ybase) + out_row * p.ldy + col;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (col + j * 8 < p.N) {
@@ -1100,9 +1106,36 @@ static int launch_tn(const CUtensorMap& tW, const CUtensorMap& tW2, const CUtens
 }  // namespace gemm
 }  // namespace moe
 
+static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
+                             const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
+                             int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
+                             void* const* peer_base, int n_peers);
+
 extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                                 const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                                 int K, int N, int E, int32_t* status, void* stream) {
+  return grouped_gemm_impl(epilogue, A, B, B2, offsets, dst_rows, row_w, Y, ldy, max_rows, K, N, E, status, stream,
+                           nullptr, nullptr, 0);
+}
+
+extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
+                                             const int32_t* row_rank, const int32_t* dst_rows, void* const* peer_base,
+                                             int n_peers, int64_t ldy, int64_t max_rows, int K, int N, int E,
+                                             int32_t* status, void* stream) {
+  using namespace moe;
+  if (!row_rank || !dst_rows || !peer_base) return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: null table");
+  if (n_peers < 1 || n_peers > 16) return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: n_peers=%d out of range", n_peers);
+  for (int g = 0; g < n_peers; ++g)
+    if (!peer_base[g] || (reinterpret_cast<uintptr_t>(peer_base[g]) & 15))
+      return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: peer buffer %d null or unaligned", g);
+  return grouped_gemm_impl(MOE_GEMM_PLAIN, A, B, nullptr, offsets, dst_rows, nullptr, peer_base[0], ldy, max_rows, K, N, E,
+                           status, stream, row_rank, peer_base, n_peers);
+}
+
+static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
+                             const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
+                             int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
+                             void* const* peer_base, int n_peers) {
   using namespace moe;
   using namespace moe::gemm;
   if (epilogue < 0 || epilogue > 3) return fail(MOE_ERR_ARG, "grouped_gemm: unknown epilogue %d", epilogue);
@@ -1132,14 +1165,15 @@ extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, cons
   const int64_t m_tiles_128 = max_rows / BM + E, m_tiles_256 = max_rows / (2 * BM) + E;
   int MT = 1, BN = 128;
   if (gate || (N % 256 == 0 && m_tiles_128 * n_tiles_256 >= dev.sm_count)) BN = 256;
-  bool pair = (gate || N % 256 == 0) && max_rows / E >= 512 &&
+  bool pair = !row_rank && (gate || N % 256 == 0) && max_rows / E >= 512 &&
               (max_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
   if (pair) { MT = 2; BN = 256; }
   // The tokens-as-N kernel is selected only by the override: measured on B200 it matches the rows-as-M
   // kernel when groups are small (both stream weights at HBM speed) and loses when they are large
   // (2-byte epilogue stores, more shared-memory reads per flop), so the default stays rows-as-M.
   int tn = 0;
-  if (const char* force = getenv("MOE_B200_GEMM_TILE_ROWS")) {   // test / measurement override: "128", "256", "pair", "tn128", "tn256"
+  const char* force_env = row_rank ? nullptr : getenv("MOE_B200_GEMM_TILE_ROWS");   // peer scatter: 128-row kernel only
+  if (const char* force = force_env) {   // test / measurement override: "128", "256", "pair", "tn128", "tn256"
     if (force[0] == 't') { tn = atoi(force + 2) == 128 ? 128 : 256; pair = false; }
     else tn = 0;
     if (force[0] == 'p' && (gate || N % 256 == 0)) { MT = 2; BN = 256; pair = true; }
@@ -1153,6 +1187,8 @@ extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, cons
     q.num_n_tiles = gate ? (N + BM - 1) / BM : (N + 2 * BM - 1) / (2 * BM);
     q.num_k_blocks = (K + BK - 1) / BK;
     q.status = status;
+    q.row_rank = nullptr;
+    for (int g = 0; g < 16; ++g) q.peer_base[g] = nullptr;
     CUtensorMap tW, tW2, tX;
     rc = make_tmap(&tW, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM);
     if (rc) return rc;
@@ -1187,6 +1223,8 @@ extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, cons
   p.num_n_tiles = (N + out_cols - 1) / out_cols;
   p.num_k_blocks = (K + BK - 1) / BK;
   p.status = status;
+  p.row_rank = row_rank;
+  for (int g = 0; g < 16; ++g) p.peer_base[g] = (peer_base && g < n_peers) ? peer_base[g] : nullptr;
 
   CUtensorMap tA, tB, tB2;
   rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)max_rows, 0, (uint32_t)(pair ? BM : MT * BM));

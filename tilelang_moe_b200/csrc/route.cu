@@ -443,6 +443,129 @@ extern "C" int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, in
 }
 
 // ====================================================================================
+// Expert parallelism over peer memory: plan tables and the dispatch copy.
+//
+// Every rank knows cnt[s][v]: how many routed rows source rank s sends to virtual expert
+// v = dest_rank * E_local + slot (an all-gather of the per-rank histograms).  From that table alone
+// each rank derives, without talking to anyone,
+//   offsets[j]   expert-major start of local expert j in its own receive buffer,
+//   dst_base[v]  where this rank's rows for virtual expert v start in the destination's buffer
+//                (expert-major there: after the rows of lower-ranked sources for the same expert),
+//   ret_rank[q], ret_row[q]   for the row it holds at expert-major position q: the source rank and the
+//                position in that source's sorted order (= the row of the source's return buffer).
+// ====================================================================================
+namespace moe {
+
+__global__ void __launch_bounds__(1024)
+ep_plan_kernel(const int32_t* __restrict__ cnt_all, int G, int El, int me, int32_t* __restrict__ offsets,
+               int32_t* __restrict__ dst_base, int32_t* __restrict__ ret_rank, int32_t* __restrict__ ret_row) {
+  extern __shared__ int32_t sh[];
+  const int E = G * El;
+  int32_t* cnt = sh;                 // [G][E]
+  int32_t* dbase = cnt + G * E;      // [E]   expert-major start of virtual expert v on its destination
+  int32_t* srcoff = dbase + E;       // [G][El] start of (source s, my expert j) in source s's sorted order
+  const int tid = threadIdx.x;
+  for (int i = tid; i < G * E; i += 1024) cnt[i] = cnt_all[i];
+  __syncthreads();
+  // per destination d: exclusive scan over its local experts of the rows they receive from all sources
+  if (tid < G) {
+    int32_t run = 0;
+    for (int j = 0; j < El; ++j) {
+      const int v = tid * El + j;
+      dbase[v] = run;
+      for (int s = 0; s < G; ++s) run += cnt[s * E + v];
+    }
+    if (tid == me) offsets[El] = run;
+  }
+  // per source s: exclusive prefix over virtual experts up to my range, then inside it
+  if (tid >= 32 && tid < 32 + G) {
+    const int s = tid - 32;
+    int32_t run = 0;
+    for (int v = 0; v < me * El; ++v) run += cnt[s * E + v];
+    for (int j = 0; j < El; ++j) { srcoff[s * El + j] = run; run += cnt[s * E + me * El + j]; }
+  }
+  __syncthreads();
+  for (int v = tid; v < E; v += 1024) {
+    int32_t b = dbase[v];
+    for (int s = 0; s < me; ++s) b += cnt[s * E + v];
+    dst_base[v] = b;
+  }
+  for (int j = tid; j < El; j += 1024) offsets[j] = dbase[me * El + j];
+  // return table: one warp per (source, local expert) segment
+  const int lane = tid & 31;
+  for (int seg = tid >> 5; seg < G * El; seg += 32) {
+    const int s = seg / El, j = seg - s * El;
+    const int v = me * El + j;
+    int32_t q0 = dbase[v];
+    for (int s2 = 0; s2 < s; ++s2) q0 += cnt[s2 * E + v];
+    const int32_t c = cnt[s * E + v], r0 = srcoff[s * El + j];
+    for (int i = lane; i < c; i += 32) { ret_rank[q0 + i] = s; ret_row[q0 + i] = r0 + i; }
+  }
+}
+
+struct PeerPtrs {
+  void* p[16];
+};
+
+// One warp per routed row p (in this rank's sorted order): copy the token's activation row straight into
+// the destination rank's receive buffer at its expert-major position.  Plain 16-byte stores to peer memory.
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm, const int32_t* __restrict__ topk_idx,
+                   const int32_t* __restrict__ id_map, const int32_t* __restrict__ offsets,
+                   const int32_t* __restrict__ dst_base, int k, int El, int64_t n, int vec_per_row, PeerPtrs peers) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = (int64_t)gridDim.x * 8;
+  for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < n; p += nwarps) {
+    const int32_t f = perm[p];
+    const int v = id_map[topk_idx[f]];
+    const int dest = v / El;
+    const int64_t row = (int64_t)dst_base[v] + (p - offsets[v]);
+    const uint4* s = x + (int64_t)(f / k) * vec_per_row;
+    uint4* d = reinterpret_cast<uint4*>(peers.p[dest]) + row * vec_per_row;
+    for (int i = lane; i < vec_per_row; i += 32) d[i] = __ldg(s + i);
+  }
+}
+
+}  // namespace moe
+
+extern "C" int moe_ep_plan(const int32_t* cnt_all, int G, int E_local, int my_rank, int32_t* offsets, int32_t* dst_base,
+                           int32_t* ret_rank, int32_t* ret_row, void* stream) {
+  using namespace moe;
+  if (!cnt_all || !offsets || !dst_base || !ret_rank || !ret_row) return fail(MOE_ERR_ARG, "ep_plan: null pointer");
+  if (G < 1 || G > 16 || E_local < 1 || my_rank < 0 || my_rank >= G) return fail(MOE_ERR_ARG, "ep_plan: bad G=%d E_local=%d rank=%d", G, E_local, my_rank);
+  const int E = G * E_local;
+  const size_t smem = ((size_t)G * E + E + (size_t)G * E_local) * sizeof(int32_t);
+  if (smem > 200 * 1024) return fail(MOE_ERR_UNSUPPORTED, "ep_plan: G*E=%d too large", G * E);
+  if (smem > 48 * 1024) MOE_CUDA_CHECK(cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  ep_plan_kernel<<<1, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(cnt_all, G, E_local, my_rank, offsets, dst_base, ret_rank, ret_row);
+  MOE_CHECK_LAUNCH("ep_plan_kernel");
+  return MOE_OK;
+}
+
+extern "C" int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx, const int32_t* id_map,
+                               const int32_t* offsets, const int32_t* dst_base, int k, int E_local, int64_t n,
+                               int64_t H, void* const* peer_recv, int G, void* stream) {
+  using namespace moe;
+  if (!x || !perm || !topk_idx || !id_map || !offsets || !dst_base || !peer_recv) return fail(MOE_ERR_ARG, "ep_dispatch: null pointer");
+  if (G < 1 || G > 16 || k < 1 || E_local < 1 || H < 8 || H % 8 || n < 0) return fail(MOE_ERR_ARG, "ep_dispatch: bad shape");
+  if (n == 0) return MOE_OK;
+  PeerPtrs pp;
+  for (int g = 0; g < 16; ++g) pp.p[g] = g < G ? peer_recv[g] : nullptr;
+  for (int g = 0; g < G; ++g)
+    if (!pp.p[g] || (reinterpret_cast<uintptr_t>(pp.p[g]) & 15)) return fail(MOE_ERR_ARG, "ep_dispatch: peer buffer %d null or unaligned", g);
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  int64_t blocks = ceil_div64(n, 8);
+  const int64_t cap = (int64_t)dev.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(x), perm, topk_idx, id_map, offsets, dst_base, k, E_local, n, (int)(H / 8), pp);
+  MOE_CHECK_LAUNCH("ep_dispatch_kernel");
+  return MOE_OK;
+}
+
+// ====================================================================================
 // Histogram entry point for callers that have no scratch buffer to give.
 //
 // The per-unit count table that moe_route_histogram keeps in caller-provided workspace lives

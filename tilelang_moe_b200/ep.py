@@ -126,6 +126,64 @@ def ep_forward(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: 
     return out
 
 
+class PeerExchange:
+    """Symmetric receive / return buffers of one expert-parallel group and the peers' addresses of them.
+
+    recv [cap_rows, H]: rows other ranks dispatch to this rank's experts, expert-major.
+    ret  [T_local*k, H]: expert outputs for this rank's routed entries, in its sorted order.
+    cap_rows defaults to the global T*k (every routed row on one rank), so no overflow path exists.
+    """
+
+    def __init__(self, t_local: int, k: int, H: int, world: int, device: torch.device, group=None,
+                 cap_rows: Optional[int] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import ops
+        group = dist.group.WORLD if group is None else group
+        self.cap = t_local * k * world if cap_rows is None else cap_rows
+        self.recv = symm_mem.empty(self.cap, H, dtype=torch.bfloat16, device=device)
+        self.ret = symm_mem.empty(t_local * k, H, dtype=torch.bfloat16, device=device)
+        self.h_recv = symm_mem.rendezvous(self.recv, group)
+        self.h_ret = symm_mem.rendezvous(self.ret, group)
+        self.recv_ptrs = ops._ptr_array(list(self.h_recv.buffer_ptrs))
+        self.ret_ptrs = ops._ptr_array(list(self.h_ret.buffer_ptrs))
+        self.cnt_all = torch.empty(world, 0, dtype=torch.int32, device=device)
+        self.plan_bufs = {}
+
+
+def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: EPPlan, id_map_dev: torch.Tensor,
+                    Wg: torch.Tensor, Wu: torch.Tensor, Wd: torch.Tensor, ops, px: PeerExchange, group=None,
+                    bufs: Optional[dict] = None, timers: Optional[dict] = None, stage=None) -> torch.Tensor:
+    """Expert-parallel forward with the exchange done by this library's own kernels over peer memory:
+    the dispatch is a gather kernel that stores rows straight into the destination's expert-major
+    buffer, the combine exchange is the down GEMM's epilogue storing into the owner's return buffer.
+    One small all-gather of histograms and two barriers per layer; no host synchronisation."""
+    G, El, E = plan.world, plan.e_local, plan.n_experts
+    Tl, H = x_local.shape
+    rank = dist.get_rank(group)
+    st = stage if stage is not None else (lambda name: _null)
+    bufs = {} if bufs is None else bufs
+    with st("route"):
+        scores, idx32 = ops.topk_softmax(logits_local, k, mode="A", index_dtype=torch.int32)
+        counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map_dev, workspace=bufs.get("hist_ws"))
+    with st("counts_allgather"):
+        if px.cnt_all.shape[1] != E:
+            px.cnt_all = torch.empty(G, E, dtype=torch.int32, device=x_local.device)
+        dist.all_gather_into_tensor(px.cnt_all.view(-1), counts, group=group)
+        offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(px.cnt_all, G, El, rank, px.cap, out=px.plan_bufs)
+    with st("dispatch"):
+        ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs)
+        px.h_recv.barrier(channel=0)
+    with st("up_gemm"):
+        act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg, offs_local, B2=Wu,
+                                      out=_take(bufs, "act", px.cap, Wg.shape[1], x_local))
+    with st("down_gemm"):
+        ops.grouped_gemm_peer_scatter(act, Wd, offs_local, ret_rank, ret_row, px.ret_ptrs, H)
+        px.h_ret.barrier(channel=1)
+    with st("combine"):
+        out = ops.combine(px.ret, k, row_of=inv, scale=scores.reshape(-1), T=Tl, out=bufs.get("out"))
+    return out
+
+
 class _Null:
     def __enter__(self):
         return self
@@ -151,7 +209,7 @@ class EPRunner:
     """Holds one rank's shard (weights of its experts, buffers) for the benchmark workload."""
 
     def __init__(self, cfg: dict, rank: int, world: int, device: torch.device, make_weights: Callable,
-                 placement: str = "balanced", calib_seed: int = 1):
+                 placement: str = "balanced", calib_seed: int = 1, exchange: str = "peer"):
         from . import _lib, ops
         from .layer import _Stage
         self.ops, self._Stage = ops, _Stage
@@ -170,6 +228,8 @@ class EPRunner:
         need = _lib.load().moe_route_histogram_workspace(self.Tl * k, E)
         self.bufs = {"hist_ws": torch.empty(max(need, 4), dtype=torch.uint8, device=device)}
         self.imbalance = None
+        self.exchange = exchange
+        self.px = PeerExchange(self.Tl, k, cfg["H"], world, device) if exchange == "peer" else None
 
     def _routed_counts(self, logits_cpu: torch.Tensor) -> List[int]:
         """Rows per expert when `logits_cpu` is routed top-k (through the router and histogram kernels)."""
@@ -183,6 +243,9 @@ class EPRunner:
 
     def forward(self, x_local, logits_local, timers=None):
         stage = (lambda name: self._Stage(timers, name)) if timers is not None else None
+        if self.px is not None:
+            return ep_forward_peer(x_local, logits_local, self.cfg["k"], self.plan, self.id_map_dev, self.Wg, self.Wu,
+                                   self.Wd, self.ops, self.px, bufs=self.bufs, timers=timers, stage=stage)
         return ep_forward(x_local, logits_local, self.cfg["k"], self.plan, self.id_map_dev, self.Wg, self.Wu,
                           self.Wd, self.ops, bufs=self.bufs, timers=timers, stage=stage)
 
@@ -208,4 +271,5 @@ class EPRunner:
         # kernels of this library per step: topk, 3 x histogram, gather, regroup, gather, up, down, combine
         h2d = (x_pin.numel() * 2 + lg_pin.numel() * 4) * self.world
         d2h = out_pin.numel() * 2 * self.world
-        return step, step_e2e, 10, h2d, d2h
+        # peer exchange: topk, 3 x histogram, plan, dispatch, up, down(+scatter), combine
+        return step, step_e2e, (9 if self.px is not None else 10), h2d, d2h

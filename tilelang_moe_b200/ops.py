@@ -225,3 +225,54 @@ def ep_regroup(recv_counts: torch.Tensor, n_recv_bound: int):
         rc = _lib.load().moe_ep_regroup(_ptr(recv_counts.contiguous()), G, El, _ptr(offsets), _ptr(src_row), _stream())
     _lib.check(rc, "moe_ep_regroup")
     return offsets, src_row
+
+
+# ----------------------------------------------------------------------------- expert parallelism over peer memory
+def _ptr_array(ptrs):
+    import ctypes
+    arr = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr
+
+
+def ep_plan(cnt_all: torch.Tensor, G: int, e_local: int, rank: int, cap_rows: int, out: Optional[dict] = None):
+    """cnt_all int32 [G, G*e_local] -> (offsets [e_local+1], dst_base [G*e_local], ret_rank [cap], ret_row [cap])."""
+    _need_cuda(cnt_all)
+    dev = cnt_all.device
+    out = {} if out is None else out
+    if "offsets" not in out:
+        out["offsets"] = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+        out["dst_base"] = torch.empty(G * e_local, dtype=torch.int32, device=dev)
+        out["ret_rank"] = torch.empty(cap_rows, dtype=torch.int32, device=dev)
+        out["ret_row"] = torch.empty(cap_rows, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().moe_ep_plan(_ptr(cnt_all), G, e_local, rank, _ptr(out["offsets"]), _ptr(out["dst_base"]),
+                                     _ptr(out["ret_rank"]), _ptr(out["ret_row"]), _stream())
+    _lib.check(rc, "moe_ep_plan")
+    return out["offsets"], out["dst_base"], out["ret_rank"], out["ret_row"]
+
+
+def ep_dispatch(x: torch.Tensor, perm: torch.Tensor, idx32: torch.Tensor, id_map: torch.Tensor, offsets: torch.Tensor,
+                dst_base: torch.Tensor, k: int, e_local: int, peer_recv_ptrs) -> None:
+    """Copy every routed row of x into the destination rank's receive buffer (peer stores)."""
+    _need_cuda(x, perm)
+    n = perm.numel()
+    arr = peer_recv_ptrs if not isinstance(peer_recv_ptrs, (list, tuple)) else _ptr_array(peer_recv_ptrs)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().moe_ep_dispatch(_ptr(x), _ptr(perm), _ptr(idx32), _ptr(id_map), _ptr(offsets), _ptr(dst_base),
+                                         k, e_local, n, x.shape[1], arr, len(arr), _stream())
+    _lib.check(rc, "moe_ep_dispatch")
+
+
+def grouped_gemm_peer_scatter(A: torch.Tensor, B: torch.Tensor, offsets: torch.Tensor, row_rank: torch.Tensor,
+                              dst_rows: torch.Tensor, peer_ptrs, ldy: int, max_rows: Optional[int] = None) -> None:
+    """Expert GEMM whose epilogue stores row r into peer buffer row_rank[r] at row dst_rows[r]."""
+    _need_cuda(A, B, offsets)
+    rows, K = A.shape
+    E, N, _ = B.shape
+    arr = peer_ptrs if not isinstance(peer_ptrs, (list, tuple)) else _ptr_array(peer_ptrs)
+    with torch.cuda.device(A.device):
+        rc = _lib.load().moe_grouped_gemm_peer_scatter(_ptr(A), _ptr(B), _ptr(offsets), _ptr(row_rank), _ptr(dst_rows),
+                                                       arr, len(arr), ldy, rows if max_rows is None else max_rows, K, N,
+                                                       E, _ptr(status_buffer(A.device)), _stream())
+    _lib.check(rc, "moe_grouped_gemm_peer_scatter")
+    _after(A.device)
