@@ -127,14 +127,16 @@ int moe_gather_rows(const void* src, const int32_t* perm, int div, int64_t n_row
  *   dst_rows int32 [rows] or NULL: output row of sorted row r (PLAIN, SCALE_SCATTER)
  *   row_w    fp32 [rows]: routing weight of sorted row r (SCALE_SCATTER)
  *   Y        bf16 [*, N] row stride ldy (fp32 for MOE_GEMM_PLAIN_F32)
- *   max_rows upper bound of offsets[E] known on the host (sizes the TMA map and
- *            the tile bound); rows beyond offsets[E] are never written
+ *   max_rows rows of A that may be read (its allocation; >= offsets[E]); rows beyond
+ *            offsets[E] are never written
+ *   expected_rows  how many rows the caller expects to be live (0 = max_rows): only
+ *            steers the choice of tile shape when max_rows is a buffer capacity
  * K % 8 == 0, N % 8 == 0.  Workspace: none.
  */
 int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2,
                      const int32_t* offsets, const int32_t* dst_rows, const float* row_w, void* Y,
-                     int64_t ldy, int64_t max_rows, int K, int N, int E, int32_t* status,
-                     void* stream);
+                     int64_t ldy, int64_t max_rows, int64_t expected_rows, int K, int N, int E,
+                     int32_t* status, void* stream);
 
 /* ---- combine ----------------------------------------------------------------------
  * out[t,:] = (shared ? shared[t,:] : 0) + sum_{s<k} c(t,s) * Yk[r(t,s),:], fp32 sum in
@@ -188,7 +190,8 @@ int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx,
 int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                   const int32_t* row_rank, const int32_t* dst_rows,
                                   void* const* peer_base, int n_peers, int64_t ldy, int64_t max_rows,
-                                  int K, int N, int E, int32_t* status, void* stream);
+                                  int64_t expected_rows, int K, int N, int E, int32_t* status,
+                                  void* stream);
 
 #ifdef __cplusplus
 }

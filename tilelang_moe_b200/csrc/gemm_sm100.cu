@@ -34,6 +34,7 @@
 namespace moe {
 namespace gemm {
 
+constexpr int EPI_PEER = 4;            // internal: plain bf16 rows stored into other GPUs' buffers (row_rank / peer_base)
 constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
@@ -54,7 +55,13 @@ struct Cfg {
   // layout: [stages][barriers 256 B][tile tables]
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
-  static constexpr int SMEM_BYTES = TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 1024;  // + alignment slack
+  static constexpr int STAGING_OFFSET = (TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 127) & ~127;   // 16-byte accesses
+  static constexpr int SMEM_BYTES = STAGING_OFFSET + 1024;  // + alignment slack
+  // peer epilogue: 4 warps x 32 rows x (128 B + 16 B pad) to turn per-thread rows into 128-byte row segments
+  static constexpr int STAGING_PITCH = 144;
+  static constexpr int SMEM_BYTES_PEER = SMEM_BYTES + 4 * 32 * STAGING_PITCH;
+  static_assert(STAGING_OFFSET % 16 == 0 && STAGING_PITCH % 16 == 0, "staging rows are accessed as 16-byte vectors");
+  static_assert(SMEM_BYTES_PEER <= 227 * 1024, "shared memory budget");
 };
 
 struct Params {
@@ -418,7 +425,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (row_ok) {
         if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
         if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[grow];
-        if (EPI == MOE_GEMM_PLAIN && p.row_rank) ybase = p.peer_base[p.row_rank[grow]];
+        if (EPI == EPI_PEER) ybase = p.peer_base[p.row_rank[grow]];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * MT * BN + half * BN);
 #pragma unroll 1
@@ -439,6 +446,38 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         const int col = n0 + c * 32;
+        if (EPI == EPI_PEER) {
+          // Remote rows: NVLink wants long contiguous writes.  Two 32-column chunks of every row are parked in
+          // shared memory (this warp's 32 rows x 128 bytes), then written out with 8 lanes per row, so that each
+          // store instruction carries four 128-byte row segments instead of thirty-two 16-byte pieces.
+          unsigned char* stg = smem + C::STAGING_OFFSET + (warp - 2) * 32 * C::STAGING_PITCH;
+          uint4* mine = reinterpret_cast<uint4*>(stg + lane * C::STAGING_PITCH + (c & 1) * 64);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
+            o.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+            o.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+            o.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            mine[j] = o;
+          }
+          if (c & 1) {
+            __syncwarp();
+            const unsigned long long row_ptr = row_ok
+                ? reinterpret_cast<unsigned long long>(reinterpret_cast<__nv_bfloat16*>(ybase) + out_row * p.ldy) : 0ull;
+            const int col0 = n0 + (c - 1) * 32;          // first of the 64 columns parked
+            const int seg = lane & 7;                    // 16-byte piece of the 128-byte segment
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + (lane >> 3);
+              const unsigned long long rp = __shfl_sync(0xFFFFFFFFu, row_ptr, r);
+              const uint4 val = *reinterpret_cast<const uint4*>(stg + r * C::STAGING_PITCH + seg * 16);
+              if (rp != 0ull && col0 + seg * 8 < p.N)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(rp) + col0 + seg * 8) = val;
+            }
+            __syncwarp();
+          }
+        } else
         if (row_ok && col < p.N) {
           if (EPI == MOE_GEMM_PLAIN_F32) {
             float* dst = reinterpret_cast<float*>(p.Y) + out_row * p.ldy + col;
@@ -1064,12 +1103,13 @@ template <int MT, int BN, int EPI>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
                   cudaStream_t st) {
   using C = Cfg<MT, BN>;
+  constexpr int SMEM = EPI == EPI_PEER ? C::SMEM_BYTES_PEER : C::SMEM_BYTES;
   static bool attr_set = false;   // per instantiation; the attribute is idempotent
   if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<MT, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<MT, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr_set = true;
   }
-  grouped_gemm_kernel<MT, BN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tA, tB, tB2, p);
+  grouped_gemm_kernel<MT, BN, EPI><<<grid, NUM_THREADS, SMEM, st>>>(tA, tB, tB2, p);
   MOE_CHECK_LAUNCH("grouped_gemm_kernel");
   return MOE_OK;
 }
@@ -1109,19 +1149,19 @@ static int launch_tn(const CUtensorMap& tW, const CUtensorMap& tW2, const CUtens
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                              const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                              int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
-                             void* const* peer_base, int n_peers);
+                             void* const* peer_base, int n_peers, int64_t expected_rows);
 
 extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                                 const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
-                                int K, int N, int E, int32_t* status, void* stream) {
+                                int64_t expected_rows, int K, int N, int E, int32_t* status, void* stream) {
   return grouped_gemm_impl(epilogue, A, B, B2, offsets, dst_rows, row_w, Y, ldy, max_rows, K, N, E, status, stream,
-                           nullptr, nullptr, 0);
+                           nullptr, nullptr, 0, expected_rows);
 }
 
 extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                              const int32_t* row_rank, const int32_t* dst_rows, void* const* peer_base,
-                                             int n_peers, int64_t ldy, int64_t max_rows, int K, int N, int E,
-                                             int32_t* status, void* stream) {
+                                             int n_peers, int64_t ldy, int64_t max_rows, int64_t expected_rows,
+                                             int K, int N, int E, int32_t* status, void* stream) {
   using namespace moe;
   if (!row_rank || !dst_rows || !peer_base) return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: null table");
   if (n_peers < 1 || n_peers > 16) return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: n_peers=%d out of range", n_peers);
@@ -1129,15 +1169,17 @@ extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const
     if (!peer_base[g] || (reinterpret_cast<uintptr_t>(peer_base[g]) & 15))
       return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: peer buffer %d null or unaligned", g);
   return grouped_gemm_impl(MOE_GEMM_PLAIN, A, B, nullptr, offsets, dst_rows, nullptr, peer_base[0], ldy, max_rows, K, N, E,
-                           status, stream, row_rank, peer_base, n_peers);
+                           status, stream, row_rank, peer_base, n_peers, expected_rows);
 }
 
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                              const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                              int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
-                             void* const* peer_base, int n_peers) {
+                             void* const* peer_base, int n_peers, int64_t expected_rows) {
   using namespace moe;
   using namespace moe::gemm;
+  // rows the caller expects to be live (<= max_rows, which may be a buffer capacity): steers the tile rule
+  const int64_t live_rows = (expected_rows > 0 && expected_rows < max_rows) ? expected_rows : max_rows;
   if (epilogue < 0 || epilogue > 3) return fail(MOE_ERR_ARG, "grouped_gemm: unknown epilogue %d", epilogue);
   if (max_rows < 0 || K < 8 || N < 8 || (K % 8) || (N % 8) || E < 1)
     return fail(MOE_ERR_ARG, "grouped_gemm: bad shape rows=%lld K=%d N=%d E=%d (K, N multiples of 8)", (long long)max_rows, K, N, E);
@@ -1162,11 +1204,11 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   // The single-CTA 256-row shape is kept for measurement (override below).
   const bool gate = epilogue == MOE_GEMM_SILU_GATE;
   const int n_tiles_256 = gate ? (N + 127) / 128 : (N + 255) / 256;
-  const int64_t m_tiles_128 = max_rows / BM + E, m_tiles_256 = max_rows / (2 * BM) + E;
+  const int64_t m_tiles_128 = live_rows / BM + E, m_tiles_256 = live_rows / (2 * BM) + E;
   int MT = 1, BN = 128;
   if (gate || (N % 256 == 0 && m_tiles_128 * n_tiles_256 >= dev.sm_count)) BN = 256;
-  bool pair = !row_rank && (gate || N % 256 == 0) && max_rows / E >= 512 &&
-              (max_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
+  bool pair = !row_rank && (gate || N % 256 == 0) && live_rows / E >= 512 &&
+              (live_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
   if (pair) { MT = 2; BN = 256; }
   // The tokens-as-N kernel is selected only by the override: measured on B200 it matches the rows-as-M
   // kernel when groups are small (both stream weights at HBM speed) and loses when they are large
@@ -1250,6 +1292,10 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
       case MOE_GEMM_PLAIN_F32: return launch_pair<MOE_GEMM_PLAIN_F32>(tA, tB, tB2, p, pgrid, st);
       default: return launch_pair<MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, pgrid, st);
     }
+  }
+  if (row_rank) {   // combine exchange fused into the epilogue: 128-row tiles, 256 (or 128) accumulator columns
+    if (BN == 256) return launch<1, 256, EPI_PEER>(tA, tB, tB2, p, grid, st);
+    return launch<1, 128, EPI_PEER>(tA, tB, tB2, p, grid, st);
   }
 #define MOE_GEMM_CASE(EPI_)                                                                  \
   if (MT == 2) return launch<2, 256, EPI_>(tA, tB, tB2, p, grid, st);                          \

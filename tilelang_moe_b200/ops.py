@@ -151,7 +151,8 @@ def gather_rows(src: torch.Tensor, perm: Optional[torch.Tensor], div: int = 1, o
 def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets: torch.Tensor,
                         B2: Optional[torch.Tensor] = None, dst_rows: Optional[torch.Tensor] = None,
                         row_w: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                        out_rows: Optional[int] = None, max_rows: Optional[int] = None) -> torch.Tensor:
+                        out_rows: Optional[int] = None, max_rows: Optional[int] = None,
+                        expected_rows: int = 0) -> torch.Tensor:
     """Expert GEMM over expert-sorted rows.  A [rows,K] bf16, B (and B2) [E,N,K] bf16,
     offsets int32 [E+1] on the device.  See include/moe_b200.h for the epilogues."""
     _need_cuda(A, B, offsets)
@@ -174,7 +175,7 @@ def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets
         out = torch.empty(rows if out_rows is None else out_rows, N, dtype=odt, device=A.device)
     with torch.cuda.device(A.device):
         rc = _lib.load().moe_grouped_gemm(epilogue, _ptr(A), _ptr(B), _ptr(B2), _ptr(offsets), _ptr(dst_rows),
-                                          _ptr(row_w), _ptr(out), out.stride(0), max_rows, K, N, E,
+                                          _ptr(row_w), _ptr(out), out.stride(0), max_rows, expected_rows, K, N, E,
                                           _ptr(status_buffer(A.device)), _stream())
     _lib.check(rc, "moe_grouped_gemm")
     _after(A.device)
@@ -264,7 +265,8 @@ def ep_dispatch(x: torch.Tensor, perm: torch.Tensor, idx32: torch.Tensor, id_map
 
 
 def grouped_gemm_peer_scatter(A: torch.Tensor, B: torch.Tensor, offsets: torch.Tensor, row_rank: torch.Tensor,
-                              dst_rows: torch.Tensor, peer_ptrs, ldy: int, max_rows: Optional[int] = None) -> None:
+                              dst_rows: torch.Tensor, peer_ptrs, ldy: int, max_rows: Optional[int] = None,
+                              expected_rows: int = 0) -> None:
     """Expert GEMM whose epilogue stores row r into peer buffer row_rank[r] at row dst_rows[r]."""
     _need_cuda(A, B, offsets)
     rows, K = A.shape
@@ -272,7 +274,7 @@ def grouped_gemm_peer_scatter(A: torch.Tensor, B: torch.Tensor, offsets: torch.T
     arr = peer_ptrs if not isinstance(peer_ptrs, (list, tuple)) else _ptr_array(peer_ptrs)
     with torch.cuda.device(A.device):
         rc = _lib.load().moe_grouped_gemm_peer_scatter(_ptr(A), _ptr(B), _ptr(offsets), _ptr(row_rank), _ptr(dst_rows),
-                                                       arr, len(arr), ldy, rows if max_rows is None else max_rows, K, N,
-                                                       E, _ptr(status_buffer(A.device)), _stream())
+                                                       arr, len(arr), ldy, rows if max_rows is None else max_rows,
+                                                       expected_rows, K, N, E, _ptr(status_buffer(A.device)), _stream())
     _lib.check(rc, "moe_grouped_gemm_peer_scatter")
     _after(A.device)
