@@ -522,7 +522,12 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm
     const int64_t row = (int64_t)dst_base[v] + (p - offsets[v]);
     const uint4* s = x + (int64_t)(f / k) * vec_per_row;
     uint4* d = reinterpret_cast<uint4*>(peers.p[dest]) + row * vec_per_row;
-    for (int i = lane; i < vec_per_row; i += 32) d[i] = __ldg(s + i);
+    int i = lane;
+    for (; i + 96 < vec_per_row; i += 128) {   // four loads in flight before the first remote store
+      const uint4 a = __ldg(s + i), b = __ldg(s + i + 32), c = __ldg(s + i + 64), e = __ldg(s + i + 96);
+      d[i] = a; d[i + 32] = b; d[i + 64] = c; d[i + 96] = e;
+    }
+    for (; i < vec_per_row; i += 32) d[i] = __ldg(s + i);
   }
 }
 

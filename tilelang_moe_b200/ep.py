@@ -172,12 +172,14 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
         offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(px.cnt_all, G, El, rank, px.cap, out=px.plan_bufs)
     with st("dispatch"):
         ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs)
+    with st("dispatch_barrier"):
         px.h_recv.barrier(channel=0)
     with st("up_gemm"):
         act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg, offs_local, B2=Wu,
                                       out=_take(bufs, "act", px.cap, Wg.shape[1], x_local), expected_rows=Tl * k)
     with st("down_gemm"):
         ops.grouped_gemm_peer_scatter(act, Wd, offs_local, ret_rank, ret_row, px.ret_ptrs, H, expected_rows=Tl * k)
+    with st("combine_barrier"):
         px.h_ret.barrier(channel=1)
     with st("combine"):
         out = ops.combine(px.ret, k, row_of=inv, scale=scores.reshape(-1), T=Tl, out=bufs.get("out"))
