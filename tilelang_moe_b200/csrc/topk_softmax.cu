@@ -176,6 +176,66 @@ __device__ __forceinline__ double block_sum_ordered(double v, RadixCtrl* ctrl, i
   return t;
 }
 
+// Descending bitonic sort of RT*EPT 64-bit entries held EPT per thread (entry g = tid*EPT + e).
+// Exchanges at distance < EPT stay in registers, distance < 32*EPT go through warp shuffles, and only the
+// few long-distance stages of the last merges use shared memory with a block barrier.
+template <int EPT>
+__device__ __forceinline__ void block_sort_desc(uint64_t* sbuf, int tid) {
+  constexpr int NSORT = RT * EPT;
+  uint64_t v[EPT];
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) v[e] = sbuf[tid * EPT + e];
+  for (int size = 2; size <= NSORT; size <<= 1) {
+    int stride = size >> 1;
+    // long distance: through shared memory
+    for (; stride >= 32 * EPT; stride >>= 1) {
+      __syncthreads();
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) sbuf[tid * EPT + e] = v[e];
+      __syncthreads();
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) {
+        const int g = tid * EPT + e;
+        const uint64_t o = sbuf[g ^ stride];
+        const bool keep_max = ((g & stride) == 0) == ((g & size) == 0);
+        v[e] = keep_max ? (v[e] > o ? v[e] : o) : (v[e] < o ? v[e] : o);
+      }
+    }
+    // inside a warp: shuffles
+    for (; stride >= EPT; stride >>= 1) {
+      const int lx = stride / EPT;
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) {
+        const int g = tid * EPT + e;
+        const uint64_t o = __shfl_xor_sync(0xFFFFFFFFu, v[e], lx);
+        const bool keep_max = ((g & stride) == 0) == ((g & size) == 0);
+        v[e] = keep_max ? (v[e] > o ? v[e] : o) : (v[e] < o ? v[e] : o);
+      }
+    }
+    // inside a thread: registers (compile-time distances)
+#pragma unroll
+    for (int st = EPT / 2; st > 0; st >>= 1) {
+      if (st <= (size >> 1)) {
+#pragma unroll
+        for (int e = 0; e < EPT; ++e) {
+          if ((e & st) == 0) {
+            const int g = tid * EPT + e;
+            const bool desc = (g & size) == 0;
+            const uint64_t a = v[e], b = v[e | st];
+            const bool swap = (a < b) == desc;
+            v[e] = swap ? b : a;
+            v[e | st] = swap ? a : b;
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) sbuf[tid * EPT + e] = v[e];
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(RT)
 topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld, int k, int kpad, int mode,
                   int slice, int vec_ok, float* __restrict__ scores, int64_t* __restrict__ idx64,
@@ -346,17 +406,25 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
     status[0] = ST_INTERNAL; status[1] = (int32_t)ctrl->sel_count; status[2] = (int32_t)row;
   }
 
-  // ---- bitonic sort, descending, of kpad 64-bit entries (padding entries are 0 and sink to the end)
-  for (int size = 2; size <= kpad; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int t = tid; t < (kpad >> 1); t += RT) {
-        const int i = 2 * t - (t & (stride - 1));
-        const int j = i + stride;
-        const bool desc = (i & size) == 0;
-        const uint64_t a = sbuf[i], b = sbuf[j];
-        if ((a < b) == desc) { sbuf[i] = b; sbuf[j] = a; }
+  // ---- bitonic sort, descending, of kpad 64-bit entries (padding entries are 0 and sink to the end):
+  //      in registers + shuffles when there is at least one entry per thread, else the plain shared-memory network
+  if (kpad >= RT) {   // block-uniform
+    if (kpad == RT) block_sort_desc<1>(sbuf, tid);
+    else if (kpad == 2 * RT) block_sort_desc<2>(sbuf, tid);
+    else if (kpad == 4 * RT) block_sort_desc<4>(sbuf, tid);
+    else block_sort_desc<8>(sbuf, tid);
+  } else {
+    for (int size = 2; size <= kpad; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int t = tid; t < (kpad >> 1); t += RT) {
+          const int i = 2 * t - (t & (stride - 1));
+          const int j = i + stride;
+          const bool desc = (i & size) == 0;
+          const uint64_t a = sbuf[i], b = sbuf[j];
+          if ((a < b) == desc) { sbuf[i] = b; sbuf[j] = a; }
+        }
+        __syncthreads();
       }
-      __syncthreads();
     }
   }
 
