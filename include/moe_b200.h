@@ -51,6 +51,12 @@ extern "C" {
 #define MOE_GEMM_SCALE_SCATTER 2  /* Y[dst(r)] = w[r] * (A[r] . B[e]^T)            */
 #define MOE_GEMM_PLAIN_F32 3      /* as PLAIN, fp32 output                         */
 
+/* 16-bit element type of activations, weights and outputs (accumulation is always fp32).
+ * The reference's wrappers default to fp16 (kernels/fusedmoe_tilelang.py:257), the
+ * benchmark contract is quoted in bf16; both run on the same kernels. */
+#define MOE_DTYPE_BF16 0
+#define MOE_DTYPE_F16 1
+
 const char* moe_last_error(void);
 int moe_abi_version(void);
 
@@ -136,7 +142,7 @@ int moe_gather_rows(const void* src, const int32_t* perm, int div, int64_t n_row
 int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2,
                      const int32_t* offsets, const int32_t* dst_rows, const float* row_w, void* Y,
                      int64_t ldy, int64_t max_rows, int64_t expected_rows, int K, int N, int E,
-                     int32_t* status, void* stream);
+                     int dtype, int32_t* status, void* stream);
 
 /* ---- combine ----------------------------------------------------------------------
  * out[t,:] = (shared ? shared[t,:] : 0) + sum_{s<k} c(t,s) * Yk[r(t,s),:], fp32 sum in
@@ -146,13 +152,13 @@ int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2,
  * when expert outputs come back unscaled from other ranks).  H % 8 == 0.
  */
 int moe_combine(const void* Yk, const void* shared, const int32_t* row_of, const float* scale,
-                int64_t T, int k, int64_t H, void* out, void* stream);
+                int64_t T, int k, int64_t H, int dtype, void* out, void* stream);
 
 /* ---- router logits ------------------------------------------------------------------
- * logits[t,e] = sum_h x[t,h] * Wr[e,h], bf16 inputs, fp32 accumulate and output.
+ * logits[t,e] = sum_h x[t,h] * Wr[e,h], 16-bit inputs, fp32 accumulate and output.
  * Replaces kernels/fusedmoe_baseline.py:72.  H % 8 == 0.
  */
-int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, float* logits,
+int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, int dtype, float* logits,
                       int32_t* status, void* stream);
 
 /* ---- expert-parallel regroup table -----------------------------------------------------
@@ -190,8 +196,8 @@ int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx,
 int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                   const int32_t* row_rank, const int32_t* dst_rows,
                                   void* const* peer_base, int n_peers, int64_t ldy, int64_t max_rows,
-                                  int64_t expected_rows, int K, int N, int E, int32_t* status,
-                                  void* stream);
+                                  int64_t expected_rows, int K, int N, int E, int dtype,
+                                  int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -28,7 +28,7 @@ def test_version_and_error_channel(lib):
     assert b"null" in lib.moe_last_error()
     rc = lib.moe_topk_softmax(ctypes.c_void_p(16), 4, 8, 8, 9, 0, ctypes.c_void_p(16), ctypes.c_void_p(16), None, None, None)
     assert rc == -1 and b"bad shape" in lib.moe_last_error()
-    rc = lib.moe_grouped_gemm(0, None, None, None, None, None, None, None, 8, 16, 0, 12, 8, 1, None, None)
+    rc = lib.moe_grouped_gemm(0, None, None, None, None, None, None, None, 8, 16, 0, 12, 8, 1, 0, None, None)
     assert rc == -1 and b"multiples of 8" in lib.moe_last_error()
     rc = lib.moe_route_histogram(None, 1, 10, 4, None, None, None, None, None, None, 0, None, None)
     assert rc == -1

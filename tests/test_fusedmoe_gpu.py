@@ -66,3 +66,16 @@ def test_no_shared_expert_skewed_routing(cuda, lib):
                           logits=logits.to(cuda))
     ops.check_status(cuda)
     torch.testing.assert_close(y.float().cpu(), ref, rtol=RTOL, atol=ATOL)
+
+
+def test_float16_layer_default_dtype_of_the_reference(cuda, lib):
+    x, w = O.make_fusedmoe_inputs(2, 96, 256, 128, 8, 1, 2, dtype=torch.float16, seed=7)
+    logits = O.router_logits(x.view(-1, 256), w["router_weight"])
+    ref = O.fusedmoe(x, *[w[n] for n in NAMES], 2, logits=logits)
+    m = kernels.FusedMoETileLang(256, 128, 8, 1, 2, 2, 96)            # dtype defaults to float16, as in the reference
+    y = m.forward(x.to(cuda), *[w[n].to(cuda) for n in NAMES], logits=logits.to(cuda))
+    ops.check_status(cuda)
+    assert y.dtype == torch.float16 and y.shape == x.shape
+    torch.testing.assert_close(y.float().cpu(), ref, rtol=RTOL, atol=ATOL)
+    x2, w2 = kernels.generate_fusedmoe_inputs(1, 8, 64, 32, 4, 1, 2, device="cuda")
+    assert x2.dtype == torch.float16 and w2["routed_down"].shape == (4, 64, 32)

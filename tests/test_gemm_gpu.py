@@ -124,3 +124,17 @@ def test_both_tile_shapes_on_ragged_groups(cuda, lib, tile_rows, monkeypatch):
     ref[perm.long()] = O.grouped_gemm(act.cpu(), Wd, eid) * w[:, None]
     _close(yk, ref)
     ops.check_status(cuda)
+
+
+def test_float16_inputs(cuda, lib):
+    """fp16 is the reference wrappers' own dtype (kernels/grouped_gemm_tilelang.py:664): same kernels, other
+    instruction-descriptor format and output conversion."""
+    g = torch.Generator().manual_seed(12)
+    T, H, I, E = 777, 384, 256, 5
+    X = torch.randn(T, H, generator=g).half()
+    W = (torch.randn(E, I, H, generator=g) * 0.05).half()
+    idx = torch.randint(0, E, (T,), generator=g)
+    y = kernels.grouped_gemm(X.to(cuda), W.to(cuda), idx.to(cuda))
+    ops.check_status(cuda)
+    assert y.dtype == torch.float16
+    torch.testing.assert_close(y.float().cpu(), O.grouped_gemm(X, W, idx), rtol=2e-3, atol=2e-3)

@@ -125,3 +125,32 @@ def test_conventions_agree_like_the_reference_test(cuda, lib):
         assert torch.equal(ib, ia) and torch.equal(ib, ir)
         assert (sb - sr).abs().max().item() < 5e-7
         assert (sa.sum(-1) < 1.0 + 1e-6).all()
+
+
+@pytest.mark.parametrize("H,E,K", [(3584, 64, 8), (4096, 128, 8), (5120, 160, 6), (2048, 8, 2), (7168, 256, 8)])
+def test_router_gemm_then_topk_like_the_reference_fusion_test(cuda, lib, H, E, K):
+    """Reference tests/test_router_fusion_correctness.py: T=256, bf16 ~ N(0,1), seed 0; pass = every row selects the
+    same expert set as topk(X.float() @ W.float()).  Here also: logits to 1e-4 and, on rows whose k-th / (k+1)-th
+    logit gap exceeds 1e-4, identical order and scores."""
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(256, H, generator=g).bfloat16()
+    W = torch.randn(E, H, generator=g).bfloat16()
+    ref_logits = X.float() @ W.float().T
+    lg = ops.router_logits(X.to(cuda), W.to(cuda))
+    ops.check_status(cuda)
+    torch.testing.assert_close(lg.cpu(), ref_logits, rtol=1e-4, atol=1e-3)
+    s, i = ops.router_topk_softmax(X.to(cuda), W.to(cuda), K)
+    s_ref, i_ref = O.topk_softmax(ref_logits, K, "B")
+    sv = torch.sort(ref_logits, dim=-1, descending=True).values
+    clear = ((sv[:, :K] - sv[:, 1:K + 1]).min(-1).values > 1e-2)
+    assert clear.sum() > 200
+    assert torch.equal(torch.sort(i.cpu()[clear], -1).values, torch.sort(i_ref[clear], -1).values)
+    assert torch.equal(i.cpu()[clear], i_ref[clear])
+    # scores: exact (1e-6) against the softmax of the logits the GPU produced; against the fp32 reference they can
+    # only be as close as the logits are (a logit error d moves a score by about d in relative terms)
+    s_own, i_own = O.topk_softmax(lg.cpu(), K, "B")
+    assert torch.equal(i.cpu(), i_own)
+    torch.testing.assert_close(s.cpu(), s_own, rtol=RTOL, atol=1e-30)
+    d = float((lg.cpu() - ref_logits).abs().max())
+    torch.testing.assert_close(s.cpu()[clear], s_ref[clear], rtol=4 * d + 1e-5, atol=1e-7)

@@ -28,6 +28,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <mutex>
 #include <stdlib.h>
 
@@ -73,6 +74,7 @@ struct Params {
   int K, N, E;
   int num_n_tiles;
   int num_k_blocks;
+  int f16;           // 0: bf16 inputs / outputs, 1: fp16
   int32_t* status;
   // optional scatter of output rows into other GPUs' buffers (expert-parallel combine): row r goes to
   // peer_base[row_rank[r]] at row dst_rows[r]; plain stores to peer memory from the epilogue
@@ -226,8 +228,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 // Instruction descriptor: D fp32, A/B bf16, both K-major, M=128, N=n.
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Instruction descriptor bits: D fp32 (bit 4), A and B format (bits 7.., 10..: 1 = bf16, 0 = fp16), both K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int n, int f16 = 0) {
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 // ------------------------------------------------------------------------------ tile schedule
@@ -256,6 +259,14 @@ __device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+// two fp32 -> two 16-bit outputs of the tensor's element type
+__device__ __forceinline__ uint32_t pack_out(float a, float b, int f16) {
+  if (f16) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  return pack_bf16(a, b);
 }
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 
@@ -360,7 +371,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else if (warp == 1) {
     // ===================================================================== MMA issuer
-    constexpr uint32_t idesc = make_idesc(BN);
+    const uint32_t idesc = make_idesc(BN, p.f16);
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
@@ -455,10 +466,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 o;
-            o.x = pack_bf16(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-            o.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-            o.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-            o.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+            o.x = pack_out(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), p.f16);
+            o.y = pack_out(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), p.f16);
+            o.z = pack_out(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), p.f16);
+            o.w = pack_out(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), p.f16);
             mine[j] = o;
           }
           if (c & 1) {
@@ -491,10 +502,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int j = 0; j < 4; ++j) {
               if (col + j * 8 < p.N) {
                 uint4 o;
-                o.x = pack_bf16(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-                o.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-                o.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-                o.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                o.x = pack_out(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), p.f16);
+                o.y = pack_out(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), p.f16);
+                o.z = pack_out(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), p.f16);
+                o.w = pack_out(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), p.f16);
                 *reinterpret_cast<uint4*>(dst + j * 8) = o;
               }
             }
@@ -594,8 +605,8 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc,
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__host__ __device__ constexpr uint32_t make_idesc_pair(int n) {   // M = 256 across the pair
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_pair(int n, int f16 = 0) {   // M = 256 across the pair
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
 template <int EPI>
@@ -706,7 +717,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   } else if (warp == 1) {
     // ===================================================================== MMA issuer (leader CTA only)
     if (leader) {
-      constexpr uint32_t idesc = make_idesc_pair(BN);
+      const uint32_t idesc = make_idesc_pair(BN, p.f16);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -798,10 +809,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             for (int j = 0; j < 4; ++j) {
               if (col + j * 8 < p.N) {
                 uint4 o;
-                o.x = pack_bf16(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]));
-                o.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-                o.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-                o.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+                o.x = pack_out(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), p.f16);
+                o.y = pack_out(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), p.f16);
+                o.z = pack_out(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), p.f16);
+                o.w = pack_out(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), p.f16);
                 *reinterpret_cast<uint4*>(dst + j * 8) = o;
               }
             }
@@ -852,8 +863,8 @@ struct TnCfg {
   static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
   static constexpr int SMEM_BYTES = TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 1024;
 };
-__host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n, int f16 = 0) {
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 template <int TN, int EPI>
@@ -965,7 +976,7 @@ grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
       int cnt = t.row_end - t.row0;
       if (cnt > TN) cnt = TN;
       const int n16 = (cnt + 15) & ~15;                        // instruction N: tokens rounded up to 16
-      const uint32_t idesc = make_idesc_mn(BM, n16);
+      const uint32_t idesc = make_idesc_mn(BM, n16, p.f16);
       if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d0 = tmem_base + (uint32_t)(acc * 2 * TN);
@@ -1044,6 +1055,7 @@ grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
             if (EPI == MOE_GEMM_SCALE_SCATTER) val *= __shfl_sync(0xFFFFFFFFu, my_w, j);
             if (d >= 0 && feat_ok) {
               if (EPI == MOE_GEMM_PLAIN_F32) reinterpret_cast<float*>(p.Y)[(int64_t)d * p.ldy + feat] = val;
+              else if (p.f16) reinterpret_cast<__half*>(p.Y)[(int64_t)d * p.ldy + feat] = __float2half_rn(val);
               else reinterpret_cast<__nv_bfloat16*>(p.Y)[(int64_t)d * p.ldy + feat] = __float2bfloat16_rn(val);
             }
           }
@@ -1083,7 +1095,8 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // bf16 tensor [d2][d1][d0] (d0 contiguous), box [1][box1][64], 128-byte swizzle, zero fill out of bounds
-static int make_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box1) {
+static int make_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t box1,
+                     int f16 = 0) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(MOE_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[3] = {d0, d1, d2};
@@ -1091,7 +1104,7 @@ static int make_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1,
   cuuint32_t box[3] = {(cuuint32_t)BK, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   const cuuint32_t rank = d2 > 0 ? 3 : 2;
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(MOE_ERR_ARG, "cuTensorMapEncodeTiled failed with %d (dims %llu,%llu,%llu box1 %u)", (int)r,
@@ -1149,19 +1162,19 @@ static int launch_tn(const CUtensorMap& tW, const CUtensorMap& tW2, const CUtens
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                              const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                              int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
-                             void* const* peer_base, int n_peers, int64_t expected_rows);
+                             void* const* peer_base, int n_peers, int64_t expected_rows, int dtype);
 
 extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                                 const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
-                                int64_t expected_rows, int K, int N, int E, int32_t* status, void* stream) {
+                                int64_t expected_rows, int K, int N, int E, int dtype, int32_t* status, void* stream) {
   return grouped_gemm_impl(epilogue, A, B, B2, offsets, dst_rows, row_w, Y, ldy, max_rows, K, N, E, status, stream,
-                           nullptr, nullptr, 0, expected_rows);
+                           nullptr, nullptr, 0, expected_rows, dtype);
 }
 
 extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                              const int32_t* row_rank, const int32_t* dst_rows, void* const* peer_base,
                                              int n_peers, int64_t ldy, int64_t max_rows, int64_t expected_rows,
-                                             int K, int N, int E, int32_t* status, void* stream) {
+                                             int K, int N, int E, int dtype, int32_t* status, void* stream) {
   using namespace moe;
   if (!row_rank || !dst_rows || !peer_base) return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: null table");
   if (n_peers < 1 || n_peers > 16) return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: n_peers=%d out of range", n_peers);
@@ -1169,15 +1182,17 @@ extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const
     if (!peer_base[g] || (reinterpret_cast<uintptr_t>(peer_base[g]) & 15))
       return fail(MOE_ERR_ARG, "grouped_gemm_peer_scatter: peer buffer %d null or unaligned", g);
   return grouped_gemm_impl(MOE_GEMM_PLAIN, A, B, nullptr, offsets, dst_rows, nullptr, peer_base[0], ldy, max_rows, K, N, E,
-                           status, stream, row_rank, peer_base, n_peers, expected_rows);
+                           status, stream, row_rank, peer_base, n_peers, expected_rows, dtype);
 }
 
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                              const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                              int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
-                             void* const* peer_base, int n_peers, int64_t expected_rows) {
+                             void* const* peer_base, int n_peers, int64_t expected_rows, int dtype) {
   using namespace moe;
   using namespace moe::gemm;
+  if (dtype != MOE_DTYPE_BF16 && dtype != MOE_DTYPE_F16) return fail(MOE_ERR_ARG, "grouped_gemm: unknown dtype %d", dtype);
+  const int f16 = dtype == MOE_DTYPE_F16;
   // rows the caller expects to be live (<= max_rows, which may be a buffer capacity): steers the tile rule
   const int64_t live_rows = (expected_rows > 0 && expected_rows < max_rows) ? expected_rows : max_rows;
   if (epilogue < 0 || epilogue > 3) return fail(MOE_ERR_ARG, "grouped_gemm: unknown epilogue %d", epilogue);
@@ -1229,17 +1244,18 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
     q.num_n_tiles = gate ? (N + BM - 1) / BM : (N + 2 * BM - 1) / (2 * BM);
     q.num_k_blocks = (K + BK - 1) / BK;
     q.status = status;
+    q.f16 = f16;
     q.row_rank = nullptr;
     for (int g = 0; g < 16; ++g) q.peer_base[g] = nullptr;
     CUtensorMap tW, tW2, tX;
-    rc = make_tmap(&tW, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM);
+    rc = make_tmap(&tW, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM, f16);
     if (rc) return rc;
     tW2 = tW;
     if (gate) {
-      rc = make_tmap(&tW2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM);
+      rc = make_tmap(&tW2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM, f16);
       if (rc) return rc;
     }
-    rc = make_tmap(&tX, A, (uint64_t)K, (uint64_t)max_rows, 0, 64);
+    rc = make_tmap(&tX, A, (uint64_t)K, (uint64_t)max_rows, 0, 64, f16);
     if (rc) return rc;
     const int64_t tiles = (max_rows / tn + E) * q.num_n_tiles;
     int g = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
@@ -1265,18 +1281,19 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   p.num_n_tiles = (N + out_cols - 1) / out_cols;
   p.num_k_blocks = (K + BK - 1) / BK;
   p.status = status;
+  p.f16 = f16;
   p.row_rank = row_rank;
   for (int g = 0; g < 16; ++g) p.peer_base[g] = (peer_base && g < n_peers) ? peer_base[g] : nullptr;
 
   CUtensorMap tA, tB, tB2;
-  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)max_rows, 0, (uint32_t)(pair ? BM : MT * BM));
+  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)max_rows, 0, (uint32_t)(pair ? BM : MT * BM), f16);
   if (rc) return rc;
   const uint32_t b_box_rows = pair ? 128u : (uint32_t)out_cols;   // a CTA of a pair stages 128 N rows
-  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows);
+  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows, f16);
   if (rc) return rc;
   tB2 = tB;
   if (epilogue == MOE_GEMM_SILU_GATE) {
-    rc = make_tmap(&tB2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows);
+    rc = make_tmap(&tB2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows, f16);
     if (rc) return rc;
   }
   int64_t tiles_bound = m_tiles_bound * p.num_n_tiles;

@@ -3,6 +3,7 @@
 // warp-private shared-memory histograms, no host round trip.
 #include "common.cuh"
 
+#include <cuda_fp16.h>
 #include <mutex>
 
 namespace moe {
@@ -151,26 +152,42 @@ gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ pe
 // ------------------------------------------------------------------------------------
 // combine: out[t,:] = shared[t,:] + sum_s Yk[t*k+s,:]   (fp32 sum in slot order, one rounding)
 // ------------------------------------------------------------------------------------
-__device__ __forceinline__ void add_bf16x8(float* acc, const uint4& v) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+// element-pair conversions for the two 16-bit types (F16 = false: bfloat16, true: half)
+template <bool F16>
+__device__ __forceinline__ float2 unpack2(uint32_t u) {
+  if (F16) return __half22float2(*reinterpret_cast<const __half2*>(&u));
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (F16) { __half2 h = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&h); }
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <bool F16>
+__device__ __forceinline__ void add_x8(float* acc, const uint4& v) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float2 f = __bfloat1622float2(h[j]);
+    const float2 f = unpack2<F16>(u[j]);
     acc[2 * j] += f.x;
     acc[2 * j + 1] += f.y;
   }
 }
 
-__device__ __forceinline__ void fma_bf16x8(float* acc, const uint4& v, float w) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+template <bool F16>
+__device__ __forceinline__ void fma_x8(float* acc, const uint4& v, float w) {
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(&v);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float2 f = __bfloat1622float2(h[j]);
+    const float2 f = unpack2<F16>(u[j]);
     acc[2 * j] = fmaf(f.x, w, acc[2 * j]);
     acc[2 * j + 1] = fmaf(f.y, w, acc[2 * j + 1]);
   }
 }
 
+template <bool F16>
 __global__ void __launch_bounds__(256)
 combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, const int32_t* __restrict__ row_of,
                const float* __restrict__ scale, int64_t T, int k, int vec_per_row, uint4* __restrict__ out) {
@@ -185,13 +202,13 @@ combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, c
       const int64_t f = t * k + s;
       const int64_t r = row_of ? (int64_t)row_of[f] : f;
       const uint4 y = __ldg(Yk + r * vec_per_row + v);
-      if (scale) fma_bf16x8(acc, y, scale[f]); else add_bf16x8(acc, y);
+      if (scale) fma_x8<F16>(acc, y, scale[f]); else add_x8<F16>(acc, y);
     }
-    if (shared) add_bf16x8(acc, __ldg(shared + g));
+    if (shared) add_x8<F16>(acc, __ldg(shared + g));
     uint4 o;
-    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+    uint32_t* ou = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    for (int j = 0; j < 4; ++j) ou[j] = pack2<F16>(acc[2 * j], acc[2 * j + 1]);
     out[g] = o;
   }
 }
@@ -199,6 +216,7 @@ combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, c
 // ------------------------------------------------------------------------------------
 // router logits for a small expert count: one warp per token, 8 experts per pass
 // ------------------------------------------------------------------------------------
+template <bool F16>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, int64_t T, int vec_per_row, int E,
                      float* __restrict__ logits) {
@@ -212,21 +230,21 @@ router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, 
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       for (int v = lane; v < vec_per_row; v += 32) {
         const uint4 xv = __ldg(xr + v);
-        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
         float xf[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(xh[j]);
+          const float2 f = unpack2<F16>(xu[j]);
           xf[2 * j] = f.x; xf[2 * j + 1] = f.y;
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (e0 + j < E) {
             const uint4 wv = __ldg(Wr + (int64_t)(e0 + j) * vec_per_row + v);
-            const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const float2 f = __bfloat1622float2(wh[q]);
+              const float2 f = unpack2<F16>(wu[q]);
               acc[j] = fmaf(xf[2 * q], f.x, acc[j]);
               acc[j] = fmaf(xf[2 * q + 1], f.y, acc[j]);
             }
@@ -389,8 +407,9 @@ extern "C" int moe_gather_rows(const void* src, const int32_t* perm, int div, in
 }
 
 extern "C" int moe_combine(const void* Yk, const void* shared, const int32_t* row_of, const float* scale, int64_t T,
-                           int k, int64_t H, void* out, void* stream) {
+                           int k, int64_t H, int dtype, void* out, void* stream) {
   using namespace moe;
+  if (dtype != MOE_DTYPE_BF16 && dtype != MOE_DTYPE_F16) return fail(MOE_ERR_ARG, "combine: unknown dtype %d", dtype);
   if (T < 0 || k < 0 || H < 8 || H % 8) return fail(MOE_ERR_ARG, "combine: bad shape T=%lld k=%d H=%lld", (long long)T, k, (long long)H);
   if (T == 0) return MOE_OK;
   if ((k > 0 && !Yk) || !out) return fail(MOE_ERR_ARG, "combine: null pointer");
@@ -403,17 +422,23 @@ extern "C" int moe_combine(const void* Yk, const void* shared, const int32_t* ro
   int64_t blocks = ceil_div64(total, 256);
   const int64_t cap = (int64_t)dev.sm_count * 8;
   if (blocks > cap) blocks = cap;
-  combine_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint4*>(Yk), reinterpret_cast<const uint4*>(shared), row_of, scale, T, k, (int)(H / 8),
-      reinterpret_cast<uint4*>(out));
+  if (dtype == MOE_DTYPE_F16)
+    combine_kernel<true><<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(Yk), reinterpret_cast<const uint4*>(shared), row_of, scale, T, k, (int)(H / 8),
+        reinterpret_cast<uint4*>(out));
+  else
+    combine_kernel<false><<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(Yk), reinterpret_cast<const uint4*>(shared), row_of, scale, T, k, (int)(H / 8),
+        reinterpret_cast<uint4*>(out));
   MOE_CHECK_LAUNCH("combine_kernel");
   return MOE_OK;
 }
 
-extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, float* logits, int32_t* status,
-                                 void* stream) {
+extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, int dtype, float* logits,
+                                 int32_t* status, void* stream) {
   using namespace moe;
   (void)status;
+  if (dtype != MOE_DTYPE_BF16 && dtype != MOE_DTYPE_F16) return fail(MOE_ERR_ARG, "router_logits: unknown dtype %d", dtype);
   if (T < 0 || H < 8 || H % 8 || E < 1) return fail(MOE_ERR_ARG, "router_logits: bad shape T=%lld H=%d E=%d", (long long)T, H, E);
   if (T == 0) return MOE_OK;
   if (!x || !Wr || !logits) return fail(MOE_ERR_ARG, "router_logits: null pointer");
@@ -424,8 +449,12 @@ extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H
   int64_t blocks = ceil_div64(T, 8);
   const int64_t cap = (int64_t)dev.sm_count * 8;
   if (blocks > cap) blocks = cap;
-  router_logits_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);
+  if (dtype == MOE_DTYPE_F16)
+    router_logits_kernel<true><<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);
+  else
+    router_logits_kernel<false><<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);
   MOE_CHECK_LAUNCH("router_logits_kernel");
   return MOE_OK;
 }

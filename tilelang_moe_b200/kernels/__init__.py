@@ -13,8 +13,8 @@ Everything runs on the CUDA library behind ``include/moe_b200.h``; there is no
 strategy auto-selection between back ends and no CPU path.  Deliberate
 differences from the reference's GPU path, all towards its PyTorch baseline:
 indices are int64 and sorted (value descending, ties lowest index first), the
-router of the fused layer accumulates logits in fp32, and the compute dtype is
-bfloat16.
+router of the fused layer accumulates logits in fp32, and both float16 (the
+reference's default) and bfloat16 are computed natively with fp32 accumulation.
 """
 from __future__ import annotations
 
@@ -54,7 +54,7 @@ def grouped_gemm(X: torch.Tensor, W: torch.Tensor, expert_indices: torch.Tensor,
                  w_layout: str = "EIH") -> torch.Tensor:
     """Y[i] = X[i] @ W[expert_indices[i]].T.
 
-    X (total_tokens, H) bfloat16; W (E, I, H); expert_indices (total_tokens,) int64
+    X (total_tokens, H) bfloat16 or float16; W (E, I, H); expert_indices (total_tokens,) int64
     -> Y (total_tokens, I).  With 2-D expert_indices (T, k) every token row is used
     by its k experts and Y is (T, k, I), without materialising a repeated X on the
     host side.  ``w_layout="EHI"`` accepts the kernel-level layout the reference's
@@ -64,8 +64,8 @@ def grouped_gemm(X: torch.Tensor, W: torch.Tensor, expert_indices: torch.Tensor,
         W = W.transpose(1, 2).contiguous()
     elif w_layout != "EIH":
         raise ValueError("w_layout must be 'EIH' or 'EHI'")
-    if X.dtype != torch.bfloat16 or W.dtype != torch.bfloat16:
-        raise ValueError("grouped_gemm computes in bfloat16")
+    if X.dtype not in _ops.DTYPE_CODE or W.dtype != X.dtype:
+        raise ValueError("grouped_gemm computes in bfloat16 or float16 (X and W of the same type)")
     if expert_indices.dim() not in (1, 2) or expert_indices.shape[0] != X.shape[0]:
         raise ValueError("expert_indices must be (total_tokens,) or (total_tokens, k)")
     E, I, H = W.shape
@@ -89,17 +89,17 @@ class FusedMoETileLang:
     """
 
     def __init__(self, d_hidden: int, d_expert: int, n_routed_experts: int, n_shared_experts: int,
-                 n_experts_per_token: int, batch_size: int, seq_len: int, dtype: torch.dtype = torch.bfloat16,
+                 n_experts_per_token: int, batch_size: int, seq_len: int, dtype: torch.dtype = torch.float16,
                  block_token: int = 128, device: Optional[torch.device] = None):
-        if dtype != torch.bfloat16:
-            raise ValueError("moe_b200 computes in bfloat16")
+        if dtype not in _ops.DTYPE_CODE:
+            raise ValueError("moe_b200 computes in bfloat16 or float16")
         self.d_hidden, self.d_expert = d_hidden, d_expert
         self.n_routed_experts, self.n_shared_experts = n_routed_experts, n_shared_experts
         self.n_experts_per_token = n_experts_per_token
         self.batch_size, self.seq_len = batch_size, seq_len
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.ws = _layer.MoEWorkspace(batch_size * seq_len, n_experts_per_token, d_hidden, d_expert,
-                                      n_routed_experts, d_expert * n_shared_experts, dev)
+                                      n_routed_experts, d_expert * n_shared_experts, dev, dtype)
 
     def forward(self, x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down,
                 logits: Optional[torch.Tensor] = None):

@@ -31,9 +31,10 @@ class MoEWorkspace:
     E: int
     SI: int
     device: torch.device
+    dtype: torch.dtype = torch.bfloat16
 
     def __post_init__(self):
-        dev, bf16 = self.device, torch.bfloat16
+        dev, bf16 = self.device, self.dtype
         n = self.T * self.k
         self.logits = torch.empty(self.T, self.E, dtype=torch.float32, device=dev)
         self.xs = torch.empty(n, self.H, dtype=bf16, device=dev)          # expert-sorted activations
@@ -103,8 +104,8 @@ def moe_forward(x: torch.Tensor, router_weight: Optional[torch.Tensor], shared_g
                 out: Optional[torch.Tensor] = None, return_routing: bool = False):
     """Full layer.  x [..., H] bf16.  Router: fp32 logits (given, or x.Wr^T), softmax over all
     experts, top-k without renormalisation (reference fusedmoe_baseline.py:72-76)."""
-    if x.dtype != torch.bfloat16:
-        raise ValueError("moe_b200 computes in bfloat16; cast the activations and weights")
+    if x.dtype not in ops.DTYPE_CODE:
+        raise ValueError("moe_b200 computes in bfloat16 or float16; cast the activations and weights")
     shape = x.shape
     H = shape[-1]
     x_flat = x.reshape(-1, H)
@@ -113,8 +114,9 @@ def moe_forward(x: torch.Tensor, router_weight: Optional[torch.Tensor], shared_g
     T = x_flat.shape[0]
     E, I, _ = routed_gate.shape
     SI = 0 if shared_gate is None else shared_gate.shape[0]
-    if ws is None or (ws.T, ws.k, ws.H, ws.I, ws.E, ws.SI) != (T, k, H, I, E, SI) or ws.device != x.device:
-        ws = MoEWorkspace(T, k, H, I, E, SI, x.device)
+    if (ws is None or (ws.T, ws.k, ws.H, ws.I, ws.E, ws.SI, ws.dtype) != (T, k, H, I, E, SI, x.dtype)
+            or ws.device != x.device):
+        ws = MoEWorkspace(T, k, H, I, E, SI, x.device, x.dtype)
     if logits is None:
         logits = ops.router_logits(x_flat, router_weight, out=ws.logits)
     scores, idx32 = ops.topk_softmax(logits, k, mode="A", index_dtype=torch.int32)

@@ -20,6 +20,19 @@ GEMM_PLAIN, GEMM_SILU_GATE, GEMM_SCALE_SCATTER, GEMM_PLAIN_F32 = 0, 1, 2, 3
 _MODES = {"B": MODE_B, "A": MODE_A, "A_norenorm": MODE_A, "A_renorm": MODE_A_RENORM,
           0: MODE_B, 1: MODE_A, 2: MODE_A_RENORM}
 
+DTYPE_CODE = {torch.bfloat16: 0, torch.float16: 1}   # MOE_DTYPE_* of include/moe_b200.h
+
+
+def _dtype_code(*ts: torch.Tensor) -> int:
+    dt = ts[0].dtype
+    if dt not in DTYPE_CODE:
+        raise ValueError("moe_b200 computes in bfloat16 or float16")
+    for t in ts[1:]:
+        if t is not None and t.dtype != dt:
+            raise ValueError(f"mixed element types: {dt} and {t.dtype}")
+    return DTYPE_CODE[dt]
+
+
 _DEBUG = os.environ.get("MOE_B200_DEBUG", "0") not in ("", "0")
 _status = {}
 _STATUS_TEXT = {1: "expert id outside [0,E)", 2: "a bounded barrier wait expired", 3: "internal selection count mismatch"}
@@ -129,8 +142,8 @@ def gather_rows(src: torch.Tensor, perm: Optional[torch.Tensor], div: int = 1, o
                 w_src: Optional[torch.Tensor] = None, w_out: Optional[torch.Tensor] = None, n_rows: Optional[int] = None):
     """out[p] = src[perm[p] // div]; optionally w_out[p] = w_src[perm[p]]."""
     _need_cuda(src, perm)
-    if src.dim() != 2 or src.dtype != torch.bfloat16 or not src.is_contiguous():
-        raise ValueError("src must be a contiguous 2-D bfloat16 tensor")
+    if src.dim() != 2 or src.dtype not in DTYPE_CODE or not src.is_contiguous():
+        raise ValueError("src must be a contiguous 2-D bfloat16 / float16 tensor")
     n = (perm.numel() if perm is not None else src.shape[0]) if n_rows is None else n_rows
     cols = src.shape[1]
     if out is None:
@@ -156,8 +169,7 @@ def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets
     """Expert GEMM over expert-sorted rows.  A [rows,K] bf16, B (and B2) [E,N,K] bf16,
     offsets int32 [E+1] on the device.  See include/moe_b200.h for the epilogues."""
     _need_cuda(A, B, offsets)
-    if A.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
-        raise ValueError("A and B must be bfloat16")
+    dt = _dtype_code(A, B, B2)
     if A.dim() != 2 or B.dim() != 3 or not A.is_contiguous() or not B.is_contiguous():
         raise ValueError("A must be contiguous [rows,K], B contiguous [E,N,K]")
     rows, K = A.shape
@@ -171,11 +183,11 @@ def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets
     if max_rows is None:
         max_rows = rows
     if out is None:
-        odt = torch.float32 if epilogue == GEMM_PLAIN_F32 else torch.bfloat16
+        odt = torch.float32 if epilogue == GEMM_PLAIN_F32 else A.dtype
         out = torch.empty(rows if out_rows is None else out_rows, N, dtype=odt, device=A.device)
     with torch.cuda.device(A.device):
         rc = _lib.load().moe_grouped_gemm(epilogue, _ptr(A), _ptr(B), _ptr(B2), _ptr(offsets), _ptr(dst_rows),
-                                          _ptr(row_w), _ptr(out), out.stride(0), max_rows, expected_rows, K, N, E,
+                                          _ptr(row_w), _ptr(out), out.stride(0), max_rows, expected_rows, K, N, E, dt,
                                           _ptr(status_buffer(A.device)), _stream())
     _lib.check(rc, "moe_grouped_gemm")
     _after(A.device)
@@ -191,28 +203,53 @@ def combine(Yk: torch.Tensor, k: int, shared: Optional[torch.Tensor] = None, out
     n, H = Yk.shape
     if T is None:
         T = (row_of.numel() if row_of is not None else n) // k
+    dt = _dtype_code(Yk, shared)
     if out is None:
-        out = torch.empty(T, H, dtype=torch.bfloat16, device=Yk.device)
+        out = torch.empty(T, H, dtype=Yk.dtype, device=Yk.device)
     with torch.cuda.device(Yk.device):
-        rc = _lib.load().moe_combine(_ptr(Yk), _ptr(shared), _ptr(row_of), _ptr(scale), T, k, H, _ptr(out), _stream())
+        rc = _lib.load().moe_combine(_ptr(Yk), _ptr(shared), _ptr(row_of), _ptr(scale), T, k, H, dt, _ptr(out), _stream())
     _lib.check(rc, "moe_combine")
     return out
 
 
+_dense_offsets = {}
+
+
+def _offsets_0_T(T: int, device: torch.device) -> torch.Tensor:
+    """Device tensor [0, T] (int32): the group table of a dense, single-group GEMM."""
+    key = (T, device.index)
+    t = _dense_offsets.get(key)
+    if t is None:
+        t = torch.tensor([0, T], dtype=torch.int32, device=device)
+        _dense_offsets[key] = t
+    return t
+
+
 def router_logits(x: torch.Tensor, router_weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """fp32 logits [T,E] = x [T,H] . Wr[E,H]^T from bf16 inputs, fp32 accumulate."""
+    """fp32 logits [T,E] = x [T,H] . Wr[E,H]^T from 16-bit inputs, fp32 accumulate.
+    Few experts (E < 32): one warp per token on CUDA cores.  Otherwise the tcgen05 GEMM with fp32 output
+    (the router weight is one dense group [1,E,H])."""
     _need_cuda(x, router_weight)
-    if x.dtype != torch.bfloat16 or router_weight.dtype != torch.bfloat16:
-        raise ValueError("router inputs must be bfloat16")
+    dt = _dtype_code(x, router_weight)
     T, H = x.shape
     E = router_weight.shape[0]
     if out is None:
         out = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    x = x.contiguous()
+    router_weight = router_weight.contiguous()
+    if E >= 32 and E % 8 == 0 and T > 0:
+        return grouped_gemm_sorted(GEMM_PLAIN_F32, x, router_weight.unsqueeze(0), _offsets_0_T(T, x.device), out=out)
     with torch.cuda.device(x.device):
-        rc = _lib.load().moe_router_logits(_ptr(x.contiguous()), _ptr(router_weight.contiguous()), T, H, E, _ptr(out),
+        rc = _lib.load().moe_router_logits(_ptr(x), _ptr(router_weight), T, H, E, dt, _ptr(out),
                                            _ptr(status_buffer(x.device)), _stream())
     _lib.check(rc, "moe_router_logits")
     return out
+
+
+def router_topk_softmax(x: torch.Tensor, router_weight: torch.Tensor, k: int, mode="B"):
+    """Router GEMM followed by top-k + softmax (reference kernels/router_gemm_topk_softmax.py computes the same
+    pair in one kernel; here the [T,E] fp32 logits make one round trip through L2)."""
+    return topk_softmax(router_logits(x, router_weight), k, mode=mode)
 
 
 def ep_regroup(recv_counts: torch.Tensor, n_recv_bound: int):
@@ -275,6 +312,7 @@ def grouped_gemm_peer_scatter(A: torch.Tensor, B: torch.Tensor, offsets: torch.T
     with torch.cuda.device(A.device):
         rc = _lib.load().moe_grouped_gemm_peer_scatter(_ptr(A), _ptr(B), _ptr(offsets), _ptr(row_rank), _ptr(dst_rows),
                                                        arr, len(arr), ldy, rows if max_rows is None else max_rows,
-                                                       expected_rows, K, N, E, _ptr(status_buffer(A.device)), _stream())
+                                                       expected_rows, K, N, E, _dtype_code(A, B),
+                                                       _ptr(status_buffer(A.device)), _stream())
     _lib.check(rc, "moe_grouped_gemm_peer_scatter")
     _after(A.device)
