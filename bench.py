@@ -223,7 +223,34 @@ def run_ours(args, cfg):
     x_cpu, logits_cpu = make_inputs(cfg)
     peaks = _peaks()
 
-    if world == 1:
+    if world == 1 and cfg["S"] > 0:
+        # full shared + routed layer through the reference-named API (router GEMM included)
+        from tilelang_moe_b200 import kernels
+        S = cfg["S"]
+        xc, wc = kernels.generate_fusedmoe_inputs(1, T, H, I, E, S, k, dtype=torch.bfloat16, device="cpu", seed=42)
+        names = ["router_weight", "shared_gate", "shared_up", "shared_down", "routed_gate", "routed_up", "routed_down"]
+        wd = [wc[n].to(dev) for n in names]
+        x = xc.to(dev)
+        mod = kernels.FusedMoETileLang(H, I, E, S, k, 1, T, dtype=torch.bfloat16)
+        replay = mod.capture(x, *wd) if args.graph else None
+
+        def step(timers=None):
+            return replay() if replay is not None else mod.forward(x, *wd)
+
+        x_pin = xc.pin_memory()
+        out_pin = torch.empty(1, T, H, dtype=torch.bfloat16).pin_memory()
+
+        def step_e2e():
+            x.copy_(x_pin, non_blocking=True)
+            out_pin.copy_(step(), non_blocking=True)
+
+        launches_per_step = 11   # router GEMV, topk, 3 x histogram, gather, up, down, shared up, shared down, combine
+        tokens_per_step = T
+        h2d, d2h = x_pin.numel() * 2, out_pin.numel() * 2
+        parallelism = "1 GPU" + (", whole layer replayed as one CUDA graph" if args.graph else ", eager launches")
+        imbalance = None
+        x_cpu, logits_cpu = xc.view(T, H), None
+    elif world == 1:
         Wg, Wu, Wd = make_weights(cfg, dev)
         ws = layer.MoEWorkspace(T, k, H, I, E, 0, dev)
         x = x_cpu.to(dev)
@@ -321,13 +348,30 @@ def run_ours(args, cfg):
                     "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "traffic": None,
                     "ms_per_launch": stage_ms["up_gemm"]}
 
+    if roofline is None and cfg["S"] > 0:
+        flops = 2.0 * T * H * E + (T * k + T * cfg["S"]) * 6.0 * H * I
+        achieved = flops / (ms / args.steps * 1e-3) / 1e12
+        roofline = {"kernel": "whole layer (router GEMV, top-k, permutation, 4 tcgen05 GEMMs, combine)", "bound": "tensor",
+                    "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                    "peak_source": peaks["source"] + " (burst cuBLAS bf16)", "traffic": None,
+                    "note": "19.4 GFLOP in ~10 launches: launch latency, not the tensor pipe, bounds this size"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
     cpu_v, cpu_desc = None, None
-    if world == 1 and not args.no_cpu:
+    if world == 1 and cfg["S"] > 0 and not args.no_cpu:
+        from oracle import moe_oracle as O
+        torch.set_num_threads(os.cpu_count() or 1)
+        ws_cpu = [wc[n] for n in names]
+        O.fusedmoe(xc, *ws_cpu, k, compute_dtype=torch.bfloat16)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            O.fusedmoe(xc, *ws_cpu, k, compute_dtype=torch.bfloat16)
+        cpu_v = T / ((time.perf_counter() - t0) / 3)
+        cpu_desc = "oracle port (torch CPU, bf16) of the whole layer, mean of 3 full passes"
+    elif world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
 
         def weights_for(e):
@@ -432,6 +476,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
+    ap.add_argument("--graph", action="store_true", help="c3: replay the layer as one CUDA graph")
     ap.add_argument("--only", default="", help="router workload: comma-separated point names to run")
     ap.add_argument("--balanced", action="store_true", help="diagnostic: uniform expert load instead of Zipf(1.1)")
     args = ap.parse_args()

@@ -79,3 +79,19 @@ def test_float16_layer_default_dtype_of_the_reference(cuda, lib):
     torch.testing.assert_close(y.float().cpu(), ref, rtol=RTOL, atol=ATOL)
     x2, w2 = kernels.generate_fusedmoe_inputs(1, 8, 64, 32, 4, 1, 2, device="cuda")
     assert x2.dtype == torch.float16 and w2["routed_down"].shape == (4, 64, 32)
+
+
+def test_graph_replay_matches_eager(cuda, lib):
+    x, w = O.make_fusedmoe_inputs(1, 256, 512, 256, 8, 1, 2, dtype=torch.bfloat16, seed=11)
+    m = kernels.FusedMoETileLang(512, 256, 8, 1, 2, 1, 256, dtype=torch.bfloat16)
+    xd = x.to(cuda)
+    wd = [w[n].to(cuda) for n in NAMES]
+    eager = m.forward(xd, *wd).clone()
+    run = m.capture(xd, *wd)
+    assert torch.equal(run(), eager)
+    # new activations written in place into the static input
+    x2 = torch.randn(1, 256, 512, generator=torch.Generator().manual_seed(5)).bfloat16()
+    xd.copy_(x2.to(cuda))
+    got = run().clone()
+    assert torch.equal(got, m.forward(xd, *wd))
+    ops.check_status(cuda)

@@ -43,14 +43,23 @@ route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, con
   const int64_t u = (int64_t)blockIdx.x * RWPB + w;
   const int64_t first = u * RUNIT;
   if (first >= n) return;
+  // all loads of the unit are issued before the first one is consumed (the walk itself is latency-bound)
+  int ev[RUNIT / 32];
+#pragma unroll
+  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+    const int64_t i = first + sidx * 32 + lane;
+    ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E) : -2;
+  }
   for (int e = lane; e < E; e += 32) wh[e] = 0;
   __syncwarp();
-  const int64_t last = first + RUNIT < n ? first + RUNIT : n;
-  for (int64_t i = first + lane; i < last; i += 32) {
-    const int e = load_id(ids, is64, i, id_map, E);
-    if (e >= 0 && e < E) atomicAdd(&wh[e], 1);
-    else if (status) status[0] = ST_BAD_EXPERT_ID;
+  bool bad = false;
+#pragma unroll
+  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+    const int e = ev[sidx];
+    if (e >= 0) atomicAdd(&wh[e], 1);
+    else if (e == -1) bad = true;
   }
+  if (bad && status) status[0] = ST_BAD_EXPERT_ID;
   __syncwarp();
   for (int e = lane; e < E; e += 32) unit_counts[u * E + e] = wh[e];
 }
@@ -107,13 +116,19 @@ route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, c
   const int64_t u = (int64_t)blockIdx.x * RWPB + w;
   const int64_t first = u * RUNIT;
   if (first >= n) return;
+  int ev[RUNIT / 32];
+#pragma unroll
+  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+    const int64_t i = first + sidx * 32 + lane;
+    ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E) : -2;
+  }
   for (int e = lane; e < E; e += 32) wh[e] = unit_base[u * E + e];
   __syncwarp();
-  const int64_t last = first + RUNIT < n ? first + RUNIT : n;
-  for (int64_t i0 = first; i0 < last; i0 += 32) {
-    const int64_t i = i0 + lane;
-    int e = i < last ? load_id(ids, is64, i, id_map, E) : -1;
-    const bool valid = e >= 0 && e < E;
+#pragma unroll
+  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+    const int64_t i = first + sidx * 32 + lane;
+    const int e = ev[sidx];
+    const bool valid = e >= 0;
     // lanes without a valid id get a private group so that they match nobody
     const unsigned grp = __match_any_sync(0xFFFFFFFFu, valid ? (unsigned)e : (0x80000000u | (unsigned)lane));
     const int r = __popc(grp & lt_mask);
@@ -214,52 +229,53 @@ combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, c
 }
 
 // ------------------------------------------------------------------------------------
-// router logits for a small expert count: one warp per token, 8 experts per pass
+// router logits for a small expert count: the router weight [E,H] is staged once per CTA in shared memory,
+// then each warp takes tokens in turn: one pass over the token row, all E dot products in registers
 // ------------------------------------------------------------------------------------
-template <bool F16>
+template <bool F16, int EMAX>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, int64_t T, int vec_per_row, int E,
                      float* __restrict__ logits) {
+  extern __shared__ uint4 wsh[];   // [E][vec_per_row]
   const int lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < E * vec_per_row; i += 256) wsh[i] = __ldg(Wr + i);
+  __syncthreads();
   const int64_t nwarps = (int64_t)gridDim.x * 8;
   for (int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); t < T; t += nwarps) {
     const uint4* xr = x + t * vec_per_row;
-    for (int e0 = 0; e0 < E; e0 += 8) {
-      float acc[8];
+    float acc[EMAX];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int v = lane; v < vec_per_row; v += 32) {
-        const uint4 xv = __ldg(xr + v);
-        const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
-        float xf[8];
+    for (int j = 0; j < EMAX; ++j) acc[j] = 0.f;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      const uint4 xv = __ldg(xr + v);
+      const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
+      float xf[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = unpack2<F16>(xu[j]);
-          xf[2 * j] = f.x; xf[2 * j + 1] = f.y;
-        }
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack2<F16>(xu[j]);
+        xf[2 * j] = f.x; xf[2 * j + 1] = f.y;
+      }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (e0 + j < E) {
-            const uint4 wv = __ldg(Wr + (int64_t)(e0 + j) * vec_per_row + v);
-            const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      for (int j = 0; j < EMAX; ++j) {
+        if (j < E) {
+          const uint4 wv = wsh[j * vec_per_row + v];
+          const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float2 f = unpack2<F16>(wu[q]);
-              acc[j] = fmaf(xf[2 * q], f.x, acc[j]);
-              acc[j] = fmaf(xf[2 * q + 1], f.y, acc[j]);
-            }
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = unpack2<F16>(wu[q]);
+            acc[j] = fmaf(xf[2 * q], f.x, acc[j]);
+            acc[j] = fmaf(xf[2 * q + 1], f.y, acc[j]);
           }
         }
       }
+    }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float s = warp_sum(acc[j]);
-        if (lane == 0 && e0 + j < E) logits[t * E + e0 + j] = s;
-      }
+    for (int j = 0; j < EMAX; ++j) {
+      const float sum = warp_sum(acc[j]);
+      if (lane == 0 && j < E) logits[t * E + j] = sum;
     }
   }
 }
-
 
 // ------------------------------------------------------------------------------------
 // expert-parallel regroup table
@@ -446,15 +462,23 @@ extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H
   DeviceInfo dev;
   int rc = current_device_info(&dev);
   if (rc) return rc;
-  int64_t blocks = ceil_div64(T, 8);
-  const int64_t cap = (int64_t)dev.sm_count * 8;
-  if (blocks > cap) blocks = cap;
-  if (dtype == MOE_DTYPE_F16)
-    router_logits_kernel<true><<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);
-  else
-    router_logits_kernel<false><<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);
+  // one CTA per SM at most: every CTA stages the whole router weight
+  if (E > 32) return fail(MOE_ERR_UNSUPPORTED, "router_logits: E=%d > 32 goes through moe_grouped_gemm (MOE_GEMM_PLAIN_F32)", E);
+  const size_t smem = (size_t)E * H * 2;
+  if (smem > 200 * 1024) return fail(MOE_ERR_UNSUPPORTED, "router_logits: E*H=%lld does not fit shared memory", (long long)E * H);
+  int64_t blocks = ceil_div64(T, 16);
+  if (blocks > dev.sm_count) blocks = dev.sm_count;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define MOE_RL_LAUNCH(F16_, EMAX_)                                                                                       \
+  do {                                                                                                                   \
+    if (smem > 48 * 1024)                                                                                                \
+      MOE_CUDA_CHECK(cudaFuncSetAttribute(router_logits_kernel<F16_, EMAX_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    router_logits_kernel<F16_, EMAX_><<<(unsigned)blocks, 256, smem, st>>>(                                              \
+        reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);                     \
+  } while (0)
+  if (dtype == MOE_DTYPE_F16) { if (E <= 8) MOE_RL_LAUNCH(true, 8); else if (E <= 16) MOE_RL_LAUNCH(true, 16); else MOE_RL_LAUNCH(true, 32); }
+  else { if (E <= 8) MOE_RL_LAUNCH(false, 8); else if (E <= 16) MOE_RL_LAUNCH(false, 16); else MOE_RL_LAUNCH(false, 32); }
+#undef MOE_RL_LAUNCH
   MOE_CHECK_LAUNCH("router_logits_kernel");
   return MOE_OK;
 }

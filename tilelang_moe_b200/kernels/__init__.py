@@ -109,6 +109,33 @@ class FusedMoETileLang:
 
     __call__ = forward
 
+    def capture(self, x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down,
+                logits: Optional[torch.Tensor] = None, warmup: int = 2):
+        """Record the whole forward (about a dozen launches, no host synchronisation anywhere) into a CUDA graph.
+
+        The tensors passed here become the graph's static inputs: write new activations into ``x`` (and
+        ``logits``) in place, call the returned function, read the returned output tensor.  Small layers are
+        bound by launch latency rather than by the kernels; replaying one graph removes it (the reference gets
+        a similar effect from its two-stream variant, kernels/fusedmoe_tilelang.py:428-553)."""
+        args = (x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down)
+        side = torch.cuda.Stream(device=x.device)
+        side.wait_stream(torch.cuda.current_stream(x.device))
+        with torch.cuda.stream(side):
+            for _ in range(max(warmup, 1)):      # first calls set kernel attributes and build cached tables
+                self.forward(*args, logits=logits)
+        torch.cuda.current_stream(x.device).wait_stream(side)
+        torch.cuda.synchronize(x.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.forward(*args, logits=logits)
+
+        def replay():
+            graph.replay()
+            return out
+
+        replay.graph, replay.output = graph, out
+        return replay
+
 
 FusedMoE = FusedMoETileLang
 _layer_cache: Dict[tuple, FusedMoETileLang] = {}

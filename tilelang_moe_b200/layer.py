@@ -50,6 +50,18 @@ class MoEWorkspace:
         self.out = torch.empty(self.T, self.H, dtype=bf16, device=dev)
 
 
+_side_streams = {}
+
+
+def _side_stream(device: torch.device) -> torch.cuda.Stream:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _side_streams.get(key)
+    if st is None:
+        st = torch.cuda.Stream(device=device)
+        _side_streams[key] = st
+    return st
+
+
 class _Stage:
     """Records a CUDA event pair around a stage when a timers dict is given (else does nothing)."""
 
@@ -71,7 +83,7 @@ class _Stage:
 def routed_forward(x_flat: torch.Tensor, scores: torch.Tensor, idx32: torch.Tensor, routed_gate: torch.Tensor,
                    routed_up: torch.Tensor, routed_down: torch.Tensor, ws: MoEWorkspace,
                    shared_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                   timers: Optional[dict] = None) -> torch.Tensor:
+                   timers: Optional[dict] = None, shared_ready: Optional[torch.cuda.Event] = None) -> torch.Tensor:
     """Routed experts + combine for routing already decided (scores fp32 [T,k], idx32 int32 [T,k]).
     ``timers``: optional dict that receives a CUDA event pair per stage."""
     E = routed_gate.shape[0]
@@ -85,6 +97,8 @@ def routed_forward(x_flat: torch.Tensor, scores: torch.Tensor, idx32: torch.Tens
     with _Stage(timers, "down_gemm"):
         ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, ws.act, routed_down, offsets, dst_rows=perm, row_w=ws.ws,
                                 out=ws.yk)
+    if shared_ready is not None:      # the shared expert ran on another stream: join before it is read
+        torch.cuda.current_stream(x_flat.device).wait_event(shared_ready)
     with _Stage(timers, "combine"):
         y = ops.combine(ws.yk, k, shared=shared_out, out=ws.out if out is None else out)
     return y
@@ -117,12 +131,25 @@ def moe_forward(x: torch.Tensor, router_weight: Optional[torch.Tensor], shared_g
     if (ws is None or (ws.T, ws.k, ws.H, ws.I, ws.E, ws.SI, ws.dtype) != (T, k, H, I, E, SI, x.dtype)
             or ws.device != x.device):
         ws = MoEWorkspace(T, k, H, I, E, SI, x.device, x.dtype)
+    shared_out, shared_ready = None, None
+    if SI > 0:
+        # The shared expert depends on x only: it runs on a second stream beside router -> permutation -> routed
+        # GEMMs and is joined before the combine (reference kernels/fusedmoe_tilelang.py:428-553 does the same with
+        # its two kernels).  Under graph capture the fork / join become parallel branches of the graph.
+        cur = torch.cuda.current_stream(x.device)
+        side = _side_stream(x.device)
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            shared_out = shared_forward(x_flat, shared_gate, shared_up, shared_down, ws)
+            shared_ready = torch.cuda.Event()
+            shared_ready.record(side)
     if logits is None:
         logits = ops.router_logits(x_flat, router_weight, out=ws.logits)
     scores, idx32 = ops.topk_softmax(logits, k, mode="A", index_dtype=torch.int32)
-    shared_out = shared_forward(x_flat, shared_gate, shared_up, shared_down, ws) if SI > 0 else None
     y = routed_forward(x_flat, scores, idx32, routed_gate, routed_up, routed_down, ws, shared_out=shared_out,
-                       out=None if out is None else out.view(T, H))
+                       out=None if out is None else out.view(T, H), shared_ready=shared_ready)
     y = y.view(*shape)
     if return_routing:
         return y, scores, idx32
