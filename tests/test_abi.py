@@ -32,7 +32,8 @@ def test_version_and_error_channel(lib):
     assert rc == -1 and b"multiples of 8" in lib.moe_last_error()
     rc = lib.moe_route_histogram(None, 1, 10, 4, None, None, None, None, None, None, 0, None, None)
     assert rc == -1
-    assert lib.moe_route_histogram_workspace(2048, 8) == 2 * 8 * 4
+    assert lib.moe_route_histogram_workspace(2048, 8) == 16 * 8 * 4          # small inputs: units of 128 ids
+    assert lib.moe_route_histogram_workspace(65536, 256) == 64 * 256 * 4     # large inputs: units of 1024 ids
     assert lib.moe_route_histogram_workspace(0, 8) == 0
 
 

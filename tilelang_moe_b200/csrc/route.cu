@@ -17,7 +17,9 @@ namespace moe {
 // earlier units; (3) every warp walks its unit again in order and hands out positions,
 // which makes the permutation the stable argsort of the ids.
 // ------------------------------------------------------------------------------------
-constexpr int RUNIT = 1024;        // entries per warp
+constexpr int RUNIT = 1024;        // entries per warp (large inputs)
+constexpr int RUNIT_SMALL = 128;   // entries per warp when the whole input is small: more warps, shorter serial walks
+constexpr int64_t RSMALL_MAX = 16384;
 constexpr int RWPB = 8;            // warps per CTA in the count / scatter kernels
 
 // Expert id of flat entry i; with an id_map (int32 [E]) the id is translated, e.g. to the
@@ -34,6 +36,7 @@ __device__ __forceinline__ int load_id(const void* ids, int is64, int64_t i, con
   return id_map ? id_map[e] : e;
 }
 
+template <int UNIT>
 __global__ void __launch_bounds__(RWPB * 32)
 route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ id_map,
                    int32_t* __restrict__ unit_counts, int32_t* __restrict__ status) {
@@ -41,12 +44,12 @@ route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, con
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   int32_t* wh = sh + (size_t)w * E;
   const int64_t u = (int64_t)blockIdx.x * RWPB + w;
-  const int64_t first = u * RUNIT;
+  const int64_t first = u * UNIT;
   if (first >= n) return;
   // all loads of the unit are issued before the first one is consumed (the walk itself is latency-bound)
-  int ev[RUNIT / 32];
+  int ev[UNIT / 32];
 #pragma unroll
-  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+  for (int sidx = 0; sidx < UNIT / 32; ++sidx) {
     const int64_t i = first + sidx * 32 + lane;
     ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E) : -2;
   }
@@ -54,7 +57,7 @@ route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, con
   __syncwarp();
   bool bad = false;
 #pragma unroll
-  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+  for (int sidx = 0; sidx < UNIT / 32; ++sidx) {
     const int e = ev[sidx];
     if (e >= 0) atomicAdd(&wh[e], 1);
     else if (e == -1) bad = true;
@@ -106,6 +109,7 @@ route_scan_kernel(int32_t* __restrict__ unit_counts, int64_t n_units, int E, int
   if (tid == 0) offsets[E] = carry_s;
 }
 
+template <int UNIT>
 __global__ void __launch_bounds__(RWPB * 32)
 route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ id_map,
                      const int32_t* __restrict__ unit_base, int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
@@ -114,18 +118,18 @@ route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, c
   const unsigned lt_mask = (1u << lane) - 1u;
   int32_t* wh = sh + (size_t)w * E;
   const int64_t u = (int64_t)blockIdx.x * RWPB + w;
-  const int64_t first = u * RUNIT;
+  const int64_t first = u * UNIT;
   if (first >= n) return;
-  int ev[RUNIT / 32];
+  int ev[UNIT / 32];
 #pragma unroll
-  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+  for (int sidx = 0; sidx < UNIT / 32; ++sidx) {
     const int64_t i = first + sidx * 32 + lane;
     ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E) : -2;
   }
   for (int e = lane; e < E; e += 32) wh[e] = unit_base[u * E + e];
   __syncwarp();
 #pragma unroll
-  for (int sidx = 0; sidx < RUNIT / 32; ++sidx) {
+  for (int sidx = 0; sidx < UNIT / 32; ++sidx) {
     const int64_t i = first + sidx * 32 + lane;
     const int e = ev[sidx];
     const bool valid = e >= 0;
@@ -364,7 +368,7 @@ ep_regroup_kernel(const int32_t* __restrict__ cnt, int G, int El, int32_t* __res
 // ====================================================================================
 extern "C" size_t moe_route_histogram_workspace(int64_t n, int E) {
   if (n <= 0 || E <= 0) return 0;
-  const int64_t units = moe::ceil_div64(n, moe::RUNIT);
+  const int64_t units = moe::ceil_div64(n, n <= moe::RSMALL_MAX ? moe::RUNIT_SMALL : moe::RUNIT);
   return (size_t)units * (size_t)E * sizeof(int32_t);
 }
 
@@ -380,22 +384,27 @@ extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64
   const size_t need = moe_route_histogram_workspace(n, E);
   if (need > 0 && (!ws || ws_bytes < need)) return fail(MOE_ERR_WORKSPACE, "route_histogram: workspace %zu < %zu", ws_bytes, need);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int64_t units = ceil_div64(n, RUNIT);
+  const bool small = n <= RSMALL_MAX;
+  const int64_t units = ceil_div64(n, small ? RUNIT_SMALL : RUNIT);
   const size_t smem = (size_t)RWPB * E * 4;
   int32_t* unit_counts = reinterpret_cast<int32_t*>(ws);
   if (smem > 48 * 1024) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_count_kernel<RUNIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_scatter_kernel<RUNIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_count_kernel<RUNIT_SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_scatter_kernel<RUNIT_SMALL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
   const unsigned blocks = (unsigned)ceil_div64(units, RWPB);
   if (units > 0) {
-    route_count_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
+    if (small) route_count_kernel<RUNIT_SMALL><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
+    else route_count_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
     MOE_CHECK_LAUNCH("route_count_kernel");
   }
   route_scan_kernel<<<1, 1024, 0, st>>>(unit_counts, units, E, counts, offsets);
   MOE_CHECK_LAUNCH("route_scan_kernel");
   if (units > 0 && (perm || inv)) {
-    route_scatter_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
+    if (small) route_scatter_kernel<RUNIT_SMALL><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
+    else route_scatter_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
     MOE_CHECK_LAUNCH("route_scatter_kernel");
   }
   return MOE_OK;
@@ -674,20 +683,20 @@ extern "C" int moe_route_histogram_static(const void* topk_idx, int idx_is_int64
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)RWPB * E * 4;
   if (smem > 48 * 1024) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_count_kernel<RUNIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(route_scatter_kernel<RUNIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
   const unsigned blocks = (unsigned)ceil_div64(units, RWPB);
   // Nothing in the array has to start at zero: the count kernel writes every entry of the
   // units x E table it will later read, so whatever an earlier call left behind is overwritten.
   if (units > 0) {
-    route_count_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
+    route_count_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
     MOE_CHECK_LAUNCH("route_count_kernel");
   }
   route_scan_kernel<<<1, 1024, 0, st>>>(unit_counts, units, E, counts, offsets);
   MOE_CHECK_LAUNCH("route_scan_kernel");
   if (units > 0 && (perm || inv)) {
-    route_scatter_kernel<<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
+    route_scatter_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
     MOE_CHECK_LAUNCH("route_scatter_kernel");
   }
   return MOE_OK;
