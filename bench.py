@@ -54,49 +54,78 @@ def _peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons through NVML (read-only queries) every few milliseconds
+    while the timed region runs; falls back to polling nvidia-smi."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.max_mhz, self._stop, self._thread, self._nvml, self.proc = None, threading.Event(), None, None, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
+            import pynvml
+            pynvml.nvmlInit()
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it is a plain index list
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            phys = self.index
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                phys = int(vis.split(",")[self.index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._nvml = None
+            self._start_smi()
+
+    def _loop(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for name, bit in self.REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def _start_smi(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "50",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read_smi, daemon=True).start()
         except OSError:
             self.proc = None
 
-    def _read(self):
+    def _read_smi(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        for r in self.rows:
+            c = [v.strip() for v in line.split(",")]
             try:
-                sm.append(float(r[1])); mx.append(float(r[2]))
+                self.samples.append(float(c[0]))
+                self.max_mhz = float(c[1])
             except (ValueError, IndexError):
                 continue
-            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
-                              ("sw_power_cap", 8)):
-                if len(r) > col and r[col].lower().startswith("active"):
-                    reasons.add(name)
-        # the busiest samples are the ones under load: median of the upper half by power would need power;
-        # clocks rise under load on this part, so report the median of all samples taken in the region
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+            for (name, _), v in zip(self.REASONS, c[2:6]):
+                if v.lower().startswith("active"):
+                    self.reasons.add(name)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1)
+        if self.proc is not None:
+            self.proc.terminate()
+        sm = self.samples
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz, "samples": len(sm),
+                "reasons": sorted(self.reasons), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------------------- inputs
@@ -183,7 +212,7 @@ def run_reference_arm(args, cfg):
             cache[e] = tuple((torch.randn(*s, generator=g) * 0.02).bfloat16() for s in ((I, H), (I, H), (H, I)))
         return cache[e]
 
-    target = max(512, min(4096, cfg["T"] * cfg["k"]))
+    target = max(512, min(12288, cfg["T"] * cfg["k"]))   # bounded: CPU weight generation costs ~0.3 s per expert
     for _ in range(args.warmup):
         cpu_sample(cfg, x, logits, weights_for, target_rows=256)
     vals, desc = [], ""
@@ -343,9 +372,16 @@ def run_ours(args, cfg):
         flops = 2.0 * rows * H * (2 * I)
         achieved = flops / (stage_ms["up_gemm"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
-        roofline = {"kernel": "grouped_gemm_kernel<256,SILU_GATE> (up GEMM, tcgen05)", "bound": "tensor",
+        # DRAM traffic per launch: ncu capture of the c5_shard8 workload (32 experts, 8192 rows: 2.076 GB read +
+        # 0.031 GB written, profiles/grouped_gemm_kernel_c5_shard8.md), which is weights once + A once + output once;
+        # it grows with the experts touched and the rows, so it is scaled by both to this launch
+        per_expert = 2 * I * H * 2 * 1.04
+        traffic = (E if world == 1 else E / world) * per_expert + rows * (H + I) * 2
+        roofline = {"kernel": "grouped_gemm_kernel<1,256,SILU_GATE> (up GEMM, tcgen05)", "bound": "tensor",
                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "traffic": None,
+                    "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "traffic": traffic,
+                    "traffic_source": "ncu capture of c5_shard8 scaled by experts and rows",
+                    "hbm_frac_of_measured": traffic / (stage_ms["up_gemm"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
                     "ms_per_launch": stage_ms["up_gemm"]}
 
     if roofline is None and cfg["S"] > 0:
@@ -377,7 +413,9 @@ def run_ours(args, cfg):
         def weights_for(e):
             return Wg[e].cpu(), Wu[e].cpu(), Wd[e].cpu()
 
-        cpu_v, cpu_desc = cpu_sample(cfg, x_cpu, logits_cpu, weights_for, target_rows=2048 if T * k > 4096 else T * k)
+        # the whole batch: every expert's weights are copied back from the GPU one expert at a time (outside the
+        # timed part), so the CPU computes exactly the layer the GPU computed
+        cpu_v, cpu_desc = cpu_sample(cfg, x_cpu, logits_cpu, weights_for, target_rows=T * k)
 
     value = tokens_per_step * args.steps / (ms * 1e-3)
     line = {
@@ -469,7 +507,7 @@ def run_router(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router"])
