@@ -154,3 +154,26 @@ def test_router_gemm_then_topk_like_the_reference_fusion_test(cuda, lib, H, E, K
     torch.testing.assert_close(s.cpu(), s_own, rtol=RTOL, atol=1e-30)
     d = float((lg.cpu() - ref_logits).abs().max())
     torch.testing.assert_close(s.cpu()[clear], s_ref[clear], rtol=4 * d + 1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("M,N,k", [(2048, 128, 6), (2500, 8, 2), (2049, 64, 8), (4100, 160, 6), (3000, 256, 8),
+                                   (2100, 512, 5), (2050, 1024, 8), (2048, 12, 3), (2200, 300, 7), (2304, 128, 1)])
+@pytest.mark.parametrize("mode", ["B", "A", "A_renorm"])
+def test_tile_path_shapes(cuda, lib, M, N, k, mode):
+    """Thread-per-row tile kernel (M >= 2048, k <= 8, aligned rows): 1, 2, 4 or 8 threads per row."""
+    lg = torch.randn(M, N, generator=torch.Generator().manual_seed(M + N + k))
+    _check(lg, k, mode, cuda)
+
+
+def test_tile_path_ties_and_specials(cuda, lib):
+    g = torch.Generator().manual_seed(17)
+    q = torch.round(torch.randn(2304, 256, generator=g) * 2) / 2          # ties everywhere, across the two halves
+    _check(q, 8, "B", cuda, oracle_slack=True)
+    # equal values already in the list must keep their order when a larger value arrives later
+    y = torch.randn(2048, 128, generator=g)
+    y[:, 40] = 1.25; y[:, 45] = 1.25; y[:, 90] = 3.0; y[:, 91] = 1.25
+    _check(y, 6, "B", cuda, oracle_slack=True)
+    x = torch.randn(2048, 64, generator=g)
+    x[5, 10] = float("nan"); x[5, 3] = float("inf"); x[6, :] = 0.0; x[6, 7] = -0.0; x[7, 1] = float("-inf")
+    _, i = ops.topk_softmax(x.to(cuda), 4)
+    assert torch.equal(i.cpu(), O.stable_topk(x, 4)[1])

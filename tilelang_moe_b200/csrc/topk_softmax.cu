@@ -1,6 +1,8 @@
 // Fused top-k + softmax router kernels for sm_100a.
 //
-// Two kernels behind one entry point:
+// Three kernels behind one entry point:
+//   * topk_tile_kernel   rows staged in shared memory by cp.async, 1-8 threads per row keep a sorted
+//                        k-entry list in registers; N <= 1024, k <= 8, aligned rows, M >= 64.
 //   * topk_warp_kernel   one warp per row, the row lives in registers; k rounds of
 //                        warp-wide arg-max by redux; N <= 1024, k <= 64.
 //   * topk_radix_kernel  a thread-block cluster per row; each CTA stages its slice
@@ -132,6 +134,157 @@ static int launch_warp(const float* logits, int64_t M, int N, int64_t ld, int k,
   if (blocks > cap) blocks = cap;
   topk_warp_kernel<ELTS, VEC><<<(unsigned)blocks, 128, 0, st>>>(logits, M, N, ld, k, mode, scores, idx64, idx32);
   MOE_CHECK_LAUNCH("topk_warp_kernel");
+  return MOE_OK;
+}
+
+
+// ------------------------------------------------------------------------------------
+// thread-per-row kernel for small k (k <= 8, N <= 1024, 16-byte aligned rows)
+//
+// A CTA of 128 threads stages a tile of rows in shared memory with 16-byte cp.async (coalesced, the only
+// read of the logits), then TPR = 1, 2, 4 or 8 adjacent threads share one row: each scans its part with a
+// sorted k-entry list in registers (compare against the k-th best, insert by a compare-exchange chain),
+// partial lists are merged over shuffles, and the first thread of the row normalises and writes.
+// The instruction cost per row is a quarter of the warp-per-row kernel's; three CTAs per SM keep ~190 KB of
+// loads in flight.  Keys are signed integers ordered like the floats: x + 0.0f folds -0.0 into +0.0 and every
+// NaN into the canonical positive NaN, which ranks above +inf.
+// ------------------------------------------------------------------------------------
+constexpr int TILE_THREADS = 128;
+constexpr int TILE_FLOATS = 128 * 128;      // staged floats per tile (rows x row length <= this)
+
+__device__ __forceinline__ int float_to_ikey(float x) {
+  const int b = __float_as_int(x + 0.0f);
+  return b ^ ((b >> 31) & 0x7FFFFFFF);
+}
+__device__ __forceinline__ float ikey_to_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7FFFFFFF)); }
+
+template <int K>
+__device__ __forceinline__ void list_insert(int (&kv)[K], int (&ki)[K], int ck, int ci) {
+  // shift chain: the candidate enters at the first entry it strictly exceeds (equal keys keep the earlier column
+  // ahead); from there on every entry moves down one place, so entries that tie with each other keep their order
+  bool p = false;
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    p = p || (ck > kv[j]);
+    const int tv = kv[j], ti = ki[j];
+    kv[j] = p ? ck : tv;
+    ki[j] = p ? ci : ti;
+    ck = p ? tv : ck;
+    ci = p ? ti : ci;
+  }
+}
+
+template <int K, int TPR>
+__global__ void __launch_bounds__(TILE_THREADS)
+topk_tile_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld, int k, int mode, int rows_per_tile,
+                 float* __restrict__ scores, int64_t* __restrict__ idx64, int32_t* __restrict__ idx32) {
+  extern __shared__ __align__(16) float tile[];
+  const int tid = threadIdx.x;
+  const int pitch = N + 4;                         // floats; 16-byte aligned rows, conflict-free 16-byte reads
+  const int vec_per_row = N >> 2;
+  const int row_in_tile = tid / TPR, part = tid % TPR;
+  const int part_vecs = (vec_per_row + TPR - 1) / TPR;
+  const int64_t n_tiles = (M + rows_per_tile - 1) / rows_per_tile;
+
+  for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int64_t row0 = t * rows_per_tile;
+    const int rows = (int)((M - row0) < rows_per_tile ? (M - row0) : rows_per_tile);
+    __syncthreads();                               // previous tile fully consumed
+    for (int v = tid; v < rows * vec_per_row; v += TILE_THREADS) {
+      const int r = v / vec_per_row, c = v - r * vec_per_row;
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tile + r * pitch + c * 4);
+      const float* src = logits + (row0 + r) * ld + c * 4;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    const bool active = row_in_tile < rows;
+    int kv[K], ki[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) { kv[j] = (int)0x80000000; ki[j] = 0; }
+    const float* rowp = tile + row_in_tile * pitch;
+    const int v_lo = part * part_vecs, v_hi = min(vec_per_row, v_lo + part_vecs);
+    if (active) {
+      for (int v = v_lo; v < v_hi; ++v) {
+        const float4 x = *reinterpret_cast<const float4*>(rowp + v * 4);
+        const int k0 = float_to_ikey(x.x), k1 = float_to_ikey(x.y), k2 = float_to_ikey(x.z), k3 = float_to_ikey(x.w);
+        const int m = max(max(k0, k1), max(k2, k3));
+        if (m > kv[K - 1]) {                       // some element of the vector enters the list
+          list_insert<K>(kv, ki, k0, v * 4);
+          list_insert<K>(kv, ki, k1, v * 4 + 1);
+          list_insert<K>(kv, ki, k2, v * 4 + 2);
+          list_insert<K>(kv, ki, k3, v * 4 + 3);
+        }
+      }
+    }
+    // merge the parts of a row: the lower part keeps its entries ahead of equal ones from higher columns
+#pragma unroll
+    for (int d = 1; d < TPR; d <<= 1) {
+      int ok[K], oi[K];
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        ok[j] = __shfl_xor_sync(0xFFFFFFFFu, kv[j], d);
+        oi[j] = __shfl_xor_sync(0xFFFFFFFFu, ki[j], d);
+      }
+      if ((part & d) == 0) {
+#pragma unroll
+        for (int j = 0; j < K; ++j) list_insert<K>(kv, ki, ok[j], oi[j]);
+      }
+    }
+    // full-row softmax denominator for the conventions that normalise over all N
+    float rowsum = 0.f;
+    const float vmax = ikey_to_float(TPR == 1 ? kv[0] : __shfl_sync(0xFFFFFFFFu, kv[0], (tid & 31) - part));
+    if (mode != MOE_TOPK_MODE_B) {
+      if (active)
+        for (int v = v_lo; v < v_hi; ++v) {
+          const float4 x = *reinterpret_cast<const float4*>(rowp + v * 4);
+          rowsum += expf(x.x - vmax) + expf(x.y - vmax) + expf(x.z - vmax) + expf(x.w - vmax);
+        }
+#pragma unroll
+      for (int d = 1; d < TPR; d <<= 1) rowsum += __shfl_xor_sync(0xFFFFFFFFu, rowsum, d);
+    }
+    if (active && part == 0) {
+      float e[K];
+      float denom = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        e[j] = j < k ? expf(ikey_to_float(kv[j]) - vmax) : 0.f;
+        denom += e[j];
+      }
+      if (mode != MOE_TOPK_MODE_B) denom = rowsum;
+      float renorm = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) { e[j] = e[j] / denom; renorm += e[j]; }
+      const int64_t o = (row0 + row_in_tile) * (int64_t)k;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (j < k) {
+          scores[o + j] = mode == MOE_TOPK_MODE_A_RENORM ? e[j] / renorm : e[j];
+          if (idx64) idx64[o + j] = (int64_t)ki[j];
+          if (idx32) idx32[o + j] = (int32_t)ki[j];
+        }
+      }
+    }
+  }
+}
+
+template <int K, int TPR>
+static int launch_tile(const float* logits, int64_t M, int N, int64_t ld, int k, int mode, float* scores,
+                       int64_t* idx64, int32_t* idx32, int sm_count, cudaStream_t st) {
+  const int rows_per_tile = TILE_THREADS / TPR;
+  const size_t smem = (size_t)rows_per_tile * (N + 4) * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(topk_tile_kernel<K, TPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
+    attr_set = true;
+  }
+  int64_t blocks = ceil_div64(M, rows_per_tile);
+  const int64_t cap = (int64_t)sm_count * 3;
+  if (blocks > cap) blocks = cap;
+  topk_tile_kernel<K, TPR><<<(unsigned)blocks, TILE_THREADS, smem, st>>>(logits, M, N, ld, k, mode, rows_per_tile, scores,
+                                                                        idx64, idx32);
+  MOE_CHECK_LAUNCH("topk_tile_kernel");
   return MOE_OK;
 }
 
@@ -510,6 +663,20 @@ extern "C" int moe_topk_softmax(const float* logits, int64_t M, int64_t N, int64
   if (rc) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int n = (int)N;
+  if (n <= 1024 && k <= 8 && n >= 8 && (n % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0) &&
+      M >= 2048) {
+    // enough rows to give every SM a tile; below that the warp-per-row kernel has the shorter critical path
+    // thread-per-row tiles: TPR threads share a row so that a tile is always <= 128 x 128 floats
+    const int tpr = n <= 128 ? 1 : (n <= 256 ? 2 : (n <= 512 ? 4 : 8));
+#define MOE_TILE_CASE(K_, T_) return launch_tile<K_, T_>(logits, M, n, ld, k, mode, scores, indices, indices32, dev.sm_count, st)
+#define MOE_TILE_K(K_) { if (tpr == 1) MOE_TILE_CASE(K_, 1); if (tpr == 2) MOE_TILE_CASE(K_, 2); if (tpr == 4) MOE_TILE_CASE(K_, 4); MOE_TILE_CASE(K_, 8); }
+    if (k <= 2) MOE_TILE_K(2)
+    if (k <= 4) MOE_TILE_K(4)
+    if (k <= 6) MOE_TILE_K(6)
+    MOE_TILE_K(8)
+#undef MOE_TILE_K
+#undef MOE_TILE_CASE
+  }
   if (n <= 1024 && k <= 64) {
     const bool vec = (n % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
 #define MOE_WARP_CASE(E_, V_) return launch_warp<E_, V_>(logits, M, n, ld, k, mode, scores, indices, indices32, dev.sm_count, st)
