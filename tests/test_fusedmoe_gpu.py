@@ -95,3 +95,27 @@ def test_graph_replay_matches_eager(cuda, lib):
     got = run().clone()
     assert torch.equal(got, m.forward(xd, *wd))
     ops.check_status(cuda)
+
+
+def test_host_pipeline_overlaps_copies_and_keeps_results(cuda, lib):
+    from tilelang_moe_b200.pipeline import HostPipeline
+    g = torch.Generator().manual_seed(2)
+    T, H, I, E, k = 256, 256, 128, 8, 2
+    x = torch.randn(T, H, generator=g).bfloat16().pin_memory()
+    lg = torch.randn(T, E, generator=g).pin_memory()
+    Wg = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16().to(cuda)
+    Wu = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16().to(cuda)
+    Wd = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16().to(cuda)
+    ws = layer.MoEWorkspace(T, k, H, I, E, 0, cuda)
+
+    def compute(xd, lgd, outd):
+        sc, ix = ops.topk_softmax(lgd, k, mode="A", index_dtype=torch.int32)
+        layer.routed_forward(xd, sc, ix, Wg, Wu, Wd, ws, out=outd)
+
+    pipe = HostPipeline(cuda, [x, lg], (T, H), torch.bfloat16, compute)
+    last = pipe.run(5)
+    torch.cuda.synchronize()
+    ref = O.fusedmoe(x, None, None, None, None, Wg.cpu(), Wu.cpu(), Wd.cpu(), k, logits=lg)
+    torch.testing.assert_close(last.float(), ref, rtol=RTOL, atol=ATOL)
+    assert torch.equal(pipe.out_host[0], pipe.out_host[1])     # every step computed the same batch
+    assert pipe.h2d_bytes == T * H * 2 + T * E * 4 and pipe.d2h_bytes == T * H * 2
