@@ -319,7 +319,7 @@ def run_ours(args, cfg):
         how = ("dispatch kernel + down-GEMM epilogue over NVLink peer memory" if args.exchange == "peer"
                else "NCCL all-to-all")
         parallelism = f"ep{world}: {E // world} experts per GPU, tokens split {T // world} per rank, {how}"
-        imbalance = runner.imbalance
+        imbalance = {"rows": runner.imbalance, "modelled_time": runner.cost_imbalance}
 
     def sync_all():
         torch.cuda.synchronize()

@@ -30,9 +30,24 @@ def contiguous_placement(n_experts: int, world: int) -> List[int]:
     return [e // per for e in range(n_experts)]
 
 
-def balanced_placement(load: Sequence[float], world: int) -> List[int]:
+def expert_cost(rows: float, tile_rows: int = 128, stream_tiles: float = 1.6) -> float:
+    """Time an expert costs its GPU, in units of one 128-row tile through both GEMMs.
+
+    An expert is tensor-core bound at ceil(rows/128) tiles, but never cheaper than streaming its weights from
+    HBM once, which on B200 at H=7168, I=2048 takes as long as about 1.6 tiles (88 MB at 6.5 TB/s against
+    11.3 GFLOP per tile at 1.3 PFLOP/s).  An expert without rows costs nothing: its weights are never touched.
+    Balancing rows alone leaves the rank holding one huge expert plus many tiny ones ~17 % slower than the rest."""
+    if rows <= 0:
+        return 0.0
+    return max(stream_tiles, float(-(-int(rows) // tile_rows)))
+
+
+def balanced_placement(load: Sequence[float], world: int, cost=None) -> List[int]:
     """Greedy longest-processing-time assignment with exactly E/world experts per rank:
-    heaviest expert first, to the least loaded rank that still has a free slot."""
+    costliest expert first, to the least loaded rank that still has a free slot.
+    ``load`` is rows per expert; ``cost`` maps rows to time (default: rows themselves)."""
+    if cost is not None:
+        load = [cost(v) for v in load]
     E = len(load)
     per = E // world
     order = sorted(range(E), key=lambda e: (-float(load[e]), e))
@@ -70,11 +85,11 @@ class EPPlan:
         if any(len(l) != self.e_local for l in self.local_experts):
             raise ValueError("placement must give every rank the same number of experts")
 
-    def imbalance(self, counts_per_expert: Sequence[float]) -> float:
-        """max over ranks / mean over ranks of routed rows under this placement."""
+    def imbalance(self, counts_per_expert: Sequence[float], cost=None) -> float:
+        """max over ranks / mean over ranks of routed rows (or of cost(rows)) under this placement."""
         tot = [0.0] * self.world
         for e, c in enumerate(counts_per_expert):
-            tot[self.expert_to_rank[e]] += float(c)
+            tot[self.expert_to_rank[e]] += float(c) if cost is None else cost(c)
         mean = sum(tot) / self.world
         return max(tot) / mean if mean > 0 else 1.0
 
@@ -223,7 +238,12 @@ class EPRunner:
         # placement from the expert loads of a calibration batch with the same popularity law
         # (a different noise draw than the timed batch): what a serving system knows in advance
         load = self._calibration_load(cfg, calib_seed)
-        e2r = balanced_placement(load, world) if placement == "balanced" else contiguous_placement(E, world)
+        if placement == "balanced":      # by routed rows
+            e2r = balanced_placement(load, world)
+        elif placement == "time":        # by modelled time; with a fixed expert count per rank it cannot beat "balanced":
+            e2r = balanced_placement(load, world, cost=expert_cost)   # the rank of the hottest expert still holds 31 others
+        else:
+            e2r = contiguous_placement(E, world)
         self.plan = EPPlan(E, world, e2r)
         self.id_map_dev = torch.tensor(self.plan.id_map, dtype=torch.int32, device=device)
         self.Wg, self.Wu, self.Wd = make_weights(cfg, device, experts=self.plan.local_experts[rank])
@@ -254,7 +274,9 @@ class EPRunner:
     def bench_closures(self, x_cpu, logits_cpu):
         """(step, step_e2e, launches per step, h2d bytes, d2h bytes) for this rank's share of the batch."""
         Tl, r, dev = self.Tl, self.rank, self.dev
-        self.imbalance = self.plan.imbalance(self._routed_counts(logits_cpu))
+        rc = self._routed_counts(logits_cpu)
+        self.imbalance = self.plan.imbalance(rc)
+        self.cost_imbalance = self.plan.imbalance(rc, cost=expert_cost)
         x_l = x_cpu[r * Tl:(r + 1) * Tl].contiguous()
         lg_l = logits_cpu[r * Tl:(r + 1) * Tl].contiguous()
         x, lg = x_l.to(dev), lg_l.to(dev)
