@@ -184,6 +184,8 @@ int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offs
  * perm / topk_idx / id_map / offsets from moe_route_histogram) into peer_recv[dest] at its
  * expert-major row: plain stores to peer memory, no collective library.  peer_recv: host
  * array of G device pointers (one receive buffer per rank, this rank's own included).
+ * Only rows bound for local expert slots [slot_lo, slot_hi) of their destination are moved, so
+ * the dispatch of a second group of experts can overlap the GEMMs of the first.
  * moe_grouped_gemm_peer_scatter is moe_grouped_gemm(MOE_GEMM_PLAIN) whose epilogue stores row r
  * into peer_base[row_rank[r]] at row dst_rows[r]: the combine exchange fused into the down GEMM.
  * Callers order the phases across ranks (a barrier after dispatch and after the scatter).
@@ -192,7 +194,8 @@ int moe_ep_plan(const int32_t* cnt_all, int G, int E_local, int my_rank, int32_t
                 int32_t* dst_base, int32_t* ret_rank, int32_t* ret_row, void* stream);
 int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx,
                     const int32_t* id_map, const int32_t* offsets, const int32_t* dst_base, int k,
-                    int E_local, int64_t n, int64_t H, void* const* peer_recv, int G, void* stream);
+                    int E_local, int slot_lo, int slot_hi, int64_t n, int64_t H,
+                    void* const* peer_recv, int G, void* stream);
 int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                   const int32_t* row_rank, const int32_t* dst_rows,
                                   void* const* peer_base, int n_peers, int64_t ldy, int64_t max_rows,

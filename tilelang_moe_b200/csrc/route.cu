@@ -574,13 +574,16 @@ struct PeerPtrs {
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm, const int32_t* __restrict__ topk_idx,
                    const int32_t* __restrict__ id_map, const int32_t* __restrict__ offsets,
-                   const int32_t* __restrict__ dst_base, int k, int El, int64_t n, int vec_per_row, PeerPtrs peers) {
+                   const int32_t* __restrict__ dst_base, int k, int El, int slot_lo, int slot_hi, int64_t n,
+                   int vec_per_row, PeerPtrs peers) {
   const int lane = threadIdx.x & 31;
   const int64_t nwarps = (int64_t)gridDim.x * 8;
   for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < n; p += nwarps) {
     const int32_t f = perm[p];
     const int v = id_map[topk_idx[f]];
     const int dest = v / El;
+    const int slot = v - dest * El;
+    if (slot < slot_lo || slot >= slot_hi) continue;   // this launch moves only the rows of local experts [lo, hi)
     const int64_t row = (int64_t)dst_base[v] + (p - offsets[v]);
     const uint4* s = x + (int64_t)(f / k) * vec_per_row;
     uint4* d = reinterpret_cast<uint4*>(peers.p[dest]) + row * vec_per_row;
@@ -610,11 +613,12 @@ extern "C" int moe_ep_plan(const int32_t* cnt_all, int G, int E_local, int my_ra
 }
 
 extern "C" int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx, const int32_t* id_map,
-                               const int32_t* offsets, const int32_t* dst_base, int k, int E_local, int64_t n,
-                               int64_t H, void* const* peer_recv, int G, void* stream) {
+                               const int32_t* offsets, const int32_t* dst_base, int k, int E_local, int slot_lo,
+                               int slot_hi, int64_t n, int64_t H, void* const* peer_recv, int G, void* stream) {
   using namespace moe;
   if (!x || !perm || !topk_idx || !id_map || !offsets || !dst_base || !peer_recv) return fail(MOE_ERR_ARG, "ep_dispatch: null pointer");
   if (G < 1 || G > 16 || k < 1 || E_local < 1 || H < 8 || H % 8 || n < 0) return fail(MOE_ERR_ARG, "ep_dispatch: bad shape");
+  if (slot_lo < 0 || slot_hi > E_local || slot_lo >= slot_hi) return fail(MOE_ERR_ARG, "ep_dispatch: bad slot range [%d,%d)", slot_lo, slot_hi);
   if (n == 0) return MOE_OK;
   PeerPtrs pp;
   for (int g = 0; g < 16; ++g) pp.p[g] = g < G ? peer_recv[g] : nullptr;
@@ -627,7 +631,8 @@ extern "C" int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t
   const int64_t cap = (int64_t)dev.sm_count * 8;
   if (blocks > cap) blocks = cap;
   ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const uint4*>(x), perm, topk_idx, id_map, offsets, dst_base, k, E_local, n, (int)(H / 8), pp);
+      reinterpret_cast<const uint4*>(x), perm, topk_idx, id_map, offsets, dst_base, k, E_local, slot_lo, slot_hi, n,
+      (int)(H / 8), pp);
   MOE_CHECK_LAUNCH("ep_dispatch_kernel");
   return MOE_OK;
 }

@@ -150,7 +150,7 @@ class PeerExchange:
     """
 
     def __init__(self, t_local: int, k: int, H: int, world: int, device: torch.device, group=None,
-                 cap_rows: Optional[int] = None):
+                 cap_rows: Optional[int] = None, overlap: bool = True):
         import torch.distributed._symmetric_memory as symm_mem
         from . import ops
         group = dist.group.WORLD if group is None else group
@@ -163,6 +163,8 @@ class PeerExchange:
         self.ret_ptrs = ops._ptr_array(list(self.h_ret.buffer_ptrs))
         self.cnt_all = torch.empty(world, 0, dtype=torch.int32, device=device)
         self.plan_bufs = {}
+        self.side = torch.cuda.Stream(device=device)
+        self.overlap = overlap
 
 
 def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: EPPlan, id_map_dev: torch.Tensor,
@@ -185,15 +187,50 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
             px.cnt_all = torch.empty(G, E, dtype=torch.int32, device=x_local.device)
         dist.all_gather_into_tensor(px.cnt_all.view(-1), counts, group=group)
         offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(px.cnt_all, G, El, rank, px.cap, out=px.plan_bufs)
-    with st("dispatch"):
-        ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs)
-    with st("dispatch_barrier"):
-        px.h_recv.barrier(channel=0)
-    with st("up_gemm"):
-        act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg, offs_local, B2=Wu,
-                                      out=_take(bufs, "act", px.cap, Wg.shape[1], x_local), expected_rows=Tl * k)
-    with st("down_gemm"):
-        ops.grouped_gemm_peer_scatter(act, Wd, offs_local, ret_rank, ret_row, px.ret_ptrs, H, expected_rows=Tl * k)
+    I = Wg.shape[1]
+    act = _take(bufs, "act", px.cap, I, x_local)
+    split = El // 2 if (px.overlap and El >= 2) else 0
+    if split == 0:
+        with st("dispatch"):
+            ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs)
+        with st("dispatch_barrier"):
+            px.h_recv.barrier(channel=0)
+        with st("up_gemm"):
+            ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg, offs_local, B2=Wu, out=act, expected_rows=Tl * k)
+        with st("down_gemm"):
+            ops.grouped_gemm_peer_scatter(act, Wd, offs_local, ret_rank, ret_row, px.ret_ptrs, H, expected_rows=Tl * k)
+    else:
+        # Two groups of local experts.  The rows of the second group travel on a side stream while the GEMMs of the
+        # first group run: the receive buffer is expert-major, so each group owns a contiguous range of it and the
+        # GEMM of a group is the same kernel on a sub-range of the offset table and of the weights.
+        cur = torch.cuda.current_stream(x_local.device)
+        with st("dispatch"):
+            ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs, 0, split)
+        with st("dispatch_barrier"):
+            px.h_recv.barrier(channel=0)
+            fork = torch.cuda.Event()
+            fork.record(cur)
+        with torch.cuda.stream(px.side):
+            px.side.wait_event(fork)   # after the first group has landed everywhere: the links are free again
+            ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs, split, El)
+            px.h_recv.barrier(channel=2)
+            second_ready = torch.cuda.Event()
+            second_ready.record(px.side)
+        half = Tl * k // 2
+        with st("up_gemm"):
+            ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg[:split], offs_local[:split + 1], B2=Wu[:split], out=act,
+                                    expected_rows=half)
+        with st("down_gemm"):
+            ops.grouped_gemm_peer_scatter(act, Wd[:split], offs_local[:split + 1], ret_rank, ret_row, px.ret_ptrs, H,
+                                          expected_rows=half)
+        with st("second_wait"):
+            cur.wait_event(second_ready)
+        with st("up_gemm_2"):
+            ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg[split:], offs_local[split:], B2=Wu[split:], out=act,
+                                    expected_rows=half)
+        with st("down_gemm_2"):
+            ops.grouped_gemm_peer_scatter(act, Wd[split:], offs_local[split:], ret_rank, ret_row, px.ret_ptrs, H,
+                                          expected_rows=half)
     with st("combine_barrier"):
         px.h_ret.barrier(channel=1)
     with st("combine"):
@@ -251,7 +288,11 @@ class EPRunner:
         self.bufs = {"hist_ws": torch.empty(max(need, 4), dtype=torch.uint8, device=device)}
         self.imbalance = None
         self.exchange = exchange
-        self.px = PeerExchange(self.Tl, k, cfg["H"], world, device) if exchange == "peer" else None
+        import os
+        # Dispatching the second half of the local experts under the first half's GEMMs pays only where the dispatch
+        # is a large share of the step: measured +2.5 % at 8 GPUs, nothing at 4, -3 % at 2 (the copy slows the GEMM).
+        overlap = os.environ.get("MOE_B200_EP_OVERLAP", "1" if world >= 8 else "0") != "0"
+        self.px = PeerExchange(self.Tl, k, cfg["H"], world, device, overlap=overlap) if exchange == "peer" else None
 
     def _routed_counts(self, logits_cpu: torch.Tensor) -> List[int]:
         """Rows per expert when `logits_cpu` is routed top-k (through the router and histogram kernels)."""

@@ -290,14 +290,17 @@ def ep_plan(cnt_all: torch.Tensor, G: int, e_local: int, rank: int, cap_rows: in
 
 
 def ep_dispatch(x: torch.Tensor, perm: torch.Tensor, idx32: torch.Tensor, id_map: torch.Tensor, offsets: torch.Tensor,
-                dst_base: torch.Tensor, k: int, e_local: int, peer_recv_ptrs) -> None:
-    """Copy every routed row of x into the destination rank's receive buffer (peer stores)."""
+                dst_base: torch.Tensor, k: int, e_local: int, peer_recv_ptrs, slot_lo: int = 0,
+                slot_hi: Optional[int] = None) -> None:
+    """Copy the routed rows of x bound for local expert slots [slot_lo, slot_hi) into the destination ranks'
+    receive buffers (peer stores)."""
     _need_cuda(x, perm)
     n = perm.numel()
     arr = peer_recv_ptrs if not isinstance(peer_recv_ptrs, (list, tuple)) else _ptr_array(peer_recv_ptrs)
     with torch.cuda.device(x.device):
         rc = _lib.load().moe_ep_dispatch(_ptr(x), _ptr(perm), _ptr(idx32), _ptr(id_map), _ptr(offsets), _ptr(dst_base),
-                                         k, e_local, n, x.shape[1], arr, len(arr), _stream())
+                                         k, e_local, slot_lo, e_local if slot_hi is None else slot_hi, n, x.shape[1],
+                                         arr, len(arr), _stream())
     _lib.check(rc, "moe_ep_dispatch")
 
 
