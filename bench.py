@@ -4,7 +4,8 @@
 
 One "step" is one forward pass of the routed MoE layer over one batch of synthetic
 tokens: top-k + softmax routing of the given fp32 logits, histogram / permutation,
-row gather, up GEMM with fused SiLU gate, down GEMM with fused weight scale + scatter,
+up GEMM with the row gather fused into its operand pipeline and the SiLU gate into its epilogue,
+down GEMM with fused weight scale + scatter,
 k-way combine.  The default workload is the DeepSeek-V3-shaped layer of the benchmark
 contract (T=8192, H=7168, I=2048, E=256, top-8, Zipf(1.1) expert load); with N > 1 the
 256 experts are sharded N ways and tokens travel by all-to-all (expert parallelism).
@@ -273,7 +274,7 @@ def run_ours(args, cfg):
             x.copy_(x_pin, non_blocking=True)
             out_pin.copy_(step(), non_blocking=True)
 
-        launches_per_step = 11   # router GEMV, topk, 3 x histogram, gather, up, down, shared up, shared down, combine
+        launches_per_step = 10 if H % 64 == 0 else 11   # router GEMV, topk, 3 x histogram, [gather,] up, down, shared up, shared down, combine
         tokens_per_step = T
         h2d, d2h = x_pin.numel() * 2, out_pin.numel() * 2
         parallelism = "1 GPU" + (", whole layer replayed as one CUDA graph" if args.graph else ", eager launches")
@@ -290,7 +291,7 @@ def run_ours(args, cfg):
             scores, idx32 = ops.topk_softmax(logits, k, mode="A", index_dtype=torch.int32)
             return layer.routed_forward(x, scores, idx32, Wg, Wu, Wd, ws, timers=timers)
 
-        launches_per_step = 8
+        launches_per_step = 7 if ws.fused_gather else 8   # topk, 3 x histogram, [gather,] up, down, combine
         x_pin = x_cpu.pin_memory()
         lg_pin = logits_cpu.pin_memory()
         out_pin = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()

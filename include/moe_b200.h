@@ -50,6 +50,9 @@ extern "C" {
 #define MOE_GEMM_SILU_GATE 1      /* Y[r] = silu(A[r].Bg[e]^T) * (A[r].Bu[e]^T)    */
 #define MOE_GEMM_SCALE_SCATTER 2  /* Y[dst(r)] = w[r] * (A[r] . B[e]^T)            */
 #define MOE_GEMM_PLAIN_F32 3      /* as PLAIN, fp32 output                         */
+#define MOE_GEMM_SCALE_SCATTER_DSTW 4 /* Y[dst(r)] = w[dst(r)] * (A[r] . B[e]^T): the weight is
+                                         read at the destination row, e.g. straight from the
+                                         [T,k] score matrix when dst = perm               */
 
 /* 16-bit element type of activations, weights and outputs (accumulation is always fp32).
  * The reference's wrappers default to fp16 (kernels/fusedmoe_tilelang.py:257), the
@@ -143,6 +146,20 @@ int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2,
                      const int32_t* offsets, const int32_t* dst_rows, const float* row_w, void* Y,
                      int64_t ldy, int64_t max_rows, int64_t expected_rows, int K, int N, int E,
                      int dtype, int32_t* status, void* stream);
+
+/* moe_grouped_gemm with the row gather fused into the operand pipeline: sorted row r of A is
+ * row gather_idx[r] / gather_div of X [x_rows, K] (gather_idx = `perm` of moe_route_histogram,
+ * gather_div = k), fetched by the kernel itself, so that neither moe_gather_rows nor the sorted
+ * copy of the activations is needed.  Same role as X[sorted_indices] feeding the kernel in
+ * kernels/grouped_gemm_tilelang.py:700 and the stacking loops of kernels/fusedmoe_tilelang.py:346-355.
+ * gather_idx int32 [max_rows]; indices are clamped to x_rows - 1.  K % 64 == 0.  Other arguments as
+ * moe_grouped_gemm.
+ */
+int moe_grouped_gemm_gathered(int epilogue, const void* X, int64_t x_rows, const int32_t* gather_idx,
+                              int gather_div, const void* B, const void* B2, const int32_t* offsets,
+                              const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy,
+                              int64_t max_rows, int64_t expected_rows, int K, int N, int E, int dtype,
+                              int32_t* status, void* stream);
 
 /* ---- combine ----------------------------------------------------------------------
  * out[t,:] = (shared ? shared[t,:] : 0) + sum_{s<k} c(t,s) * Yk[r(t,s),:], fp32 sum in

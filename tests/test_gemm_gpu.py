@@ -138,3 +138,58 @@ def test_float16_inputs(cuda, lib):
     ops.check_status(cuda)
     assert y.dtype == torch.float16
     torch.testing.assert_close(y.float().cpu(), O.grouped_gemm(X, W, idx), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("T,k,H,I,E,dtype", [(300, 1, 64, 40, 3, torch.bfloat16), (1000, 2, 256, 384, 6, torch.bfloat16),
+                                             (4096, 8, 1024, 512, 64, torch.bfloat16), (777, 4, 448, 264, 9, torch.float16),
+                                             (5, 2, 128, 64, 40, torch.bfloat16)])
+def test_fused_row_gather_is_bit_identical_to_gather_then_gemm(cuda, lib, T, k, H, I, E, dtype):
+    """The kernel's own row fetch (cp.async into the swizzled operand stage) must feed the tensor cores exactly
+    what the TMA path reads from a pre-gathered matrix: every output bit equal, for each epilogue."""
+    g = torch.Generator().manual_seed(T + k + H)
+    x = torch.randn(T, H, generator=g).to(dtype).to(cuda)
+    Wg = (torch.randn(E, I, H, generator=g) * 0.06).to(dtype).to(cuda)
+    Wu = (torch.randn(E, I, H, generator=g) * 0.06).to(dtype).to(cuda)
+    idx = torch.argsort(torch.rand(T, E, generator=g), dim=1)[:, :k].contiguous().to(cuda)
+    _, offsets, perm, _ = ops.route_histogram(idx, E, want_inv=False)
+    xs = ops.gather_rows(x, perm, div=k)
+    n = T * k
+    ref_gate = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, xs, Wg, offsets, B2=Wu)
+    got_gate = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, x, Wg, offsets, B2=Wu, gather=perm, gather_div=k)
+    ref_plain = ops.grouped_gemm_sorted(ops.GEMM_PLAIN, xs, Wg, offsets, dst_rows=perm,
+                                        out=torch.zeros(n, I, dtype=dtype, device=cuda))
+    got_plain = ops.grouped_gemm_sorted(ops.GEMM_PLAIN, x, Wg, offsets, dst_rows=perm, gather=perm, gather_div=k,
+                                        out=torch.zeros(n, I, dtype=dtype, device=cuda))
+    ref_f32 = ops.grouped_gemm_sorted(ops.GEMM_PLAIN_F32, xs, Wg, offsets)
+    got_f32 = ops.grouped_gemm_sorted(ops.GEMM_PLAIN_F32, x, Wg, offsets, gather=perm, gather_div=k)
+    ops.check_status(cuda)
+    assert got_gate.shape == (n, I)
+    assert torch.equal(got_gate, ref_gate)
+    assert torch.equal(got_plain, ref_plain)
+    assert torch.equal(got_f32, ref_f32)
+
+
+def test_fused_row_gather_rejects_unsupported_k(cuda, lib):
+    x = torch.zeros(8, 72, dtype=torch.bfloat16, device=cuda)
+    W = torch.zeros(1, 8, 72, dtype=torch.bfloat16, device=cuda)
+    offs = torch.tensor([0, 8], dtype=torch.int32, device=cuda)
+    perm = torch.arange(8, dtype=torch.int32, device=cuda)
+    with pytest.raises(ValueError):
+        ops.grouped_gemm_sorted(ops.GEMM_PLAIN, x, W, offs, gather=perm)
+
+
+def test_scale_scatter_weight_read_at_destination(cuda, lib):
+    """SCALE_SCATTER_DSTW reads the routing weight at the destination row (the [T,k] score matrix itself when
+    dst = perm): same bits as SCALE_SCATTER fed with the weights gathered into sorted order."""
+    g = torch.Generator().manual_seed(11)
+    T, k, H, I, E = 900, 4, 256, 192, 10
+    act = torch.randn(T * k, I, generator=g).bfloat16().to(cuda)
+    Wd = (torch.randn(E, H, I, generator=g) * 0.06).bfloat16().to(cuda)
+    scores = torch.rand(T, k, generator=g).to(cuda)
+    idx = torch.argsort(torch.rand(T, E, generator=g), dim=1)[:, :k].contiguous().to(cuda)
+    _, offsets, perm, _ = ops.route_histogram(idx, E, want_inv=False)
+    w_sorted = scores.reshape(-1)[perm.long()].contiguous()
+    ref = ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, act, Wd, offsets, dst_rows=perm, row_w=w_sorted)
+    got = ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER_DSTW, act, Wd, offsets, dst_rows=perm, row_w=scores.reshape(-1))
+    ops.check_status(cuda)
+    assert torch.equal(got, ref)

@@ -22,6 +22,8 @@ SIGNATURES = {
     "moe_route_histogram_static": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "moe_gather_rows": (_i32, [_vp, _vp, _i32, _i64, _i64, _vp, _vp, _vp, _vp]),
     "moe_grouped_gemm": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "moe_grouped_gemm_gathered": (_i32, [_i32, _vp, _i64, _vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                                         _i32, _i32, _i32, _i32, _vp, _vp]),
     "moe_combine": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _i32, _vp, _vp]),
     "moe_ep_regroup": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp]),
     "moe_ep_plan": (_i32, [_vp, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),

@@ -20,6 +20,11 @@
 // Tiles are enumerated on the device from the expert offsets (no host sync): expert-major, then
 // N tile, then M tile, so that CTAs running side by side share one B tile through L2.
 //
+// Optional row gather (128-row tiles): instead of a TMA box of a pre-gathered A, two more warps copy the
+// tile's A rows straight from the un-permuted activation matrix (row = gather[r] / div) with 16-byte
+// cp.async into the same 128-byte-swizzled stage layout, completing on the stage's full barrier next to the
+// TMA of B.  This removes the separate gather pass (one write and one read of the sorted copy of A).
+//
 // Epilogues: plain bf16 / fp32, SiLU(gate)*up with gate and up accumulated side by side in TMEM
 // by one N=256 instruction, and routing-weight scale + scatter to the (token, slot) row.
 //
@@ -35,11 +40,12 @@
 namespace moe {
 namespace gemm {
 
-constexpr int EPI_PEER = 4;            // internal: plain bf16 rows stored into other GPUs' buffers (row_rank / peer_base)
+constexpr int EPI_PEER = 16;           // internal: plain bf16 rows stored into other GPUs' buffers (row_rank / peer_base)
 constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS_GATHER = 256;   // 128-row kernel: + two warps that gather A rows when asked to
 constexpr int MAX_E = 1024;
 constexpr uint64_t WAIT_LIMIT_NS = 1000ull * 1000ull * 1000ull;   // 1 s per barrier wait
 constexpr uint64_t DRAIN_LIMIT_NS = 20ull * 1000ull * 1000ull;    // 20 ms when draining after a failure
@@ -80,6 +86,13 @@ struct Params {
   // peer_base[row_rank[r]] at row dst_rows[r]; plain stores to peer memory from the epilogue
   const int32_t* row_rank;
   void* peer_base[16];
+  // optional gather of the A rows (128-row kernel only): sorted row r is row a_gather[r] / a_div of a_src
+  const int32_t* a_gather;
+  const void* a_src;
+  int a_div;
+  int a_src_rows;
+  int a_rows;          // entries of a_gather
+  int w_by_dst;        // SCALE_SCATTER: row_w is indexed by the destination row instead of the sorted row
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -175,6 +188,18 @@ __device__ __forceinline__ void tma_prefetch_3d(const void* tmap, int c0, int c1
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
+
+// copies src_bytes (16 or 0) from global memory and fills the rest of the 16 bytes with zeros
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// the barrier receives one arrival once every cp.async this thread has issued so far has landed
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// orders shared-memory writes made through the generic proxy before later reads by the async proxy (tcgen05.mma)
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -272,7 +297,7 @@ __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f +
 
 // ------------------------------------------------------------------------------ kernel
 template <int MT, int BN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS_GATHER, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmB2, const Params p) {
   using C = Cfg<MT, BN>;
@@ -295,10 +320,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
   const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
   const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
+  const bool gather = MT == 1 && p.a_gather != nullptr;
 
   // ---- set-up: barriers, TMEM, tile table
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    // full: the TMA producer's arrive (+ one arrival per lane of the two gather warps once its copies have landed)
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, gather ? 65 : 1); mbar_init(empty0 + 8 * s, 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -311,7 +338,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets[e];
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS_GATHER) offs[e] = p.offsets[e];
   __syncthreads();
   if (warp == 2) {  // prefix of M tiles per expert, one warp, chunks of consecutive experts per lane
     const int per = (E + 31) / 32;
@@ -349,8 +376,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t full = full0 + 8 * stage;
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
           const uint32_t sb = sa + C::A_BYTES;
-          mbar_arrive_expect_tx(full, C::STAGE_BYTES);
-          tma_load_2d(sa, &tmA, full, kb * BK, t.row0);
+          mbar_arrive_expect_tx(full, gather ? C::B_BYTES : C::STAGE_BYTES);
+          if (!gather) tma_load_2d(sa, &tmA, full, kb * BK, t.row0);
           if (EPI == MOE_GEMM_SILU_GATE) {
             tma_load_3d(sb, &tmB, full, kb * BK, n0, t.e);
             tma_load_3d(sb + C::B_BYTES / 2, &tmB2, full, kb * BK, n0, t.e);
@@ -387,6 +414,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 3)) { ok = false; break; }
         tc_fence_after();
         if (lane == 0) {
+          if (gather) fence_proxy_async();   // the A rows were written by cp.async, not by the TMA unit
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
           const uint64_t adesc = make_smem_desc(sa);
           const uint64_t bdesc = make_smem_desc(sa + C::A_BYTES);
@@ -414,6 +442,56 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       __syncwarp();
       mbar_wait_drain(drain_bar, 0, DRAIN_LIMIT_NS);
     }
+  } else if (warp >= 6) {
+    // ===================================================================== A-row gather (only when asked to)
+    // Two warps, 64 tile rows each.  8 lanes cover the 128 bytes of one row, so one cp.async instruction moves
+    // four whole 128-byte row pieces; a lane keeps the 16 source pointers it needs for the whole tile.
+    if (gather) {
+      const unsigned char* src_base = reinterpret_cast<const unsigned char*>(p.a_src);
+      const size_t row_bytes = (size_t)p.K * 2;
+      const int chunk = lane & 7, sub = lane >> 3;
+      const int half_row0 = (warp - 6) * 64;             // first tile row of this warp
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+        // lane l reads the list entries of rows l and l + 32 of this warp's half.  Rows past the end of the
+        // expert's group are filled with zeros (nothing is read for them): their products are never stored,
+        // and zero operands keep the tensor cores' switching power down on the padding of ragged groups
+        uint32_t src_row[2];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          int r = t.row0 + half_row0 + lane + 32 * s;
+          if (r > p.a_rows - 1) r = p.a_rows - 1;
+          const uint32_t v = (uint32_t)p.a_gather[r] / (uint32_t)p.a_div;
+          src_row[s] = v < (uint32_t)p.a_src_rows ? v : (uint32_t)(p.a_src_rows - 1);
+        }
+        const unsigned char* rp[16];
+        uint32_t live = 0;                                                  // bit `it`: that row belongs to the group
+#pragma unroll
+        for (int it = 0; it < 16; ++it) {
+          const int row = it * 4 + sub;                                     // row within this warp's half
+          const uint32_t sr = __shfl_sync(0xFFFFFFFFu, src_row[it >> 3], row & 31);
+          rp[it] = src_base + (size_t)sr * row_bytes + chunk * 16;
+          if (t.row0 + half_row0 + row < t.row_end) live |= 1u << it;
+        }
+        for (int kb = 0; kb < NKB; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES) + half_row0 * 128;
+          const size_t koff = (size_t)kb * (BK * 2);
+#pragma unroll
+          for (int it = 0; it < 16; ++it) {
+            const int row = it * 4 + sub;
+            // 128-byte swizzle: 16-byte chunk c of row r sits at chunk (c ^ (r & 7)) of that row
+            cp_async_16(sa + row * 128 + ((chunk ^ (row & 7)) << 4), rp[it] + koff, (live >> it) & 1u ? 16u : 0u);
+          }
+          cp_async_arrive_noinc(full0 + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      cp_async_wait_all();   // nothing of this warp's is still in flight when the CTA retires its shared memory
+    }
   } else {
     // ===================================================================== epilogue (warps 2..5)
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
@@ -435,7 +513,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       void* ybase = p.Y;
       if (row_ok) {
         if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
-        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[grow];
+        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[p.w_by_dst ? out_row : (int64_t)grow];
         if (EPI == EPI_PEER) ybase = p.peer_base[p.row_rank[grow]];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * MT * BN + half * BN);
@@ -774,7 +852,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       float w = 1.0f;
       if (row_ok) {
         if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
-        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[grow];
+        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[p.w_by_dst ? out_row : (int64_t)grow];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
       const bool any_rows = t.row0 + (int)rank * BM < t.row_end;   // warp-uniform: this CTA's half holds rows
@@ -1046,7 +1124,7 @@ grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
           float my_w = 1.0f;
           if (tok < t.row0 + cnt) {
             my_dst = (!GATE && p.dst_rows) ? p.dst_rows[tok] : tok;
-            if (EPI == MOE_GEMM_SCALE_SCATTER) my_w = p.row_w[tok];
+            if (EPI == MOE_GEMM_SCALE_SCATTER) my_w = p.row_w[p.w_by_dst ? my_dst : tok];
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -1122,7 +1200,7 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
     MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<MT, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr_set = true;
   }
-  grouped_gemm_kernel<MT, BN, EPI><<<grid, NUM_THREADS, SMEM, st>>>(tA, tB, tB2, p);
+  grouped_gemm_kernel<MT, BN, EPI><<<grid, NUM_THREADS_GATHER, SMEM, st>>>(tA, tB, tB2, p);
   MOE_CHECK_LAUNCH("grouped_gemm_kernel");
   return MOE_OK;
 }
@@ -1159,16 +1237,39 @@ static int launch_tn(const CUtensorMap& tW, const CUtensorMap& tW2, const CUtens
 }  // namespace gemm
 }  // namespace moe
 
+struct GatherArgs {           // A rows fetched through an index list instead of a pre-gathered matrix
+  const int32_t* idx = nullptr;
+  int div = 1;
+  int64_t src_rows = 0;
+};
+
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                              const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                              int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
-                             void* const* peer_base, int n_peers, int64_t expected_rows, int dtype);
+                             void* const* peer_base, int n_peers, int64_t expected_rows, int dtype,
+                             const GatherArgs& ga = GatherArgs());
 
 extern "C" int moe_grouped_gemm(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                                 const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                                 int64_t expected_rows, int K, int N, int E, int dtype, int32_t* status, void* stream) {
   return grouped_gemm_impl(epilogue, A, B, B2, offsets, dst_rows, row_w, Y, ldy, max_rows, K, N, E, status, stream,
                            nullptr, nullptr, 0, expected_rows, dtype);
+}
+
+extern "C" int moe_grouped_gemm_gathered(int epilogue, const void* X, int64_t x_rows, const int32_t* gather_idx,
+                                         int gather_div, const void* B, const void* B2, const int32_t* offsets,
+                                         const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy,
+                                         int64_t max_rows, int64_t expected_rows, int K, int N, int E, int dtype,
+                                         int32_t* status, void* stream) {
+  using namespace moe;
+  if (!gather_idx) return fail(MOE_ERR_ARG, "grouped_gemm_gathered: null index list");
+  if (gather_div < 1 || x_rows < 1 || x_rows > 0x7FFFFFFFll)
+    return fail(MOE_ERR_ARG, "grouped_gemm_gathered: bad gather_div=%d or x_rows=%lld", gather_div, (long long)x_rows);
+  if (K % 64) return fail(MOE_ERR_UNSUPPORTED, "grouped_gemm_gathered: K=%d must be a multiple of 64", K);
+  GatherArgs ga;
+  ga.idx = gather_idx; ga.div = gather_div; ga.src_rows = x_rows;
+  return grouped_gemm_impl(epilogue, X, B, B2, offsets, dst_rows, row_w, Y, ldy, max_rows, K, N, E, status, stream,
+                           nullptr, nullptr, 0, expected_rows, dtype, ga);
 }
 
 extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
@@ -1188,14 +1289,20 @@ extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
                              const int32_t* dst_rows, const float* row_w, void* Y, int64_t ldy, int64_t max_rows,
                              int K, int N, int E, int32_t* status, void* stream, const int32_t* row_rank,
-                             void* const* peer_base, int n_peers, int64_t expected_rows, int dtype) {
+                             void* const* peer_base, int n_peers, int64_t expected_rows, int dtype,
+                             const GatherArgs& ga) {
   using namespace moe;
   using namespace moe::gemm;
   if (dtype != MOE_DTYPE_BF16 && dtype != MOE_DTYPE_F16) return fail(MOE_ERR_ARG, "grouped_gemm: unknown dtype %d", dtype);
   const int f16 = dtype == MOE_DTYPE_F16;
   // rows the caller expects to be live (<= max_rows, which may be a buffer capacity): steers the tile rule
   const int64_t live_rows = (expected_rows > 0 && expected_rows < max_rows) ? expected_rows : max_rows;
-  if (epilogue < 0 || epilogue > 3) return fail(MOE_ERR_ARG, "grouped_gemm: unknown epilogue %d", epilogue);
+  if (epilogue < 0 || epilogue > 4) return fail(MOE_ERR_ARG, "grouped_gemm: unknown epilogue %d", epilogue);
+  const int w_by_dst = epilogue == MOE_GEMM_SCALE_SCATTER_DSTW;
+  if (w_by_dst) {
+    if (!dst_rows) return fail(MOE_ERR_ARG, "grouped_gemm: SCALE_SCATTER_DSTW needs dst_rows");
+    epilogue = MOE_GEMM_SCALE_SCATTER;
+  }
   if (max_rows < 0 || K < 8 || N < 8 || (K % 8) || (N % 8) || E < 1)
     return fail(MOE_ERR_ARG, "grouped_gemm: bad shape rows=%lld K=%d N=%d E=%d (K, N multiples of 8)", (long long)max_rows, K, N, E);
   if (E > MAX_E) return fail(MOE_ERR_UNSUPPORTED, "grouped_gemm: E=%d exceeds %d", E, MAX_E);
@@ -1222,14 +1329,15 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   const int64_t m_tiles_128 = live_rows / BM + E, m_tiles_256 = live_rows / (2 * BM) + E;
   int MT = 1, BN = 128;
   if (gate || (N % 256 == 0 && m_tiles_128 * n_tiles_256 >= dev.sm_count)) BN = 256;
-  bool pair = !row_rank && (gate || N % 256 == 0) && live_rows / E >= 512 &&
+  bool pair = !row_rank && !ga.idx && (gate || N % 256 == 0) && live_rows / E >= 512 &&
               (live_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
   if (pair) { MT = 2; BN = 256; }
   // The tokens-as-N kernel is selected only by the override: measured on B200 it matches the rows-as-M
   // kernel when groups are small (both stream weights at HBM speed) and loses when they are large
   // (2-byte epilogue stores, more shared-memory reads per flop), so the default stays rows-as-M.
   int tn = 0;
-  const char* force_env = row_rank ? nullptr : getenv("MOE_B200_GEMM_TILE_ROWS");   // peer scatter: 128-row kernel only
+  // peer scatter and row gather: 128-row kernel only
+  const char* force_env = (row_rank || ga.idx) ? nullptr : getenv("MOE_B200_GEMM_TILE_ROWS");
   if (const char* force = force_env) {   // test / measurement override: "128", "256", "pair", "tn128", "tn256"
     if (force[0] == 't') { tn = atoi(force + 2) == 128 ? 128 : 256; pair = false; }
     else tn = 0;
@@ -1247,6 +1355,7 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
     q.f16 = f16;
     q.row_rank = nullptr;
     for (int g = 0; g < 16; ++g) q.peer_base[g] = nullptr;
+    q.a_gather = nullptr; q.a_src = nullptr; q.a_div = 1; q.a_src_rows = 0; q.a_rows = 0; q.w_by_dst = w_by_dst;
     CUtensorMap tW, tW2, tX;
     rc = make_tmap(&tW, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM, f16);
     if (rc) return rc;
@@ -1284,9 +1393,13 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   p.f16 = f16;
   p.row_rank = row_rank;
   for (int g = 0; g < 16; ++g) p.peer_base[g] = (peer_base && g < n_peers) ? peer_base[g] : nullptr;
+  p.w_by_dst = w_by_dst;
+  p.a_gather = ga.idx; p.a_src = A; p.a_div = ga.div; p.a_src_rows = (int)ga.src_rows; p.a_rows = (int)max_rows;
 
   CUtensorMap tA, tB, tB2;
-  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)max_rows, 0, (uint32_t)(pair ? BM : MT * BM), f16);
+  // with a row gather A is the un-permuted matrix (src_rows rows) and its tensor map is never used by the kernel
+  const uint64_t a_map_rows = ga.idx ? (uint64_t)ga.src_rows : (uint64_t)max_rows;
+  rc = make_tmap(&tA, A, (uint64_t)K, a_map_rows, 0, (uint32_t)(pair ? BM : MT * BM), f16);
   if (rc) return rc;
   const uint32_t b_box_rows = pair ? 128u : (uint32_t)out_cols;   // a CTA of a pair stages 128 N rows
   rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows, f16);

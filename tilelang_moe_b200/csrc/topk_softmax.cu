@@ -306,6 +306,8 @@ struct RadixCtrl {
   uint32_t k_rem;
   uint32_t sel_count;
   uint32_t blk_maxkey;
+  uint32_t loc_count;   // selected entries compacted in this CTA
+  uint32_t loc_base;    // their first slot in the leading CTA's buffer
   double blk_sum;
 };
 static_assert(sizeof(RadixCtrl) <= RCTRL_BYTES, "control block too large");
@@ -403,7 +405,8 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
   RadixCtrl* ctrl = reinterpret_cast<RadixCtrl*>(smem_raw);
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem_raw + RCTRL_BYTES);
   uint64_t* sbuf = reinterpret_cast<uint64_t*>(smem_raw + RCTRL_BYTES + 2 * RBINS * 4);
-  uint32_t* keys = reinterpret_cast<uint32_t*>(sbuf + kpad);
+  uint64_t* lbuf = sbuf + kpad;                      // this CTA's selected entries before they go to the leader
+  uint32_t* keys = reinterpret_cast<uint32_t*>(lbuf + kpad);
 
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   const unsigned lt_mask = (1u << lane) - 1u;
@@ -462,10 +465,13 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
     uint32_t g[RBPT];
 #pragma unroll
     for (int j = 0; j < RBPT; ++j) g[j] = 0u;
-    for (unsigned c = 0; c < C; ++c) {
-      const uint32_t* rh = cluster.map_shared_rank(h, c);
-      const uint4 v = *reinterpret_cast<const uint4*>(rh + tid * RBPT);
-      g[0] += v.x; g[1] += v.y; g[2] += v.z; g[3] += v.w;
+#pragma unroll
+    for (unsigned c = 0; c < 8; ++c) {   // all remote loads are issued before the first is consumed
+      if (c < C) {
+        const uint32_t* rh = cluster.map_shared_rank(h, c);
+        const uint4 v = *reinterpret_cast<const uint4*>(rh + tid * RBPT);
+        g[0] += v.x; g[1] += v.y; g[2] += v.z; g[3] += v.w;
+      }
     }
     const uint32_t tsum = g[0] + g[1] + g[2] + g[3];
     uint32_t inc = tsum;  // suffix-inclusive sum over lanes >= lane
@@ -514,9 +520,12 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
     for (unsigned c = 0; c < C; ++c) rowsum += cluster.map_shared_rank(ctrl, c)->blk_sum;
   }
 
-  // ---- gather the selected entries into the leading CTA
-  uint32_t* lead_count = cluster.map_shared_rank(&ctrl->sel_count, 0);
+  // ---- gather the selected entries into the leading CTA: compact them locally first (shared-memory atomics are
+  //      cheap, remote ones are not), reserve their place in the leader's buffer with one remote atomic, copy
   uint64_t* lead_sbuf = cluster.map_shared_rank(sbuf, 0);
+  uint32_t* lead_count = cluster.map_shared_rank(&ctrl->sel_count, 0);
+  if (tid == 0) ctrl->loc_count = 0u;
+  __syncthreads();
   for (int base = 0; base < len; base += RT) {
     const int i = base + tid;
     const uint32_t kk = i < len ? keys[i] : 0u;
@@ -524,9 +533,9 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
     const unsigned m = __ballot_sync(FULL, sel);
     if (m) {
       uint32_t b = 0u;
-      if (lane == 0) b = atomicAdd(lead_count, (uint32_t)__popc(m));
+      if (lane == 0) b = atomicAdd(&ctrl->loc_count, (uint32_t)__popc(m));
       b = __shfl_sync(FULL, b, 0);
-      if (sel) lead_sbuf[b + __popc(m & lt_mask)] = pack_entry(kk, (uint32_t)(begin + i));
+      if (sel) lbuf[b + __popc(m & lt_mask)] = pack_entry(kk, (uint32_t)(begin + i));
     }
   }
   if (!take_all && take > 0u) {  // block-uniform: only the first `take` equal entries, in index order
@@ -546,11 +555,18 @@ topk_radix_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld
       }
       const uint32_t myrank = before + (uint32_t)__popc(m & lt_mask);
       if (eq && myrank < take) {
-        const uint32_t slot = atomicAdd(lead_count, 1u);
-        lead_sbuf[slot] = pack_entry(thr, (uint32_t)(begin + i));
+        const uint32_t slot = atomicAdd(&ctrl->loc_count, 1u);
+        lbuf[slot] = pack_entry(thr, (uint32_t)(begin + i));
       }
       running += total;
     }
+  }
+  __syncthreads();
+  if (tid == 0) ctrl->loc_base = atomicAdd(lead_count, ctrl->loc_count);
+  __syncthreads();
+  {
+    const uint32_t cnt = ctrl->loc_count, base0 = ctrl->loc_base;
+    for (uint32_t i = tid; i < cnt; i += RT) lead_sbuf[base0 + i] = lbuf[i];
   }
   cluster.sync();
   if (crank != 0) return;  // nobody reads another CTA's shared memory past this point
@@ -626,7 +642,7 @@ static int launch_radix(const float* logits, int64_t M, int N, int64_t ld, int k
   int kpad = next_pow2(k);
   if (kpad < 2) kpad = 2;
   if (kpad > RMAX_KPAD) return fail(MOE_ERR_UNSUPPORTED, "topk_softmax: k=%d exceeds %d", k, RMAX_KPAD);
-  const size_t smem = (size_t)RCTRL_BYTES + 2 * RBINS * 4 + (size_t)kpad * 8 + (size_t)slice * 4;
+  const size_t smem = (size_t)RCTRL_BYTES + 2 * RBINS * 4 + (size_t)kpad * 16 + (size_t)slice * 4;
   const int vec_ok = (N % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
   MOE_CUDA_CHECK(cudaFuncSetAttribute(topk_radix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 

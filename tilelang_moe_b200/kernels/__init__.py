@@ -72,9 +72,13 @@ def grouped_gemm(X: torch.Tensor, W: torch.Tensor, expert_indices: torch.Tensor,
     k = expert_indices.shape[1] if expert_indices.dim() == 2 else 1
     n = X.shape[0] * k
     _, offsets, perm, _ = _ops.route_histogram(expert_indices, E, want_inv=False)
-    xs = _ops.gather_rows(X.contiguous(), perm, div=k)
     Y = torch.empty(n, I, dtype=X.dtype, device=X.device)
-    _ops.grouped_gemm_sorted(_ops.GEMM_PLAIN, xs, W.contiguous(), offsets, dst_rows=perm, out=Y)
+    if H % 64 == 0:     # the GEMM fetches the rows of X through the permutation itself
+        _ops.grouped_gemm_sorted(_ops.GEMM_PLAIN, X.contiguous(), W.contiguous(), offsets, dst_rows=perm, out=Y,
+                                 gather=perm, gather_div=k)
+    else:
+        xs = _ops.gather_rows(X.contiguous(), perm, div=k)
+        _ops.grouped_gemm_sorted(_ops.GEMM_PLAIN, xs, W.contiguous(), offsets, dst_rows=perm, out=Y)
     return Y.view(X.shape[0], k, I) if expert_indices.dim() == 2 else Y
 
 

@@ -1,8 +1,10 @@
 """The MoE layer forward as a fixed sequence of launches on one stream.
 
-    logits -> top-k + softmax -> histogram / offsets / permutation -> row gather
-           -> up GEMM (SiLU gate fused) -> down GEMM (weight scale + scatter fused)
-           -> combine (k-way sum + shared expert)
+    logits -> top-k + softmax -> histogram / offsets / permutation
+           -> up GEMM (row gather fused into its operand pipeline, SiLU gate fused into its epilogue)
+           -> down GEMM (routing-weight scale + scatter fused) -> combine (k-way sum + shared expert)
+
+(for a hidden size that is not a multiple of 64 the rows are gathered by a separate kernel first).
 
 No step reads anything back to the host: tile tables are derived on the device
 from the expert offsets, and scratch is sized from T, k, H, I alone, so one
@@ -13,6 +15,7 @@ and ``FusedMoETileLang.forward`` (reference kernels/fusedmoe_tilelang.py:309-417
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -37,8 +40,11 @@ class MoEWorkspace:
         dev, bf16 = self.device, self.dtype
         n = self.T * self.k
         self.logits = torch.empty(self.T, self.E, dtype=torch.float32, device=dev)
-        self.xs = torch.empty(n, self.H, dtype=bf16, device=dev)          # expert-sorted activations
-        self.ws = torch.empty(n, dtype=torch.float32, device=dev)         # routing weight per sorted row
+        # the up GEMM fetches the activation rows itself (MOE_B200_FUSED_GATHER=0: separate gather pass, for measurement)
+        self.fused_gather = self.H % 64 == 0 and os.environ.get("MOE_B200_FUSED_GATHER", "1") != "0"
+        if not self.fused_gather:
+            self.xs = torch.empty(n, self.H, dtype=bf16, device=dev)      # expert-sorted activations
+            self.ws = torch.empty(n, dtype=torch.float32, device=dev)     # routing weight per sorted row
         self.act = torch.empty(n, self.I, dtype=bf16, device=dev)         # SiLU(gate)*up per sorted row
         self.yk = torch.empty(n, self.H, dtype=bf16, device=dev)          # scaled expert output per (token, slot)
         need = _lib.load().moe_route_histogram_workspace(n, self.E)
@@ -90,13 +96,21 @@ def routed_forward(x_flat: torch.Tensor, scores: torch.Tensor, idx32: torch.Tens
     k = idx32.shape[1]
     with _Stage(timers, "histogram"):
         counts, offsets, perm, _ = ops.route_histogram(idx32, E, want_inv=False, workspace=ws.hist_ws)
-    with _Stage(timers, "gather"):
-        ops.gather_rows(x_flat, perm, div=k, out=ws.xs, w_src=scores, w_out=ws.ws)
-    with _Stage(timers, "up_gemm"):
-        ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, ws.xs, routed_gate, offsets, B2=routed_up, out=ws.act)
-    with _Stage(timers, "down_gemm"):
-        ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, ws.act, routed_down, offsets, dst_rows=perm, row_w=ws.ws,
-                                out=ws.yk)
+    if ws.fused_gather:
+        with _Stage(timers, "up_gemm"):
+            ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, x_flat, routed_gate, offsets, B2=routed_up, out=ws.act,
+                                    gather=perm, gather_div=k)
+        with _Stage(timers, "down_gemm"):   # the weight of sorted row r is scores.flat[perm[r]]: read at the destination
+            ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER_DSTW, ws.act, routed_down, offsets, dst_rows=perm,
+                                    row_w=scores.reshape(-1), out=ws.yk)
+    else:
+        with _Stage(timers, "gather"):
+            ops.gather_rows(x_flat, perm, div=k, out=ws.xs, w_src=scores, w_out=ws.ws)
+        with _Stage(timers, "up_gemm"):
+            ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, ws.xs, routed_gate, offsets, B2=routed_up, out=ws.act)
+        with _Stage(timers, "down_gemm"):
+            ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, ws.act, routed_down, offsets, dst_rows=perm,
+                                    row_w=ws.ws, out=ws.yk)
     if shared_ready is not None:      # the shared expert ran on another stream: join before it is read
         torch.cuda.current_stream(x_flat.device).wait_event(shared_ready)
     with _Stage(timers, "combine"):

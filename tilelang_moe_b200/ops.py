@@ -16,7 +16,7 @@ import torch
 from . import _lib
 
 MODE_B, MODE_A, MODE_A_RENORM = 0, 1, 2
-GEMM_PLAIN, GEMM_SILU_GATE, GEMM_SCALE_SCATTER, GEMM_PLAIN_F32 = 0, 1, 2, 3
+GEMM_PLAIN, GEMM_SILU_GATE, GEMM_SCALE_SCATTER, GEMM_PLAIN_F32, GEMM_SCALE_SCATTER_DSTW = 0, 1, 2, 3, 4
 _MODES = {"B": MODE_B, "A": MODE_A, "A_norenorm": MODE_A, "A_renorm": MODE_A_RENORM,
           0: MODE_B, 1: MODE_A, 2: MODE_A_RENORM}
 
@@ -165,9 +165,14 @@ def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets
                         B2: Optional[torch.Tensor] = None, dst_rows: Optional[torch.Tensor] = None,
                         row_w: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                         out_rows: Optional[int] = None, max_rows: Optional[int] = None,
-                        expected_rows: int = 0) -> torch.Tensor:
+                        expected_rows: int = 0, gather: Optional[torch.Tensor] = None,
+                        gather_div: int = 1) -> torch.Tensor:
     """Expert GEMM over expert-sorted rows.  A [rows,K] bf16, B (and B2) [E,N,K] bf16,
-    offsets int32 [E+1] on the device.  See include/moe_b200.h for the epilogues."""
+    offsets int32 [E+1] on the device.  See include/moe_b200.h for the epilogues.
+
+    With ``gather`` (int32 [rows], the ``perm`` of route_histogram) A is the un-permuted
+    matrix and sorted row r is A[gather[r] // gather_div]: the kernel fetches the rows itself
+    (K must be a multiple of 64)."""
     _need_cuda(A, B, offsets)
     dt = _dtype_code(A, B, B2)
     if A.dim() != 2 or B.dim() != 3 or not A.is_contiguous() or not B.is_contiguous():
@@ -180,16 +185,31 @@ def grouped_gemm_sorted(epilogue: int, A: torch.Tensor, B: torch.Tensor, offsets
         raise ValueError("B2 must match B")
     if offsets.dtype != torch.int32 or offsets.numel() != E + 1:
         raise ValueError("offsets must be int32 [E+1]")
+    if gather is not None:
+        _need_cuda(gather)
+        if gather.dtype != torch.int32 or gather.dim() != 1 or not gather.is_contiguous():
+            raise ValueError("gather must be a contiguous int32 vector")
+        if K % 64:
+            raise ValueError("a fused row gather needs K to be a multiple of 64")
+        x_rows, rows = rows, gather.numel()
     if max_rows is None:
         max_rows = rows
     if out is None:
         odt = torch.float32 if epilogue == GEMM_PLAIN_F32 else A.dtype
         out = torch.empty(rows if out_rows is None else out_rows, N, dtype=odt, device=A.device)
     with torch.cuda.device(A.device):
-        rc = _lib.load().moe_grouped_gemm(epilogue, _ptr(A), _ptr(B), _ptr(B2), _ptr(offsets), _ptr(dst_rows),
-                                          _ptr(row_w), _ptr(out), out.stride(0), max_rows, expected_rows, K, N, E, dt,
-                                          _ptr(status_buffer(A.device)), _stream())
-    _lib.check(rc, "moe_grouped_gemm")
+        if gather is not None:
+            name = "moe_grouped_gemm_gathered"
+            rc = _lib.load().moe_grouped_gemm_gathered(
+                epilogue, _ptr(A), x_rows, _ptr(gather), gather_div, _ptr(B), _ptr(B2), _ptr(offsets), _ptr(dst_rows),
+                _ptr(row_w), _ptr(out), out.stride(0), max_rows, expected_rows, K, N, E, dt,
+                _ptr(status_buffer(A.device)), _stream())
+        else:
+            name = "moe_grouped_gemm"
+            rc = _lib.load().moe_grouped_gemm(epilogue, _ptr(A), _ptr(B), _ptr(B2), _ptr(offsets), _ptr(dst_rows),
+                                              _ptr(row_w), _ptr(out), out.stride(0), max_rows, expected_rows, K, N, E,
+                                              dt, _ptr(status_buffer(A.device)), _stream())
+    _lib.check(rc, name)
     _after(A.device)
     return out
 
