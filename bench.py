@@ -523,24 +523,88 @@ def run_router(args):
                       "results": results}), flush=True)
 
 
+def run_gemm_grid(args):
+    """The reference benchmark's grouped-GEMM grid (benchmarks/benchmark_grouped_gemm.py:77-93 of the reference):
+    Qwen3-235B / DeepSeek-V2 / DeepSeek-V3 expert shapes x E_local in {8,16,32} x input tokens in {1024..16384},
+    tokens_per_expert = tokens * top_k // E_total rows on every local expert, Y = X . W[e]^T in bf16.  Per point:
+    median CUDA-event time of one launch (L2 flushed before it), TFLOP/s and weight-stream GB/s against the measured
+    peaks, and parity of 64 sampled rows against an fp32 matmul of the same bf16 inputs."""
+    from tilelang_moe_b200 import _lib, ops
+    _lib.load()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    models = [("Qwen3-235B", 4096, 3072, 128, 8), ("DeepSeek-V2", 5120, 1536, 160, 6), ("DeepSeek-V3", 7168, 2048, 256, 8)]
+    results = []
+    iters = args.steps if args.steps > 10 else 30
+    for name, H, I, E_total, top_k in models:
+        for E_local in (8, 16, 32):
+            g = torch.Generator(device=dev).manual_seed(E_local)
+            W = torch.randn(E_local, I, H, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
+            for tokens in (1024, 2048, 4096, 8192, 16384):
+                tag = f"{name}_E{E_local}_T{tokens}"
+                if args.only and tag not in args.only.split(","):
+                    continue
+                per = max(tokens * top_k // E_total, 1)
+                rows = E_local * per
+                X = torch.randn(rows, H, device=dev, dtype=torch.bfloat16, generator=g)
+                offs = torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev)
+                Y = torch.empty(rows, I, device=dev, dtype=torch.bfloat16)
+                for _ in range(3):
+                    ops.grouped_gemm_sorted(ops.GEMM_PLAIN, X, W, offs, out=Y)
+                times = []
+                for _ in range(iters):
+                    flush.zero_()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    ops.grouped_gemm_sorted(ops.GEMM_PLAIN, X, W, offs, out=Y)
+                    b.record()
+                    torch.cuda.synchronize()
+                    times.append(a.elapsed_time(b) * 1e3)
+                ops.check_status(dev)
+                us = statistics.median(times)
+                sel = torch.randint(0, rows, (64,), device=dev, generator=g)
+                ref = torch.einsum("rh,rih->ri", X[sel].float(), W[sel // per].float())
+                got = Y[sel].float()
+                err = ((got - ref).abs() / (ref.abs() + 2.0)).max().item()    # 1e-2 rel + 2e-2 abs contract, as one ratio
+                flops = 2.0 * rows * H * I
+                byts = (E_local * H * I + rows * H + rows * I) * 2
+                results.append({"name": tag, "rows": rows, "rows_per_expert": per, "us": round(us, 2),
+                                "TFLOPs": round(flops / us / 1e6, 1), "GBps": round(byts / us / 1e3, 1),
+                                "frac_tensor_burst": round(flops / us / 1e6 / peaks["bf16_tflops"], 3),
+                                "frac_hbm": round(byts / us / 1e3 / peaks["hbm_gbs"], 3),
+                                "parity_err_over_tol": round(err / 1e-2, 3)})
+    worst = max(r["parity_err_over_tol"] for r in results)
+    best = max(max(r["frac_tensor_burst"], r["frac_hbm"]) for r in results)
+    print(json.dumps({"metric": "grouped_gemm_us", "unit": "us", "value": results[0]["us"], "higher_is_better": False,
+                      "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "gemm_grid: reference grouped-GEMM benchmark grid, uniform rows per expert"},
+                      "peak_tflops_burst": peaks["bf16_tflops"], "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                      "best_roof_fraction": best, "parity_ok": worst <= 1.0, "worst_parity_err_over_tol": worst,
+                      "results": results}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router", "gemm_grid"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--graph", action="store_true", help="c3: replay the layer as one CUDA graph")
-    ap.add_argument("--only", default="", help="router workload: comma-separated point names to run")
+    ap.add_argument("--only", default="", help="router / gemm_grid workloads: comma-separated point names to run")
     ap.add_argument("--balanced", action="store_true", help="diagnostic: uniform expert load instead of Zipf(1.1)")
     args = ap.parse_args()
     global BALANCED
     BALANCED = args.balanced
     if args.workload == "router":
         return run_router(args)
+    if args.workload == "gemm_grid":
+        return run_gemm_grid(args)
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, cfg)

@@ -8,7 +8,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libmoe_b200.so"
+import os
+
+# MOE_B200_LIBRARY selects another build of the same ABI (the tile-timeline build, libmoe_b200_trace.so)
+LIB_PATH = Path(os.environ.get("MOE_B200_LIBRARY") or Path(__file__).resolve().parent / "libmoe_b200.so")
 
 # every symbol declared in include/moe_b200.h: name -> (restype, argtypes)
 _i64, _i32, _vp, _sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t

@@ -47,16 +47,21 @@ def needs_build() -> bool:
     return any(d.stat().st_mtime > t for d in deps if d.exists())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not needs_build():
+TRACE_LIB = PKG / "libmoe_b200_trace.so"   # --trace: same sources with -DMOE_GEMM_TRACE (tile timeline tool only)
+
+
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Path:
+    if not trace and not force and not needs_build():
         return LIB
     objs = []
-    obj_dir = PKG / "build"
+    obj_dir = PKG / ("build_trace" if trace else "build")
     obj_dir.mkdir(exist_ok=True)
     procs = []
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if trace:
+            cmd.insert(1, "-DMOE_GEMM_TRACE")
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -72,14 +77,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("nvcc compilation failed")
-    link = [_nvcc(), "-shared", "-o", str(LIB), *[str(o) for o in objs], "-gencode",
+    target = TRACE_LIB if trace else LIB
+    link = [_nvcc(), "-shared", "-o", str(target), *[str(o) for o in objs], "-gencode",
             "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n" + r.stdout)
-    return LIB
+    return target
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv)
     print(path)

@@ -37,6 +37,20 @@
 #include <mutex>
 #include <stdlib.h>
 
+// -DMOE_GEMM_TRACE (the `--trace` build): the 128-row kernel stamps every tile with %globaltimer at three points
+// and every CTA with a clock64 / %globaltimer pair, into fixed device arrays read back by moe_gemm_trace_read.
+// Not compiled into the product library.
+#ifdef MOE_GEMM_TRACE
+#define MOE_TRACE_MAX_TILES 32768
+#define MOE_TRACE_MAX_CTAS 256
+__device__ unsigned long long g_trace_tile[3][MOE_TRACE_MAX_TILES];   // MMA start, accumulator ready, epilogue done
+__device__ int g_trace_cta[MOE_TRACE_MAX_TILES];
+__device__ long long g_trace_clk[MOE_TRACE_MAX_CTAS][4];              // clock64, ns at start; clock64, ns at end
+#define MOE_TRACE(...) __VA_ARGS__
+#else
+#define MOE_TRACE(...)
+#endif
+
 namespace moe {
 namespace gemm {
 
@@ -360,6 +374,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = tstart[E] * NT;
+  MOE_TRACE(if (threadIdx.x == 0 && blockIdx.x < MOE_TRACE_MAX_CTAS) {
+    g_trace_clk[blockIdx.x][0] = clock64(); g_trace_clk[blockIdx.x][1] = (long long)global_timer_ns(); })
 
   if (warp == 0) {
     // ===================================================================== TMA producer
@@ -413,6 +429,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int kb = 0; kb < NKB; ++kb) {
         if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 3)) { ok = false; break; }
         tc_fence_after();
+        MOE_TRACE(if (lane == 0 && kb == 0 && tile < MOE_TRACE_MAX_TILES) {
+          g_trace_tile[0][tile] = global_timer_ns(); g_trace_cta[tile] = blockIdx.x; })
         if (lane == 0) {
           if (gather) fence_proxy_async();   // the A rows were written by cp.async, not by the TMA unit
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -502,6 +520,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
       tc_fence_after();
+      MOE_TRACE(if (warp == 2 && lane == 0 && tile < MOE_TRACE_MAX_TILES) g_trace_tile[1][tile] = global_timer_ns();)
 #pragma unroll 1
       for (int half = 0; half < MT; ++half) {
       if (half == 1 && t.row0 + BM >= t.row_end) break;   // nothing was accumulated for rows 128..255
@@ -591,6 +610,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       }  // halves
+      MOE_TRACE(if (warp == 2 && lane == 0 && tile < MOE_TRACE_MAX_TILES) g_trace_tile[2][tile] = global_timer_ns();)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
@@ -601,6 +621,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // ---- teardown
   tc_fence_before();
   __syncthreads();
+  MOE_TRACE(if (threadIdx.x == 0 && blockIdx.x < MOE_TRACE_MAX_CTAS) {
+    g_trace_clk[blockIdx.x][2] = clock64(); g_trace_clk[blockIdx.x][3] = (long long)global_timer_ns(); })
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -1441,3 +1463,16 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   }
 #undef MOE_GEMM_CASE
 }
+
+#ifdef MOE_GEMM_TRACE
+// tile_ns: 3 x MOE_TRACE_MAX_TILES uint64, tile_cta: MOE_TRACE_MAX_TILES int32, cta_clk: MOE_TRACE_MAX_CTAS x 4 int64
+// (host buffers); the stamps of the most recent launch of the 128-row kernel on the current device.
+extern "C" int moe_gemm_trace_read(unsigned long long* tile_ns, int* tile_cta, long long* cta_clk) {
+  using namespace moe;
+  MOE_CUDA_CHECK(cudaDeviceSynchronize());
+  MOE_CUDA_CHECK(cudaMemcpyFromSymbol(tile_ns, g_trace_tile, sizeof(unsigned long long) * 3 * MOE_TRACE_MAX_TILES));
+  MOE_CUDA_CHECK(cudaMemcpyFromSymbol(tile_cta, g_trace_cta, sizeof(int) * MOE_TRACE_MAX_TILES));
+  MOE_CUDA_CHECK(cudaMemcpyFromSymbol(cta_clk, g_trace_clk, sizeof(long long) * 4 * MOE_TRACE_MAX_CTAS));
+  return MOE_OK;
+}
+#endif
