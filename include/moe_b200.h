@@ -178,6 +178,20 @@ int moe_combine(const void* Yk, const void* shared, const int32_t* row_of, const
 int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, int dtype, float* logits,
                       int32_t* status, void* stream);
 
+/* Router GEMM + top-k + softmax in ONE kernel: the [T,E] logits never travel through memory (they are
+ * written only if logits_out != NULL).  Same result as moe_router_logits / moe_grouped_gemm(PLAIN_F32)
+ * followed by moe_topk_softmax on those logits: indices sorted by value, ties lowest index first.
+ * Replaces the fused family of kernels/router_gemm_topk_softmax.py:148-1141.
+ *   x [T,H], Wr [E,H] 16-bit (dtype), fp32 accumulation; scores fp32 [T,k]; indices int64 and / or
+ *   indices32 int32 [T,k]; mode as moe_topk_softmax.
+ * Two kernels behind it: E <= 32 with E*H*2 <= 200 KB - CUDA cores, one warp per token, any k <= E;
+ * otherwise E % 8 == 0, E <= 256, k <= 8 - tcgen05 GEMM whose epilogue selects from the TMEM accumulator row.
+ * Other shapes: MOE_ERR_UNSUPPORTED (use the two separate calls).
+ */
+int moe_router_topk(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype,
+                    float* scores, int64_t* indices, int32_t* indices32, float* logits_out,
+                    int32_t* status, void* stream);
+
 /* ---- expert-parallel regroup table -----------------------------------------------------
  * No counterpart in the reference (it has no multi-GPU code).  recv_counts int32
  * [G][E_local]: rows received from source rank s for local expert j, laid out

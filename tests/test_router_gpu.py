@@ -140,7 +140,7 @@ def test_router_gemm_then_topk_like_the_reference_fusion_test(cuda, lib, H, E, K
     lg = ops.router_logits(X.to(cuda), W.to(cuda))
     ops.check_status(cuda)
     torch.testing.assert_close(lg.cpu(), ref_logits, rtol=1e-4, atol=1e-3)
-    s, i = ops.router_topk_softmax(X.to(cuda), W.to(cuda), K)
+    s, i = ops.router_topk_softmax(X.to(cuda), W.to(cuda), K, fused=True)
     s_ref, i_ref = O.topk_softmax(ref_logits, K, "B")
     sv = torch.sort(ref_logits, dim=-1, descending=True).values
     clear = ((sv[:, :K] - sv[:, 1:K + 1]).min(-1).values > 1e-2)
@@ -177,3 +177,43 @@ def test_tile_path_ties_and_specials(cuda, lib):
     x[5, 10] = float("nan"); x[5, 3] = float("inf"); x[6, :] = 0.0; x[6, 7] = -0.0; x[7, 1] = float("-inf")
     _, i = ops.topk_softmax(x.to(cuda), 4)
     assert torch.equal(i.cpu(), O.stable_topk(x, 4)[1])
+
+
+@pytest.mark.parametrize("T,H,E,K,dtype", [(300, 512, 64, 8, torch.bfloat16), (1000, 1024, 256, 8, torch.bfloat16),
+                                           (129, 256, 160, 6, torch.float16), (77, 2048, 8, 2, torch.bfloat16),
+                                           (515, 640, 32, 4, torch.bfloat16), (64, 7168, 256, 1, torch.bfloat16),
+                                           (200, 128, 24, 24, torch.bfloat16)])
+@pytest.mark.parametrize("mode", ["B", "A", "A_renorm"])
+def test_one_kernel_router_equals_gemm_then_topk(cuda, lib, T, H, E, K, dtype, mode):
+    """moe_router_topk (selection inside the GEMM's epilogue, or the CUDA-core kernel for few experts) against the
+    two separate calls: the same logits bit for bit, hence the same indices; scores to 1e-6.  Inputs are quantised
+    so that equal logits occur and the lowest-index rule is exercised."""
+    g = torch.Generator().manual_seed(T + E)
+    X = (torch.round(torch.randn(T, H, generator=g) * 2) / 2).to(dtype).to(cuda)
+    W = (torch.round(torch.randn(E, H, generator=g) * 2) / 8).to(dtype).to(cuda)
+    assert ops.router_topk_fused_supported(H, E, K)
+    lg = ops.router_logits(X, W)
+    s2, i2 = ops.topk_softmax(lg, K, mode=mode)
+    lg_out = torch.full((T, E), float("nan"), dtype=torch.float32, device=cuda)
+    s1, i1 = ops.router_topk_softmax(X, W, K, mode=mode, logits_out=lg_out, fused=True)
+    s32, i32 = ops.router_topk_softmax(X, W, K, mode=mode, index_dtype=torch.int32, fused=True)
+    ops.check_status(cuda)
+    assert torch.equal(lg_out, lg)
+    assert i1.dtype == torch.int64 and i32.dtype == torch.int32
+    assert torch.equal(i1, i2) and torch.equal(i32.long(), i2)
+    torch.testing.assert_close(s1, s2, rtol=2e-6, atol=1e-30)
+    assert torch.equal(s32, s1)
+    # and against the oracle on those logits (ties lowest index first)
+    s_ref, i_ref = O.topk_softmax(lg.cpu(), K, mode)
+    assert torch.equal(i1.cpu(), i_ref)
+    assert (lg.cpu()[:, :-1] == lg.cpu()[:, 1:]).any() or E <= 8     # the quantised inputs do produce equal logits
+
+
+def test_one_kernel_router_falls_back_for_other_shapes(cuda, lib):
+    g = torch.Generator().manual_seed(3)
+    X = torch.randn(100, 256, generator=g).bfloat16().to(cuda)
+    W = torch.randn(320, 256, generator=g).bfloat16().to(cuda)      # more experts than one accumulator tile holds
+    assert not ops.router_topk_fused_supported(256, 320, 4)
+    s, i = ops.router_topk_softmax(X, W, 4)
+    s2, i2 = ops.topk_softmax(ops.router_logits(X, W), 4)
+    assert torch.equal(i, i2) and torch.equal(s, s2)

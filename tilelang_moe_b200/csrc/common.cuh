@@ -62,10 +62,38 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
   return __uint_as_float(b);
 }
 
+// Signed-integer keys ordered like the floats (thread-per-row selection lists): x + 0.0f folds -0.0 into +0.0 and
+// every NaN into the canonical positive NaN, which ranks above +inf.
+__device__ __forceinline__ int float_to_ikey(float x) {
+  const int b = __float_as_int(x + 0.0f);
+  return b ^ ((b >> 31) & 0x7FFFFFFF);
+}
+__device__ __forceinline__ float ikey_to_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7FFFFFFF)); }
+
+template <int K>
+__device__ __forceinline__ void list_insert(int (&kv)[K], int (&ki)[K], int ck, int ci) {
+  // shift chain: the candidate enters at the first entry it strictly exceeds (equal keys keep the earlier column
+  // ahead); from there on every entry moves down one place, so entries that tie with each other keep their order
+  bool p = false;
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    p = p || (ck > kv[j]);
+    const int tv = kv[j], ti = ki[j];
+    kv[j] = p ? ck : tv;
+    ki[j] = p ? ci : ti;
+    ck = p ? tv : ck;
+    ci = p ? ti : ci;
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
   return v;
 }
+
+// tcgen05 router GEMM whose epilogue does top-k + softmax per row (gemm_sm100.cu); E <= 256, E % 8 == 0, k <= 8
+int router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype, float* scores,
+                     int64_t* indices, int32_t* indices32, float* logits_out, int32_t* status, void* stream);
 
 }  // namespace moe

@@ -54,6 +54,7 @@ __device__ long long g_trace_clk[MOE_TRACE_MAX_CTAS][4];              // clock64
 namespace moe {
 namespace gemm {
 
+constexpr int EPI_ROUTER = 17;         // internal: top-k + softmax of each accumulator row (fused router), no matrix output
 constexpr int EPI_PEER = 16;           // internal: plain bf16 rows stored into other GPUs' buffers (row_rank / peer_base)
 constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
@@ -86,27 +87,34 @@ struct Cfg {
 };
 
 struct Params {
-  const int32_t* offsets;
-  const int32_t* dst_rows;
-  const float* row_w;
-  void* Y;
-  int64_t ldy;
-  int K, N, E;
-  int num_n_tiles;
-  int num_k_blocks;
-  int f16;           // 0: bf16 inputs / outputs, 1: fp16
-  int32_t* status;
+  const int32_t* offsets = nullptr;
+  const int32_t* dst_rows = nullptr;
+  const float* row_w = nullptr;
+  void* Y = nullptr;
+  int64_t ldy = 0;
+  int K = 0, N = 0, E = 0;
+  int num_n_tiles = 0;
+  int num_k_blocks = 0;
+  int f16 = 0;           // 0: bf16 inputs / outputs, 1: fp16
+  int32_t* status = nullptr;
   // optional scatter of output rows into other GPUs' buffers (expert-parallel combine): row r goes to
   // peer_base[row_rank[r]] at row dst_rows[r]; plain stores to peer memory from the epilogue
-  const int32_t* row_rank;
-  void* peer_base[16];
+  const int32_t* row_rank = nullptr;
+  void* peer_base[16] = {};
   // optional gather of the A rows (128-row kernel only): sorted row r is row a_gather[r] / a_div of a_src
-  const int32_t* a_gather;
-  const void* a_src;
-  int a_div;
-  int a_src_rows;
-  int a_rows;          // entries of a_gather
-  int w_by_dst;        // SCALE_SCATTER: row_w is indexed by the destination row instead of the sorted row
+  const int32_t* a_gather = nullptr;
+  const void* a_src = nullptr;
+  int a_div = 1;
+  int a_src_rows = 0;
+  int a_rows = 0;          // entries of a_gather
+  int w_by_dst = 0;        // SCALE_SCATTER: row_w is indexed by the destination row instead of the sorted row
+  // fused router (EPI_ROUTER): the N = n_experts accumulator columns of a row are its logits
+  int dense_rows = 0;      // offsets == nullptr: one group of this many rows
+  float* r_scores = nullptr;     // fp32 [rows, r_k]
+  int64_t* r_idx64 = nullptr;    // either may be null
+  int32_t* r_idx32 = nullptr;
+  float* r_logits = nullptr;     // optional fp32 [rows, N] copy of the logits
+  int r_k = 0, r_mode = 0;
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -352,7 +360,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS_GATHER) offs[e] = p.offsets[e];
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS_GATHER) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
   if (warp == 2) {  // prefix of M tiles per expert, one warp, chunks of consecutive experts per lane
     const int per = (E + 31) / 32;
@@ -536,6 +544,69 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (EPI == EPI_PEER) ybase = p.peer_base[p.row_rank[grow]];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * MT * BN + half * BN);
+      if (EPI == EPI_ROUTER) {
+        // This thread's accumulator row holds the N logits of one token: keep the k largest in a sorted list
+        // (ascending column scan + strict comparison = lowest index first among equals), then normalise.
+        constexpr int KMAX = 8;
+        int kv[KMAX], ki[KMAX];
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) { kv[j] = (int)0x80000000; ki[j] = 0; }
+        const int chunks = (p.N + 31) / 32;
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = c * 32 + j;
+            const int key = float_to_ikey(__uint_as_float(v[j]));
+            if (col < p.N && key > kv[KMAX - 1]) list_insert<KMAX>(kv, ki, key, col);
+          }
+          if (p.r_logits && row_ok) {
+            float* dst = p.r_logits + (int64_t)grow * p.N + c * 32;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (c * 32 + j * 4 < p.N)   // N % 8 == 0: whole 16-byte vectors
+                *reinterpret_cast<uint4*>(dst + j * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
+        }
+        const float vmax = ikey_to_float(kv[0]);
+        float rowsum = 0.f;
+        if (p.r_mode != MOE_TOPK_MODE_B) {       // conventions that normalise over all experts: second pass over TMEM
+#pragma unroll 1
+          for (int c = 0; c < chunks; ++c) {
+            uint32_t v[32];
+            tmem_ld32(taddr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c * 32 + j < p.N) rowsum += expf(__uint_as_float(v[j]) - vmax);
+          }
+        }
+        if (row_ok) {
+          float e[KMAX];
+          float denom = 0.f;
+#pragma unroll
+          for (int j = 0; j < KMAX; ++j) {
+            e[j] = j < p.r_k ? expf(ikey_to_float(kv[j]) - vmax) : 0.f;
+            denom += e[j];
+          }
+          if (p.r_mode != MOE_TOPK_MODE_B) denom = rowsum;
+          float renorm = 0.f;
+#pragma unroll
+          for (int j = 0; j < KMAX; ++j) { e[j] = e[j] / denom; renorm += e[j]; }
+          const int64_t o = (int64_t)grow * p.r_k;
+#pragma unroll
+          for (int j = 0; j < KMAX; ++j) {
+            if (j < p.r_k) {
+              p.r_scores[o + j] = p.r_mode == MOE_TOPK_MODE_A_RENORM ? e[j] / renorm : e[j];
+              if (p.r_idx64) p.r_idx64[o + j] = (int64_t)ki[j];
+              if (p.r_idx32) p.r_idx32[o + j] = (int32_t)ki[j];
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < OUT_COLS / 32; ++c) {
         uint32_t v[32];
@@ -609,6 +680,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       }
+      }  // not the router epilogue
       }  // halves
       MOE_TRACE(if (warp == 2 && lane == 0 && tile < MOE_TRACE_MAX_TILES) g_trace_tile[2][tile] = global_timer_ns();)
       tc_fence_before();
@@ -1292,6 +1364,48 @@ extern "C" int moe_grouped_gemm_gathered(int epilogue, const void* X, int64_t x_
   ga.idx = gather_idx; ga.div = gather_div; ga.src_rows = x_rows;
   return grouped_gemm_impl(epilogue, X, B, B2, offsets, dst_rows, row_w, Y, ldy, max_rows, K, N, E, status, stream,
                            nullptr, nullptr, 0, expected_rows, dtype, ga);
+}
+
+// Router GEMM with the top-k + softmax of every logits row done in the epilogue (declared in common.cuh; the
+// public entry point moe_router_topk validates the arguments and picks between this and the CUDA-core kernel).
+int moe::router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype,
+                          float* scores, int64_t* indices, int32_t* indices32, float* logits_out,
+                          int32_t* status, void* stream) {
+  using namespace moe::gemm;
+  if (dtype != MOE_DTYPE_BF16 && dtype != MOE_DTYPE_F16) return fail(MOE_ERR_ARG, "router_topk: unknown dtype %d", dtype);
+  if (T < 0 || H < 8 || (H % 8) || E < 8 || (E % 8) || k < 1 || k > E)
+    return fail(MOE_ERR_ARG, "router_topk: bad shape T=%lld H=%d E=%d k=%d (H, E multiples of 8)", (long long)T, H, E, k);
+  if (E > 256 || k > 8) return fail(MOE_ERR_UNSUPPORTED, "router_topk: the fused kernel takes E <= 256 and k <= 8 (E=%d k=%d)", E, k);
+  if (mode < 0 || mode > 2) return fail(MOE_ERR_ARG, "router_topk: unknown mode %d", mode);
+  if (T == 0) return MOE_OK;
+  if (T > 0x7FFFFF00ll) return fail(MOE_ERR_UNSUPPORTED, "router_topk: too many rows");
+  if (!x || !Wr || !scores || (!indices && !indices32)) return fail(MOE_ERR_ARG, "router_topk: null pointer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(Wr) | reinterpret_cast<uintptr_t>(logits_out)) & 15)
+    return fail(MOE_ERR_ARG, "router_topk: x, Wr and logits_out must be 16-byte aligned");
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  const int f16 = dtype == MOE_DTYPE_F16;
+  const int BN = E > 128 ? 256 : 128;
+  Params p;
+  p.K = H; p.N = E; p.E = 1;
+  p.num_n_tiles = 1;
+  p.num_k_blocks = (H + BK - 1) / BK;
+  p.status = status;
+  p.f16 = f16;
+  p.dense_rows = (int)T;
+  p.r_scores = scores; p.r_idx64 = indices; p.r_idx32 = indices32; p.r_logits = logits_out;
+  p.r_k = k; p.r_mode = mode;
+  CUtensorMap tA, tB;
+  rc = make_tmap(&tA, x, (uint64_t)H, (uint64_t)T, 0, (uint32_t)BM, f16);
+  if (rc) return rc;
+  rc = make_tmap(&tB, Wr, (uint64_t)H, (uint64_t)E, 1, (uint32_t)BN, f16);   // rows past E read as zeros
+  if (rc) return rc;
+  const int64_t tiles = (T + BM - 1) / BM;
+  const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (BN == 256) return launch<1, 256, EPI_ROUTER>(tA, tB, tB, p, grid, st);
+  return launch<1, 128, EPI_ROUTER>(tA, tB, tB, p, grid, st);
 }
 
 extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,

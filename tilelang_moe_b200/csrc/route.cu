@@ -239,7 +239,8 @@ combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, c
 template <bool F16, int EMAX>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, int64_t T, int vec_per_row, int E,
-                     float* __restrict__ logits) {
+                     float* __restrict__ logits, int k, int mode, float* __restrict__ scores,
+                     int64_t* __restrict__ idx64, int32_t* __restrict__ idx32) {
   extern __shared__ uint4 wsh[];   // [E][vec_per_row]
   const int lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < E * vec_per_row; i += 256) wsh[i] = __ldg(Wr + i);
@@ -273,10 +274,35 @@ router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, 
         }
       }
     }
+    float mine = 0.f;                                  // lane j ends up with the logit of expert j
 #pragma unroll
     for (int j = 0; j < EMAX; ++j) {
       const float sum = warp_sum(acc[j]);
-      if (lane == 0 && j < E) logits[t * E + j] = sum;
+      if (lane == j) mine = sum;
+    }
+    if (logits && lane < E) logits[t * E + lane] = mine;
+    if (k > 0) {
+      // fused top-k + softmax over the E <= 32 logits held one per lane: k rounds of warp arg-max, lowest
+      // lane first among equals; lane r keeps the r-th winner
+      const unsigned FULL = 0xFFFFFFFFu;
+      int key = lane < E ? float_to_ikey(mine) : (int)0x80000000;
+      int win_key = (int)0x80000000, win_idx = 0;
+      for (int r = 0; r < k; ++r) {
+        const int m = __reduce_max_sync(FULL, key);
+        const int sel = __ffs(__ballot_sync(FULL, key == m)) - 1;
+        if (lane == r) { win_key = m; win_idx = sel; }
+        if (lane == sel) key = (int)0x80000000;
+      }
+      const float vmax = ikey_to_float(__shfl_sync(FULL, win_key, 0));
+      const float e = lane < k ? expf(ikey_to_float(win_key) - vmax) : 0.f;
+      const float denom = mode == MOE_TOPK_MODE_B ? warp_sum(e) : warp_sum(lane < E ? expf(mine - vmax) : 0.f);
+      float sc = e / denom;
+      if (mode == MOE_TOPK_MODE_A_RENORM) sc = sc / warp_sum(sc);
+      if (lane < k) {
+        scores[t * k + lane] = sc;
+        if (idx64) idx64[t * k + lane] = (int64_t)win_idx;
+        if (idx32) idx32[t * k + lane] = (int32_t)win_idx;
+      }
     }
   }
 }
@@ -459,6 +485,35 @@ extern "C" int moe_combine(const void* Yk, const void* shared, const int32_t* ro
   return MOE_OK;
 }
 
+// E <= 32 experts whose weight fits shared memory: CUDA cores, one warp per token; k == 0: logits only
+static int router_small(const void* x, const void* Wr, int64_t T, int H, int E, int dtype, float* logits, int k, int mode,
+                        float* scores, int64_t* idx64, int32_t* idx32, void* stream) {
+  using namespace moe;
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  // one CTA per SM at most: every CTA stages the whole router weight
+  const size_t smem = (size_t)E * H * 2;
+  int64_t blocks = ceil_div64(T, 16);
+  if (blocks > dev.sm_count) blocks = dev.sm_count;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define MOE_RL_LAUNCH(F16_, EMAX_)                                                                                       \
+  do {                                                                                                                   \
+    if (smem > 48 * 1024)                                                                                                \
+      MOE_CUDA_CHECK(cudaFuncSetAttribute(router_logits_kernel<F16_, EMAX_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    router_logits_kernel<F16_, EMAX_><<<(unsigned)blocks, 256, smem, st>>>(                                              \
+        reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits, k, mode, scores,     \
+        idx64, idx32);                                                                                                   \
+  } while (0)
+  if (dtype == MOE_DTYPE_F16) { if (E <= 8) MOE_RL_LAUNCH(true, 8); else if (E <= 16) MOE_RL_LAUNCH(true, 16); else MOE_RL_LAUNCH(true, 32); }
+  else { if (E <= 8) MOE_RL_LAUNCH(false, 8); else if (E <= 16) MOE_RL_LAUNCH(false, 16); else MOE_RL_LAUNCH(false, 32); }
+#undef MOE_RL_LAUNCH
+  MOE_CHECK_LAUNCH("router_logits_kernel");
+  return MOE_OK;
+}
+
+static bool router_small_fits(int H, int E) { return E <= 32 && (size_t)E * H * 2 <= 200 * 1024; }
+
 extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H, int E, int dtype, float* logits,
                                  int32_t* status, void* stream) {
   using namespace moe;
@@ -468,28 +523,29 @@ extern "C" int moe_router_logits(const void* x, const void* Wr, int64_t T, int H
   if (T == 0) return MOE_OK;
   if (!x || !Wr || !logits) return fail(MOE_ERR_ARG, "router_logits: null pointer");
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(Wr)) & 15) return fail(MOE_ERR_ARG, "router_logits: pointers must be 16-byte aligned");
-  DeviceInfo dev;
-  int rc = current_device_info(&dev);
-  if (rc) return rc;
-  // one CTA per SM at most: every CTA stages the whole router weight
   if (E > 32) return fail(MOE_ERR_UNSUPPORTED, "router_logits: E=%d > 32 goes through moe_grouped_gemm (MOE_GEMM_PLAIN_F32)", E);
-  const size_t smem = (size_t)E * H * 2;
-  if (smem > 200 * 1024) return fail(MOE_ERR_UNSUPPORTED, "router_logits: E*H=%lld does not fit shared memory", (long long)E * H);
-  int64_t blocks = ceil_div64(T, 16);
-  if (blocks > dev.sm_count) blocks = dev.sm_count;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-#define MOE_RL_LAUNCH(F16_, EMAX_)                                                                                       \
-  do {                                                                                                                   \
-    if (smem > 48 * 1024)                                                                                                \
-      MOE_CUDA_CHECK(cudaFuncSetAttribute(router_logits_kernel<F16_, EMAX_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    router_logits_kernel<F16_, EMAX_><<<(unsigned)blocks, 256, smem, st>>>(                                              \
-        reinterpret_cast<const uint4*>(x), reinterpret_cast<const uint4*>(Wr), T, H / 8, E, logits);                     \
-  } while (0)
-  if (dtype == MOE_DTYPE_F16) { if (E <= 8) MOE_RL_LAUNCH(true, 8); else if (E <= 16) MOE_RL_LAUNCH(true, 16); else MOE_RL_LAUNCH(true, 32); }
-  else { if (E <= 8) MOE_RL_LAUNCH(false, 8); else if (E <= 16) MOE_RL_LAUNCH(false, 16); else MOE_RL_LAUNCH(false, 32); }
-#undef MOE_RL_LAUNCH
-  MOE_CHECK_LAUNCH("router_logits_kernel");
-  return MOE_OK;
+  if (!router_small_fits(H, E)) return fail(MOE_ERR_UNSUPPORTED, "router_logits: E*H=%lld does not fit shared memory", (long long)E * H);
+  return router_small(x, Wr, T, H, E, dtype, logits, 0, 0, nullptr, nullptr, nullptr, stream);
+}
+
+extern "C" int moe_router_topk(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype,
+                               float* scores, int64_t* indices, int32_t* indices32, float* logits_out, int32_t* status,
+                               void* stream) {
+  using namespace moe;
+  if (dtype != MOE_DTYPE_BF16 && dtype != MOE_DTYPE_F16) return fail(MOE_ERR_ARG, "router_topk: unknown dtype %d", dtype);
+  if (T < 0 || H < 8 || H % 8 || E < 1 || k < 1 || k > E)
+    return fail(MOE_ERR_ARG, "router_topk: bad shape T=%lld H=%d E=%d k=%d", (long long)T, H, E, k);
+  if (mode < 0 || mode > 2) return fail(MOE_ERR_ARG, "router_topk: unknown mode %d", mode);
+  if (T == 0) return MOE_OK;
+  if (!x || !Wr || !scores || (!indices && !indices32)) return fail(MOE_ERR_ARG, "router_topk: null pointer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(Wr) | reinterpret_cast<uintptr_t>(logits_out)) & 15)
+    return fail(MOE_ERR_ARG, "router_topk: x, Wr and logits_out must be 16-byte aligned");
+  if (router_small_fits(H, E))
+    return router_small(x, Wr, T, H, E, dtype, logits_out, k, mode, scores, indices, indices32, stream);
+  if (E % 8 || E < 8 || E > 256 || k > 8)
+    return fail(MOE_ERR_UNSUPPORTED, "router_topk: fused kernels take E <= 32 (small H), or E %% 8 == 0, E <= 256, k <= 8 "
+                "(E=%d k=%d): use moe_router_logits / moe_grouped_gemm + moe_topk_softmax", E, k);
+  return router_topk_gemm(x, Wr, T, H, E, k, mode, dtype, scores, indices, indices32, logits_out, status, stream);
 }
 
 extern "C" int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets, int32_t* src_row,

@@ -152,28 +152,6 @@ static int launch_warp(const float* logits, int64_t M, int N, int64_t ld, int k,
 constexpr int TILE_THREADS = 128;
 constexpr int TILE_FLOATS = 128 * 128;      // staged floats per tile (rows x row length <= this)
 
-__device__ __forceinline__ int float_to_ikey(float x) {
-  const int b = __float_as_int(x + 0.0f);
-  return b ^ ((b >> 31) & 0x7FFFFFFF);
-}
-__device__ __forceinline__ float ikey_to_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7FFFFFFF)); }
-
-template <int K>
-__device__ __forceinline__ void list_insert(int (&kv)[K], int (&ki)[K], int ck, int ci) {
-  // shift chain: the candidate enters at the first entry it strictly exceeds (equal keys keep the earlier column
-  // ahead); from there on every entry moves down one place, so entries that tie with each other keep their order
-  bool p = false;
-#pragma unroll
-  for (int j = 0; j < K; ++j) {
-    p = p || (ck > kv[j]);
-    const int tv = kv[j], ti = ki[j];
-    kv[j] = p ? ck : tv;
-    ki[j] = p ? ci : ti;
-    ck = p ? tv : ck;
-    ci = p ? ti : ci;
-  }
-}
-
 template <int K, int TPR>
 __global__ void __launch_bounds__(TILE_THREADS)
 topk_tile_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld, int k, int mode, int rows_per_tile,

@@ -159,9 +159,10 @@ def moe_forward(x: torch.Tensor, router_weight: Optional[torch.Tensor], shared_g
             shared_out = shared_forward(x_flat, shared_gate, shared_up, shared_down, ws)
             shared_ready = torch.cuda.Event()
             shared_ready.record(side)
-    if logits is None:
-        logits = ops.router_logits(x_flat, router_weight, out=ws.logits)
-    scores, idx32 = ops.topk_softmax(logits, k, mode="A", index_dtype=torch.int32)
+    if logits is None:     # router GEMM + top-k + softmax: one kernel when the shape allows, logits never stored
+        scores, idx32 = ops.router_topk_softmax(x_flat, router_weight, k, mode="A", index_dtype=torch.int32)
+    else:
+        scores, idx32 = ops.topk_softmax(logits, k, mode="A", index_dtype=torch.int32)
     y = routed_forward(x_flat, scores, idx32, routed_gate, routed_up, routed_down, ws, shared_out=shared_out,
                        out=None if out is None else out.view(T, H), shared_ready=shared_ready)
     y = y.view(*shape)

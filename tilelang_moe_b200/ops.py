@@ -247,7 +247,7 @@ def _offsets_0_T(T: int, device: torch.device) -> torch.Tensor:
 
 def router_logits(x: torch.Tensor, router_weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 logits [T,E] = x [T,H] . Wr[E,H]^T from 16-bit inputs, fp32 accumulate.
-    Few experts (E < 32): one warp per token on CUDA cores.  Otherwise the tcgen05 GEMM with fp32 output
+    Few experts (E <= 32, weight within 200 KB): one warp per token on CUDA cores.  Otherwise the tcgen05 GEMM with fp32 output
     (the router weight is one dense group [1,E,H])."""
     _need_cuda(x, router_weight)
     dt = _dtype_code(x, router_weight)
@@ -257,7 +257,8 @@ def router_logits(x: torch.Tensor, router_weight: torch.Tensor, out: Optional[to
         out = torch.empty(T, E, dtype=torch.float32, device=x.device)
     x = x.contiguous()
     router_weight = router_weight.contiguous()
-    if E >= 32 and E % 8 == 0 and T > 0:
+    small = E <= 32 and E * H * 2 <= 200 * 1024        # the whole router weight fits one CTA's shared memory
+    if not small and E % 8 == 0 and T > 0:
         return grouped_gemm_sorted(GEMM_PLAIN_F32, x, router_weight.unsqueeze(0), _offsets_0_T(T, x.device), out=out)
     with torch.cuda.device(x.device):
         rc = _lib.load().moe_router_logits(_ptr(x), _ptr(router_weight), T, H, E, dt, _ptr(out),
@@ -266,10 +267,51 @@ def router_logits(x: torch.Tensor, router_weight: torch.Tensor, out: Optional[to
     return out
 
 
-def router_topk_softmax(x: torch.Tensor, router_weight: torch.Tensor, k: int, mode="B"):
-    """Router GEMM followed by top-k + softmax (reference kernels/router_gemm_topk_softmax.py computes the same
-    pair in one kernel; here the [T,E] fp32 logits make one round trip through L2)."""
-    return topk_softmax(router_logits(x, router_weight), k, mode=mode)
+def router_topk_fused_supported(H: int, E: int, k: int) -> bool:
+    """Shapes the one-kernel router (moe_router_topk) takes; others run as router_logits + topk_softmax."""
+    if H % 8 or k < 1 or k > E:
+        return False
+    if E <= 32 and E * H * 2 <= 200 * 1024:
+        return True
+    return E % 8 == 0 and 8 <= E <= 256 and k <= 8
+
+
+def router_topk_softmax(x: torch.Tensor, router_weight: torch.Tensor, k: int, mode="B",
+                        index_dtype: torch.dtype = torch.int64, logits_out: Optional[torch.Tensor] = None,
+                        fused: Optional[bool] = None):
+    """scores, indices of top-k + softmax over the router logits x . Wr^T (reference
+    kernels/router_gemm_topk_softmax.py computes the same pair in one kernel).  One launch when the shape allows
+    (CUDA cores for E <= 32, else the tcgen05 GEMM with the selection in its epilogue): the [T,E] logits are only
+    written if ``logits_out`` is given.  Other shapes: router GEMM, then topk_softmax on its fp32 logits.
+    ``fused``: None = pick by shape, True / False = force the one-kernel / two-kernel path."""
+    _need_cuda(x, router_weight)
+    T, H = x.shape
+    E = router_weight.shape[0]
+    if fused is None:
+        # Measured on B200: with few row tiles the selection in the epilogue is not hidden behind another tile's
+        # main loop, and the separate top-k kernel (all SMs) is quicker; from about 32 tokens per expert the single
+        # kernel wins (T=16384: 93 vs 124 us at E=256, 44 vs 48 us at E=64).  Few experts: always one kernel.
+        fused = E <= 64 or T >= 32 * E
+    if not fused or not router_topk_fused_supported(H, E, k) or T == 0:
+        return topk_softmax(router_logits(x, router_weight, out=logits_out), k, mode=mode, index_dtype=index_dtype)
+    dt = _dtype_code(x, router_weight)
+    if index_dtype not in (torch.int64, torch.int32):
+        raise ValueError("index_dtype must be int64 or int32")
+    x = x.contiguous()
+    router_weight = router_weight.contiguous()
+    if logits_out is not None and (logits_out.shape != (T, E) or logits_out.dtype != torch.float32
+                                   or not logits_out.is_contiguous()):
+        raise ValueError("logits_out must be a contiguous fp32 [T,E] tensor")
+    scores = torch.empty(T, k, dtype=torch.float32, device=x.device)
+    idx = torch.empty(T, k, dtype=index_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().moe_router_topk(_ptr(x), _ptr(router_weight), T, H, E, k, _MODES[mode], dt,
+                                         _ptr(scores), _ptr(idx) if index_dtype == torch.int64 else None,
+                                         _ptr(idx) if index_dtype == torch.int32 else None, _ptr(logits_out),
+                                         _ptr(status_buffer(x.device)), _stream())
+    _lib.check(rc, "moe_router_topk")
+    _after(x.device)
+    return scores, idx
 
 
 def ep_regroup(recv_counts: torch.Tensor, n_recv_bound: int):
