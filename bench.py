@@ -626,13 +626,81 @@ def run_gemm_grid(args):
                       "results": results}), flush=True)
 
 
+def run_mhc(args):
+    """mHC pre / post blocks on the reference benchmark's four shapes (benchmarks/benchmark_mhc.py:66-73 of the
+    reference; hc_mult = 4, value distributions of its generators).  Per point: median CUDA-event time of one call
+    (L2 flushed before it), algorithmic bytes / time against the measured copy bandwidth, parity of the first 32
+    tokens against the oracle.  pre = 2 launches (split-K tensor-core GEMM, finishing kernel), post = 1 launch.
+    Algorithmic bytes - pre: residual read once + layer_input written; post: x and residual read, output written."""
+    from oracle import moe_oracle as O
+    from tilelang_moe_b200 import _lib, kernels, ops
+    _lib.load()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    iters = args.steps if args.steps > 10 else 50
+    published = {"Config-1": (22.7, 10.7), "Config-2": (31.3, 22.1), "Config-3": (76.4, 57.5), "Config-4": (264.0, 207.1)}
+    results = []
+    for name, T, H, hc in (("Config-1", 512, 1280, 4), ("Config-2", 1024, 2560, 4), ("Config-3", 2048, 4096, 4),
+                           ("Config-4", 8192, 4096, 4)):
+        if args.only and name not in args.only.split(","):
+            continue
+        d = O.make_mhc_inputs(T, H, hc, seed=42)
+        g = {k_: v.to(dev) for k_, v in d.items()}
+        fn3 = ops.mhc_split_weights(g["fn"])
+        ws = torch.empty(max(_lib.load().moe_mhc_pre_workspace(T, hc, H), 16), dtype=torch.uint8, device=dev)
+
+        def pre():
+            return ops.mhc_pre(g["residual"], fn3, g["hc_scale"], g["hc_base"], workspace=ws)
+
+        def post():
+            return ops.mhc_post(g["x"], g["residual"], g["post_layer_mix"], g["comb_res_mix"])
+
+        row = {"name": name, "T": T, "hidden": H, "hc_mult": hc}
+        for label, fn_, byts in (("pre", pre, T * (hc * H + H) * 2 + T * (hc + hc * hc) * 4),
+                                 ("post", post, T * (H + 2 * hc * H) * 2 + T * (hc + hc * hc) * 4)):
+            for _ in range(3):
+                fn_()
+            times = []
+            for _ in range(iters):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn_()
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b) * 1e3)
+            us = statistics.median(times)
+            row[label + "_us"] = round(us, 2)
+            row[label + "_GBps"] = round(byts / us / 1e3, 1)
+            row[label + "_frac_hbm_measured"] = round(byts / us / 1e3 / peaks["hbm_gbs"], 3)
+        ops.check_status(dev)
+        n = min(T, 32)
+        ref = O.mhc_pre(d["residual"][:n], d["fn"], d["hc_scale"], d["hc_base"], accumulate=torch.float64)
+        got = pre()
+        err_pre = max(float((got[0][:n].cpu() - ref[0]).abs().max()), float((got[1][:n].cpu() - ref[1]).abs().max()))
+        err_li = float(((got[2][:n].cpu().float() - ref[2].float()).abs() / (ref[2].float().abs() + 1e-3)).max())
+        refo = O.mhc_post(d["x"][:n], d["residual"][:n], d["post_layer_mix"][:n], d["comb_res_mix"][:n])
+        err_post = float(((post()[:n].cpu().float() - refo.float()).abs() / (refo.float().abs() + 1e-3)).max())
+        row.update({"pre_mix_abs_err": err_pre, "layer_input_rel_err": round(err_li, 5), "post_rel_err": round(err_post, 5),
+                    "parity_ok": err_pre < 1e-5 and err_li <= 2 ** -7 and err_post <= 2 ** -7,
+                    "reference_published_us_other_hw": {"pre": published[name][0], "post": published[name][1]}})
+        results.append(row)
+    print(json.dumps({"metric": "mhc_pre_us", "unit": "us", "value": results[-1]["pre_us"], "higher_is_better": False,
+                      "n_gpus": 1, "dtype": "bf16 data, fp32 arithmetic", "data": "synthetic",
+                      "config": {"workload": "mhc: pre and post blocks, reference benchmark shapes, hc_mult=4"},
+                      "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                      "parity_ok": all(r["parity_ok"] for r in results), "results": results}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router", "gemm_grid"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router", "gemm_grid", "mhc"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
@@ -646,6 +714,8 @@ def main():
         return run_router(args)
     if args.workload == "gemm_grid":
         return run_gemm_grid(args)
+    if args.workload == "mhc":
+        return run_mhc(args)
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, cfg)

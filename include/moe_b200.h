@@ -203,6 +203,29 @@ int moe_router_topk(const void* x, const void* Wr, int64_t T, int H, int E, int 
 int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets,
                    int32_t* src_row, void* stream);
 
+/* ---- mHC pre / post blocks ---------------------------------------------------------------
+ * The operators on either side of the MoE layer in the model the reference targets
+ * (kernels/mhc_baseline.py:48-163; recommended entry points kernels/mhc_tilelang.py:494-582).
+ *   R = 2*hc_mult + hc_mult^2, K = hc_mult*hidden.  hc_mult 2 or 4, hidden % 8 == 0, K*2 <= 200 KB.
+ * moe_mhc_split_weights: fn fp32 [R, K] -> fn3 bf16 [3*R, K] = hi, mid, lo with hi+mid+lo = fn to 24 bits;
+ *   done once per weight, lets the skinny GEMM run on the tensor cores in bf16 at fp32 accuracy.
+ * moe_mhc_pre: residual bf16 [T, hc_mult, hidden] ->
+ *   post_mix fp32 [T, hc_mult], comb_mix fp32 [T, hc_mult, hc_mult], layer_input bf16 [T, hidden].
+ *   mixes = (residual_flat . fn^T) * rsqrt(mean(residual_flat^2) + rms_eps) * scale + base;
+ *   pre = sigmoid(mixes[:hc]) + hc_pre_eps; post_mix = sigmoid(mixes[hc:2hc]) * hc_post_mult_value;
+ *   comb_mix = Sinkhorn(mixes[2hc:], sinkhorn_repeat, hc_sinkhorn_eps); layer_input = sum_m pre[m]*residual[m].
+ *   ws: moe_mhc_pre_workspace(T, hc_mult, hidden) bytes of device scratch (the split-K slices of the GEMM).
+ * moe_mhc_post: out bf16 [T, hc_mult, hidden] = x[T,hidden] * post_layer_mix[T,hc] + comb_res_mix[T,hc,hc]^T @ residual.
+ */
+size_t moe_mhc_pre_workspace(int64_t T, int hc_mult, int64_t hidden);
+int moe_mhc_split_weights(const float* fn, int rows, int64_t K, void* fn3, void* stream);
+int moe_mhc_pre(const void* residual, const void* fn3, const float* hc_scale, const float* hc_base, int64_t T,
+                int hc_mult, int64_t hidden, float rms_eps, float hc_pre_eps, float hc_sinkhorn_eps,
+                float hc_post_mult_value, int sinkhorn_repeat, void* ws, size_t ws_bytes, float* post_mix,
+                float* comb_mix, void* layer_input, int32_t* status, void* stream);
+int moe_mhc_post(const void* x, const void* residual, const float* post_layer_mix, const float* comb_res_mix,
+                 int64_t T, int hc_mult, int64_t hidden, void* out, void* stream);
+
 /* ---- expert parallelism over peer memory ---------------------------------------------
  * No counterpart in the reference.  cnt_all int32 [G][G*E_local]: cnt_all[s][v] = rows that
  * source rank s routes to virtual expert v = dest_rank*E_local + slot (all-gather of the

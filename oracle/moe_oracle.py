@@ -263,3 +263,64 @@ def zipf_logits(T: int, E: int, s: float = 1.1, seed: int = 0) -> torch.Tensor:
     u = torch.rand(T, E, generator=g, dtype=torch.float64).clamp_(1e-12, 1 - 1e-12)
     gumbel = -(-(u.log())).log()
     return (logp[None, :] + gumbel).to(torch.float32)
+
+
+# ----------------------------------------------------------------------------- mHC pre / post blocks
+def sinkhorn(x: torch.Tensor, repeat: int, eps: float) -> torch.Tensor:
+    """Row softmax + eps, a column normalisation, then (repeat-1) x [row normalisation, column normalisation],
+    every divisor with + eps (reference kernels/mhc_baseline.py:18-43).  x fp32 [..., hc, hc]."""
+    x = torch.softmax(x, dim=-1) + eps
+    x = x / (x.sum(dim=-2, keepdim=True) + eps)
+    for _ in range(repeat - 1):
+        x = x / (x.sum(dim=-1, keepdim=True) + eps)
+        x = x / (x.sum(dim=-2, keepdim=True) + eps)
+    return x
+
+
+def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, hc_scale: torch.Tensor, hc_base: torch.Tensor,
+            rms_eps: float = 1e-6, hc_pre_eps: float = 1e-6, hc_sinkhorn_eps: float = 1e-6,
+            hc_post_mult_value: float = 1.0, sinkhorn_repeat: int = 10, accumulate=torch.float32):
+    """mHC pre block (reference kernels/mhc_baseline.py:48-128).  residual bf16 [T, hc, hidden], fn fp32
+    [2hc+hc*hc, hc*hidden], hc_scale fp32 [3], hc_base fp32 [2hc+hc*hc] ->
+    post_mix fp32 [T,hc,1], comb_mix fp32 [T,hc,hc], layer_input bf16 [T,hidden].
+    ``accumulate=torch.float64`` evaluates the dot products and the sum of squares in double precision (the
+    yardstick the GPU tests use; the default follows the reference's fp32 evaluation)."""
+    T, hc, hidden = residual.shape
+    flat = residual.reshape(T, hc * hidden).to(accumulate)
+    sqrsum = flat.square().sum(-1)
+    rms = (sqrsum / fn.shape[-1] + rms_eps).rsqrt()
+    mixes = ((flat @ fn.to(accumulate).T) * rms.unsqueeze(-1)).float()
+    scale = torch.cat([hc_scale[0].expand(hc), hc_scale[1].expand(hc), hc_scale[2].expand(hc * hc)])
+    mixes = mixes * scale + hc_base
+    pre = mixes[:, :hc].sigmoid().unsqueeze(-1) + hc_pre_eps
+    post = (mixes[:, hc:2 * hc].sigmoid() * hc_post_mult_value).unsqueeze(-1)
+    comb = sinkhorn(mixes[:, 2 * hc:].reshape(T, hc, hc), sinkhorn_repeat, hc_sinkhorn_eps)
+    layer_input = (residual * pre).sum(-2).bfloat16()
+    return post, comb, layer_input
+
+
+def mhc_post(x: torch.Tensor, residual: torch.Tensor, post_layer_mix: torch.Tensor, comb_res_mix: torch.Tensor):
+    """mHC post block (reference kernels/mhc_baseline.py:136-163): x bf16 [T,hidden], residual bf16 [T,hc,hidden],
+    post_layer_mix fp32 [T,hc,1], comb_res_mix fp32 [T,hc,hc] -> bf16 [T,hc,hidden] =
+    x * post_layer_mix + comb_res_mix^T @ residual, evaluated in fp32."""
+    term1 = x.float().unsqueeze(-2) * post_layer_mix
+    term2 = torch.bmm(comb_res_mix.transpose(1, 2), residual.float())
+    return (term1 + term2).bfloat16()
+
+
+def make_mhc_inputs(num_tokens: int, hidden: int, hc: int = 4, seed: int = 42):
+    """Seeded mHC inputs with the value distributions of the reference benchmark
+    (benchmarks/benchmark_mhc.py:79-108): residual ~ N(0,1)*(1+0.01*m) in bf16, fn ~ 1e-4*N(0,1)*(1+0.01*m) in fp32,
+    hc_scale, hc_base ~ 0.1*N(0,1); post-block inputs ~ N(0,1).  Drawn on the CPU."""
+    g = torch.Generator().manual_seed(seed)
+    r3 = 2 * hc + hc * hc
+    ramp = (1 + torch.arange(hc).mul(0.01)).view(1, -1, 1)
+    residual = (torch.randn(num_tokens, hc, hidden, generator=g) * ramp).bfloat16()
+    fn = (torch.randn(r3, hc, hidden, generator=g) * 1e-4 * ramp).flatten(1, 2).contiguous()
+    hc_scale = torch.randn(3, generator=g) * 0.1
+    hc_base = torch.randn(r3, generator=g) * 0.1
+    x = torch.randn(num_tokens, hidden, generator=g).bfloat16()
+    post_layer_mix = torch.randn(num_tokens, hc, 1, generator=g)
+    comb_res_mix = torch.randn(num_tokens, hc, hc, generator=g)
+    return dict(residual=residual, fn=fn, hc_scale=hc_scale, hc_base=hc_base, x=x, post_layer_mix=post_layer_mix,
+                comb_res_mix=comb_res_mix)

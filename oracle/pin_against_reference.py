@@ -154,6 +154,27 @@ def pin_fusedmoe(ref):
                         topk_scores=sc.numpy(), **fix)
 
 
+def pin_mhc(ref):
+    """mHC pre / post: the oracle must reproduce the reference's PyTorch functions bit for bit on CPU (same ops in
+    the same order); the reference's outputs become the fixture."""
+    d = O.make_mhc_inputs(24, 256, 4, seed=42)
+    kw = dict(rms_eps=1e-6, hc_pre_eps=1e-6, hc_sinkhorn_eps=1e-6, hc_post_mult_value=1.0, sinkhorn_repeat=10)
+    # larger mixing weights than the benchmark's 1e-4 so that sigmoid / Sinkhorn see a real spread
+    d["fn"] = d["fn"] * 300.0
+    rp, rc, rl = ref.mhc_pre_pytorch(d["residual"], d["fn"], d["hc_scale"], d["hc_base"], **kw)
+    op, oc, ol = O.mhc_pre(d["residual"], d["fn"], d["hc_scale"], d["hc_base"], **kw)
+    assert torch.equal(rp, op) and torch.equal(rc, oc) and torch.equal(rl, ol), "mhc_pre drifted from the reference"
+    assert (rc.sum(-1) - 1).abs().max() < 1e-4 and (rc.sum(-2) - 1).abs().max() < 1e-4
+    ro = ref.mhc_post_pytorch(d["x"], d["residual"], d["post_layer_mix"], d["comb_res_mix"])
+    oo = O.mhc_post(d["x"], d["residual"], d["post_layer_mix"], d["comb_res_mix"])
+    assert torch.equal(ro, oo), "mhc_post drifted from the reference"
+    np.savez_compressed(GOLDEN / "mhc.npz", residual=_bf16_bits(d["residual"]), fn=d["fn"].numpy(),
+                        hc_scale=d["hc_scale"].numpy(), hc_base=d["hc_base"].numpy(), x=_bf16_bits(d["x"]),
+                        post_layer_mix=d["post_layer_mix"].numpy(), comb_res_mix=d["comb_res_mix"].numpy(),
+                        ref_post_mix=rp.numpy(), ref_comb_mix=rc.numpy(), ref_layer_input=_bf16_bits(rl),
+                        ref_post_out=_bf16_bits(ro))
+
+
 def main():
     ref_dir = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MOE_REFERENCE_DIR", ""))
     if not (ref_dir / "kernels" / "topk_softmax_baseline.py").is_file():
@@ -164,6 +185,7 @@ def main():
     pin_histogram()
     pin_grouped_gemm(_load(ref_dir, "grouped_gemm_baseline"))
     pin_fusedmoe(_load(ref_dir, "fusedmoe_baseline"))
+    pin_mhc(_load(ref_dir, "mhc_baseline"))
     print("oracle pinned; fixtures written to", GOLDEN)
 
 

@@ -113,3 +113,21 @@ def test_zipf_logits_are_skewed():
 def test_benchmark_input_recipe_matches_the_oracle_copy():
     from tilelang_moe_b200 import inputs
     assert torch.equal(inputs.zipf_logits(300, 64, 1.1, seed=5), O.zipf_logits(300, 64, 1.1, seed=5))
+
+
+def test_mhc_oracle_matches_the_reference_fixture():
+    """oracle.mhc_pre / mhc_post reproduce, bit for bit, what the reference's kernels/mhc_baseline.py produced on the
+    same inputs (outputs stored by oracle/pin_against_reference.py)."""
+    g = np.load(GOLDEN / "mhc.npz")
+    bf = lambda a: torch.from_numpy(a.copy()).view(torch.bfloat16)
+    residual, fn = bf(g["residual"]), torch.from_numpy(g["fn"])
+    post, comb, li = O.mhc_pre(residual, fn, torch.from_numpy(g["hc_scale"]), torch.from_numpy(g["hc_base"]))
+    assert torch.equal(post, torch.from_numpy(g["ref_post_mix"]))
+    assert torch.equal(comb, torch.from_numpy(g["ref_comb_mix"]))
+    assert torch.equal(li, bf(g["ref_layer_input"]))
+    out = O.mhc_post(bf(g["x"]), residual, torch.from_numpy(g["post_layer_mix"]), torch.from_numpy(g["comb_res_mix"]))
+    assert torch.equal(out, bf(g["ref_post_out"]))
+    # the double-precision yardstick used by the GPU tests stays within fp32 rounding of the fp32 evaluation
+    p64, c64, _ = O.mhc_pre(residual, fn, torch.from_numpy(g["hc_scale"]), torch.from_numpy(g["hc_base"]),
+                            accumulate=torch.float64)
+    assert (p64 - post).abs().max() < 1e-5 and (c64 - comb).abs().max() < 1e-5

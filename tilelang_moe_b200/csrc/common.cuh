@@ -96,4 +96,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 int router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype, float* scores,
                      int64_t* indices, int32_t* indices32, float* logits_out, int32_t* status, void* stream);
 
+// bf16 split-K GEMM with fp32 slices (gemm_sm100.cu): Y[T, S*N], N <= 128, K % (64*S) == 0
+int gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S, float* Y, int32_t* status, void* stream);
+
 }  // namespace moe

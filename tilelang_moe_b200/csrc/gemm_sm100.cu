@@ -115,6 +115,11 @@ struct Params {
   int32_t* r_idx32 = nullptr;
   float* r_logits = nullptr;     // optional fp32 [rows, N] copy of the logits
   int r_k = 0, r_mode = 0;
+  // 128-row kernel: bytes the B box(es) of one stage bring (a box may have fewer rows than the tile has columns)
+  int b_tx_bytes = 0;
+  // split-K (plain fp32 output only): the N-tile index counts K slices of num_k_blocks blocks each; slice s of
+  // row r lands in columns [s*N, (s+1)*N) of Y and the caller adds the slices
+  int ksplit = 0;
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -393,20 +398,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
-      const int n0 = t.n_tile * OUT_COLS;
+      const int n0 = p.ksplit ? 0 : t.n_tile * OUT_COLS;
+      const int k0 = p.ksplit ? t.n_tile * NKB * BK : 0;        // first K element of this tile's slice
       for (int kb = 0; kb < NKB; ++kb) {
         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
         if (lane == 0) {
           const uint32_t full = full0 + 8 * stage;
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
           const uint32_t sb = sa + C::A_BYTES;
-          mbar_arrive_expect_tx(full, gather ? C::B_BYTES : C::STAGE_BYTES);
-          if (!gather) tma_load_2d(sa, &tmA, full, kb * BK, t.row0);
+          mbar_arrive_expect_tx(full, gather ? p.b_tx_bytes : C::A_BYTES + p.b_tx_bytes);
+          if (!gather) tma_load_2d(sa, &tmA, full, k0 + kb * BK, t.row0);
           if (EPI == MOE_GEMM_SILU_GATE) {
             tma_load_3d(sb, &tmB, full, kb * BK, n0, t.e);
             tma_load_3d(sb + C::B_BYTES / 2, &tmB2, full, kb * BK, n0, t.e);
           } else {
-            tma_load_3d(sb, &tmB, full, kb * BK, n0, t.e);
+            tma_load_3d(sb, &tmB, full, k0 + kb * BK, n0, t.e);
           }
         }
         __syncwarp();
@@ -534,7 +540,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (half == 1 && t.row0 + BM >= t.row_end) break;   // nothing was accumulated for rows 128..255
       const int grow = t.row0 + half * BM + q * 32 + lane;   // sorted row handled by this thread
       const bool row_ok = grow < t.row_end;
-      const int n0 = t.n_tile * OUT_COLS;
+      const int n0 = p.ksplit ? 0 : t.n_tile * OUT_COLS;
       int64_t out_row = grow;
       float w = 1.0f;
       void* ybase = p.Y;
@@ -659,7 +665,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         } else
         if (row_ok && col < p.N) {
           if (EPI == MOE_GEMM_PLAIN_F32) {
-            float* dst = reinterpret_cast<float*>(p.Y) + out_row * p.ldy + col;
+            float* dst = reinterpret_cast<float*>(p.Y) + out_row * p.ldy + col + (p.ksplit ? t.n_tile * p.N : 0);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               if (col + j * 4 < p.N)
@@ -1399,13 +1405,44 @@ int moe::router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E
   CUtensorMap tA, tB;
   rc = make_tmap(&tA, x, (uint64_t)H, (uint64_t)T, 0, (uint32_t)BM, f16);
   if (rc) return rc;
-  rc = make_tmap(&tB, Wr, (uint64_t)H, (uint64_t)E, 1, (uint32_t)BN, f16);   // rows past E read as zeros
+  rc = make_tmap(&tB, Wr, (uint64_t)H, (uint64_t)E, 1, (uint32_t)E, f16);    // only the E weight rows are fetched
   if (rc) return rc;
+  p.b_tx_bytes = E * BK * 2;
   const int64_t tiles = (T + BM - 1) / BM;
   const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (BN == 256) return launch<1, 256, EPI_ROUTER>(tA, tB, tB, p, grid, st);
   return launch<1, 128, EPI_ROUTER>(tA, tB, tB, p, grid, st);
+}
+
+// Y[T, S*N] fp32: slice s of the K dimension of A[T,K] . B[N,K]^T in columns [s*N, (s+1)*N) (declared in common.cuh).
+// Split-K gives a skinny GEMM (few row tiles, long K) one tile per SM; the caller adds the S slices.
+int moe::gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S, float* Y, int32_t* status,
+                         void* stream) {
+  using namespace moe::gemm;
+  if (T < 1 || N < 8 || N > 128 || (N % 8) || S < 1 || K < 8 || (K % 8) || (S > 1 && (K % (64 * S))))
+    return fail(MOE_ERR_ARG, "gemm_splitk: bad shape T=%lld K=%d N=%d S=%d", (long long)T, K, N, S);
+  if (T > 0x7FFFFF00ll) return fail(MOE_ERR_UNSUPPORTED, "gemm_splitk: too many rows");
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  Params p;
+  p.K = K; p.N = N; p.E = 1;
+  p.num_n_tiles = S;
+  p.num_k_blocks = (K / S + BK - 1) / BK;
+  p.ksplit = S > 1;
+  p.status = status;
+  p.dense_rows = (int)T;
+  p.Y = Y; p.ldy = (int64_t)S * N;
+  p.b_tx_bytes = N * BK * 2;
+  CUtensorMap tA, tB;
+  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)T, 0, (uint32_t)BM, 0);
+  if (rc) return rc;
+  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)N, 0);
+  if (rc) return rc;
+  const int64_t tiles = ((T + BM - 1) / BM) * S;
+  const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
+  return launch<1, 128, MOE_GEMM_PLAIN_F32>(tA, tB, tB, p, grid, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
@@ -1537,7 +1574,11 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   const uint64_t a_map_rows = ga.idx ? (uint64_t)ga.src_rows : (uint64_t)max_rows;
   rc = make_tmap(&tA, A, (uint64_t)K, a_map_rows, 0, (uint32_t)(pair ? BM : MT * BM), f16);
   if (rc) return rc;
-  const uint32_t b_box_rows = pair ? 128u : (uint32_t)out_cols;   // a CTA of a pair stages 128 N rows
+  uint32_t b_box_rows = pair ? 128u : (uint32_t)out_cols;   // a CTA of a pair stages 128 N rows
+  // fewer weight rows than tile columns: fetch only those (the rest of the B stage keeps whatever it held; the
+  // accumulator columns it feeds are never stored)
+  if (!pair && !gate && N < out_cols) b_box_rows = (uint32_t)N;
+  p.b_tx_bytes = (int)b_box_rows * BK * 2 * (gate ? 2 : 1);
   rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows, f16);
   if (rc) return rc;
   tB2 = tB;

@@ -8,6 +8,8 @@ Same names, argument order and return types as the reference's public API
     fusedmoe_tilelang(x, router_weight, ...)      kernels/fusedmoe_tilelang.py:605-647
     FusedMoETileLang(...).forward(...)            kernels/fusedmoe_tilelang.py:241-417
     generate_fusedmoe_inputs(...)                 kernels/fusedmoe_baseline.py:311-375
+    mhc_pre(residual, fn, hc_scale, hc_base, ...) kernels/mhc_tilelang.py:494-545
+    mhc_post(x, residual, post_mix, comb_mix)     kernels/mhc_tilelang.py:575-582
 
 Everything runs on the CUDA library behind ``include/moe_b200.h``; there is no
 strategy auto-selection between back ends and no CPU path.  Deliberate
@@ -28,7 +30,7 @@ from .. import ops as _ops
 
 __all__ = [
     "topk_softmax", "topk_softmax_best", "grouped_gemm", "grouped_gemm_best", "fusedmoe_tilelang", "fusedmoe",
-    "FusedMoETileLang", "FusedMoE", "generate_fusedmoe_inputs", "route_histogram",
+    "FusedMoETileLang", "FusedMoE", "generate_fusedmoe_inputs", "route_histogram", "mhc_pre", "mhc_post",
 ]
 
 
@@ -187,3 +189,30 @@ def generate_fusedmoe_inputs(batch_size: int, seq_len: int, d_hidden: int, d_exp
         "routed_down": draw(n_routed_experts, d_hidden, d_expert) / math.sqrt(d_expert),
     }
     return x, weights
+
+
+_mhc_split_cache: Dict[tuple, torch.Tensor] = {}
+
+
+def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, hc_scale: torch.Tensor, hc_base: torch.Tensor,
+            rms_eps: float = 1e-6, hc_pre_eps: float = 1e-6, hc_sinkhorn_eps: float = 1e-6,
+            hc_post_mult_value: float = 1.0, sinkhorn_repeat: int = 10):
+    """mHC pre block, arguments and results as the reference's ``mhc_pre`` (kernels/mhc_tilelang.py:494-545):
+    residual bf16 (num_tokens, hc_mult, hidden), fn fp32 (2*hc+hc*hc, hc*hidden), hc_scale fp32 (3,), hc_base fp32
+    (2*hc+hc*hc,) -> (post_mix fp32 (T,hc,1), comb_mix fp32 (T,hc,hc), layer_input bf16 (T,hidden)).
+    The bf16 split of ``fn`` is built on first use and cached per weight tensor (and its version counter)."""
+    key = (fn.data_ptr(), fn._version, tuple(fn.shape), fn.device)
+    fn3 = _mhc_split_cache.get(key)
+    if fn3 is None:
+        if len(_mhc_split_cache) > 64:
+            _mhc_split_cache.clear()
+        fn3 = _ops.mhc_split_weights(fn)
+        _mhc_split_cache[key] = fn3
+    return _ops.mhc_pre(residual, fn3, hc_scale, hc_base, rms_eps, hc_pre_eps, hc_sinkhorn_eps, hc_post_mult_value,
+                        sinkhorn_repeat)
+
+
+def mhc_post(x: torch.Tensor, residual: torch.Tensor, post_layer_mix: torch.Tensor,
+             comb_res_mix: torch.Tensor) -> torch.Tensor:
+    """mHC post block (reference kernels/mhc_tilelang.py:575-582): bf16 (T, hc_mult, hidden)."""
+    return _ops.mhc_post(x, residual, post_layer_mix, comb_res_mix)

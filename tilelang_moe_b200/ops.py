@@ -314,6 +314,73 @@ def router_topk_softmax(x: torch.Tensor, router_weight: torch.Tensor, k: int, mo
     return scores, idx
 
 
+# ----------------------------------------------------------------------------- mHC pre / post blocks
+def mhc_split_weights(fn: torch.Tensor) -> torch.Tensor:
+    """fn fp32 [R, K] -> bf16 [3R, K] (hi, mid, lo; hi + mid + lo == fn to 24 bits).  Once per weight."""
+    _need_cuda(fn)
+    if fn.dtype != torch.float32 or fn.dim() != 2:
+        raise ValueError("fn must be a 2-D float32 tensor")
+    fn = fn.contiguous()
+    R, K = fn.shape
+    fn3 = torch.empty(3 * R, K, dtype=torch.bfloat16, device=fn.device)
+    with torch.cuda.device(fn.device):
+        rc = _lib.load().moe_mhc_split_weights(_ptr(fn), R, K, _ptr(fn3), _stream())
+    _lib.check(rc, "moe_mhc_split_weights")
+    return fn3
+
+
+def mhc_pre(residual: torch.Tensor, fn3: torch.Tensor, hc_scale: torch.Tensor, hc_base: torch.Tensor,
+            rms_eps: float = 1e-6, hc_pre_eps: float = 1e-6, hc_sinkhorn_eps: float = 1e-6,
+            hc_post_mult_value: float = 1.0, sinkhorn_repeat: int = 10, workspace: Optional[torch.Tensor] = None):
+    """mHC pre block on split weights (mhc_split_weights(fn)).  residual bf16 [T, hc, hidden] ->
+    (post_mix fp32 [T,hc,1], comb_mix fp32 [T,hc,hc], layer_input bf16 [T,hidden])."""
+    _need_cuda(residual, fn3, hc_scale, hc_base)
+    if residual.dtype != torch.bfloat16 or residual.dim() != 3:
+        raise ValueError("residual must be bfloat16 [T, hc_mult, hidden]")
+    T, hc, hidden = residual.shape
+    R = 2 * hc + hc * hc
+    if fn3.dtype != torch.bfloat16 or tuple(fn3.shape) != (3 * R, hc * hidden) or not fn3.is_contiguous():
+        raise ValueError("fn3 must be the contiguous bfloat16 [3*(2hc+hc^2), hc*hidden] output of mhc_split_weights")
+    if hc_scale.dtype != torch.float32 or hc_scale.numel() != 3 or hc_base.dtype != torch.float32 or hc_base.numel() != R:
+        raise ValueError("hc_scale must be float32 [3] and hc_base float32 [2hc+hc^2]")
+    residual = residual.contiguous()
+    dev = residual.device
+    lib = _lib.load()
+    need = lib.moe_mhc_pre_workspace(T, hc, hidden)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+    post = torch.empty(T, hc, 1, dtype=torch.float32, device=dev)
+    comb = torch.empty(T, hc, hc, dtype=torch.float32, device=dev)
+    layer_input = torch.empty(T, hidden, dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.moe_mhc_pre(_ptr(residual), _ptr(fn3), _ptr(hc_scale.contiguous()), _ptr(hc_base.contiguous()), T, hc,
+                             hidden, rms_eps, hc_pre_eps, hc_sinkhorn_eps, hc_post_mult_value, sinkhorn_repeat,
+                             _ptr(workspace), workspace.numel() * workspace.element_size(), _ptr(post), _ptr(comb),
+                             _ptr(layer_input), _ptr(status_buffer(dev)), _stream())
+    _lib.check(rc, "moe_mhc_pre")
+    _after(dev)
+    return post, comb, layer_input
+
+
+def mhc_post(x: torch.Tensor, residual: torch.Tensor, post_layer_mix: torch.Tensor,
+             comb_res_mix: torch.Tensor) -> torch.Tensor:
+    """out bf16 [T, hc, hidden] = x * post_layer_mix + comb_res_mix^T @ residual (fp32 arithmetic)."""
+    _need_cuda(x, residual, post_layer_mix, comb_res_mix)
+    if x.dtype != torch.bfloat16 or residual.dtype != torch.bfloat16 or residual.dim() != 3:
+        raise ValueError("x and residual must be bfloat16, residual [T, hc_mult, hidden]")
+    T, hc, hidden = residual.shape
+    if tuple(x.shape) != (T, hidden) or post_layer_mix.numel() != T * hc or comb_res_mix.numel() != T * hc * hc:
+        raise ValueError("shape mismatch between x, residual and the mixing coefficients")
+    if post_layer_mix.dtype != torch.float32 or comb_res_mix.dtype != torch.float32:
+        raise ValueError("mixing coefficients must be float32")
+    out = torch.empty(T, hc, hidden, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().moe_mhc_post(_ptr(x.contiguous()), _ptr(residual.contiguous()), _ptr(post_layer_mix.contiguous()),
+                                      _ptr(comb_res_mix.contiguous()), T, hc, hidden, _ptr(out), _stream())
+    _lib.check(rc, "moe_mhc_post")
+    return out
+
+
 def ep_regroup(recv_counts: torch.Tensor, n_recv_bound: int):
     """recv_counts int32 [G, E_local] -> (offsets int32 [E_local+1], src_row int32 [n_recv_bound])."""
     _need_cuda(recv_counts)
