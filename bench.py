@@ -388,11 +388,14 @@ def run_ours(args, cfg):
         flops = 2.0 * rows * H * (2 * I)
         achieved = flops / (stage_ms["up_gemm"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
-        # DRAM traffic per launch: ncu capture of the c5_shard8 workload (32 experts, 8192 rows: 2.076 GB read +
-        # 0.031 GB written, profiles/grouped_gemm_kernel_c5_shard8.md), which is weights once + A once + output once;
-        # it grows with the experts touched and the rows, so it is scaled by both to this launch
+        # DRAM traffic per launch: ncu capture of the c5_shard8 workload (32 experts, 8192 rows of 1024 tokens: 2.009 GB
+        # read + 0.031 GB written, profiles/grouped_gemm_kernel_c5_shard8.md) = weights x 1.04 + the activations once +
+        # the output once; it grows with the experts touched and the rows, so it is scaled by both to this launch.
+        # On one GPU the kernel gathers its rows from the T x H activations (L2-resident, read once); with expert
+        # parallelism it reads the rows x H receive buffer.
         per_expert = 2 * I * H * 2 * 1.04
-        traffic = (E if world == 1 else E / world) * per_expert + rows * (H + I) * 2
+        a_bytes = T * H * 2 if world == 1 else rows * H * 2
+        traffic = (E if world == 1 else E / world) * per_expert + a_bytes + rows * I * 2
         roofline = {"kernel": "grouped_gemm_kernel<1,256,SILU_GATE> (up GEMM, tcgen05)", "bound": "tensor",
                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "traffic": traffic,
