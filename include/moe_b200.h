@@ -203,6 +203,25 @@ int moe_router_topk(const void* x, const void* Wr, int64_t T, int H, int E, int 
 int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets,
                    int32_t* src_row, void* stream);
 
+/* ---- the whole layer in one call -----------------------------------------------------
+ * FusedMoEPyTorch.forward / FusedMoETileLang.forward (kernels/fusedmoe_baseline.py:46-91,
+ * kernels/fusedmoe_tilelang.py:309-417) as one C call that sequences the entry points above on
+ * `stream`: router (logits fp32 [T,E] if given, else x . router_weight^T) -> softmax over all experts,
+ * top-k without renormalisation -> histogram / offsets / permutation -> up GEMM (gathering its rows,
+ * SiLU gate fused) -> down GEMM (routing weight + scatter fused) -> combine with the shared expert.
+ *   x [T,H]; router_weight [E,H] or NULL; shared_gate, shared_up [SI,H], shared_down [H,SI] (SI = 0: no
+ *   shared expert, pointers ignored); routed_gate, routed_up [E,I,H], routed_down [E,H,I]; out [T,H]; all
+ *   16-bit of `dtype`.  ws: moe_layer_workspace(T,k,H,I,E,SI) bytes of device scratch, 256-byte aligned.
+ *   side_stream: optional second stream for the shared expert (fork / join by events; NULL = same stream).
+ * Results are bit-identical to issuing the calls one by one.  No host synchronisation.
+ */
+size_t moe_layer_workspace(int64_t T, int k, int H, int I, int E, int SI);
+int moe_layer_forward(const void* x, const void* router_weight, const float* logits, const void* shared_gate,
+                      const void* shared_up, const void* shared_down, const void* routed_gate,
+                      const void* routed_up, const void* routed_down, int64_t T, int H, int I, int E, int k,
+                      int SI, int dtype, void* ws, size_t ws_bytes, void* out, int32_t* status, void* stream,
+                      void* side_stream);
+
 /* ---- mHC pre / post blocks ---------------------------------------------------------------
  * The operators on either side of the MoE layer in the model the reference targets
  * (kernels/mhc_baseline.py:48-163; recommended entry points kernels/mhc_tilelang.py:494-582).

@@ -119,3 +119,31 @@ def test_host_pipeline_overlaps_copies_and_keeps_results(cuda, lib):
     torch.testing.assert_close(last.float(), ref, rtol=RTOL, atol=ATOL)
     assert torch.equal(pipe.out_host[0], pipe.out_host[1])     # every step computed the same batch
     assert pipe.h2d_bytes == T * H * 2 + T * E * 4 and pipe.d2h_bytes == T * H * 2
+
+
+@pytest.mark.parametrize("B,S,H,I,E,NS,k,dtype", [(1, 300, 512, 256, 8, 1, 2, torch.bfloat16),     # shared expert, few experts
+                                                 (2, 128, 256, 128, 64, 0, 6, torch.bfloat16),    # no shared expert
+                                                 (1, 200, 200, 72, 16, 2, 4, torch.float16),      # H % 64 != 0: gather pass
+                                                 (1, 2304, 1024, 128, 64, 1, 8, torch.bfloat16)]) # enough rows for the one-kernel router
+def test_single_call_layer_equals_the_staged_calls(cuda, lib, B, S, H, I, E, NS, k, dtype):
+    """moe_layer_forward (one C call) only sequences the library's own entry points: its output must equal, bit for
+    bit, the layer issued stage by stage from Python - with the router computed from x and from given logits."""
+    x, w = O.make_fusedmoe_inputs(B, S, H, I, E, NS, k, dtype=dtype, seed=B + S)
+    xd = x.to(cuda)
+    wd = [w[n].to(cuda) for n in NAMES]
+    if NS == 0:
+        wd[1] = wd[2] = wd[3] = None
+    m = kernels.FusedMoETileLang(H, I, E, NS, k, B, S, dtype=dtype)
+    y1 = m.forward(xd, *wd).clone()
+    y0 = layer.moe_forward(xd, *wd, k).clone()
+    ops.check_status(cuda)
+    assert y1.shape == x.shape and torch.equal(y1, y0)
+    lg = ops.router_logits(xd.view(-1, H), wd[0])
+    y1l = m.forward(xd, *wd, logits=lg).clone()
+    y0l = layer.moe_forward(xd, *wd, k, logits=lg).clone()
+    assert torch.equal(y1l, y0l)
+    ref = O.fusedmoe(x, *[w[n] for n in NAMES], k, logits=lg.cpu())
+    torch.testing.assert_close(y1l.float().cpu(), ref, rtol=RTOL, atol=ATOL)
+    # and as one replayed CUDA graph
+    replay = m.capture(xd, *wd, logits=lg)
+    assert torch.equal(replay(), y0l)

@@ -33,6 +33,9 @@ SIGNATURES = {
     "moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, C.POINTER(C.c_void_p), _i32, _vp]),
     "moe_grouped_gemm_peer_scatter": (_i32, [_vp, _vp, _vp, _vp, _vp, C.POINTER(C.c_void_p), _i32, _i64, _i64, _i64,
                                              _i32, _i32, _i32, _i32, _vp, _vp]),
+    "moe_layer_workspace": (_sz, [_i64, _i32, _i32, _i32, _i32, _i32]),
+    "moe_layer_forward": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _i32,
+                                 _vp, _sz, _vp, _vp, _vp, _vp]),
     "moe_mhc_pre_workspace": (_sz, [_i64, _i32, _i64]),
     "moe_mhc_split_weights": (_i32, [_vp, _i32, _i64, _vp, _vp]),
     "moe_mhc_pre": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, C.c_float, C.c_float, C.c_float, C.c_float, _i32,

@@ -18,7 +18,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libmoe_b200.so"
-SOURCES = ["common.cu", "topk_softmax.cu", "route.cu", "gemm_sm100.cu", "mhc.cu"]
+SOURCES = ["common.cu", "topk_softmax.cu", "route.cu", "gemm_sm100.cu", "mhc.cu", "layer.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

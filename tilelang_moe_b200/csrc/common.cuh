@@ -99,4 +99,8 @@ int router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E, int
 // bf16 split-K GEMM with fp32 slices (gemm_sm100.cu): Y[T, S*N], N <= 128, K % (64*S) == 0
 int gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S, float* Y, int32_t* status, void* stream);
 
+// dense single-group GEMM through the grouped kernel, no offsets table on the device (gemm_sm100.cu)
+int dense_gemm(int epilogue, const void* A, const void* B, const void* B2, int64_t rows, int K, int N, void* Y,
+               int64_t ldy, int dtype, int32_t* status, void* stream);
+
 }  // namespace moe

@@ -828,7 +828,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish_pair();
   }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets[e];
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
   if (warp == 2) {
     const int per = (E + 31) / 32;
@@ -1082,7 +1082,7 @@ grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets[e];
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
   if (warp == 2) {  // prefix of token chunks per expert
     const int per = (E + 31) / 32;
@@ -1341,6 +1341,7 @@ struct GatherArgs {           // A rows fetched through an index list instead of
   const int32_t* idx = nullptr;
   int div = 1;
   int64_t src_rows = 0;
+  int64_t dense_rows = 0;     // > 0 with offsets == nullptr: one group of this many rows (E must be 1)
 };
 
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
@@ -1415,6 +1416,16 @@ int moe::router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E
   return launch<1, 128, EPI_ROUTER>(tA, tB, tB, p, grid, st);
 }
 
+// One dense group: Y[rows, N] = epilogue(A[rows, K] . B[N, K]^T) without a device-side offsets table (declared in
+// common.cuh; used for the shared expert of the single-call layer).
+int moe::dense_gemm(int epilogue, const void* A, const void* B, const void* B2, int64_t rows, int K, int N, void* Y,
+                    int64_t ldy, int dtype, int32_t* status, void* stream) {
+  GatherArgs ga;
+  ga.dense_rows = rows;
+  return grouped_gemm_impl(epilogue, A, B, B2, nullptr, nullptr, nullptr, Y, ldy, rows, K, N, 1, status, stream, nullptr,
+                           nullptr, 0, 0, dtype, ga);
+}
+
 // Y[T, S*N] fp32: slice s of the K dimension of A[T,K] . B[N,K]^T in columns [s*N, (s+1)*N) (declared in common.cuh).
 // Split-K gives a skinny GEMM (few row tiles, long K) one tile per SM; the caller adds the S slices.
 int moe::gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S, float* Y, int32_t* status,
@@ -1481,7 +1492,7 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   if (E > MAX_E) return fail(MOE_ERR_UNSUPPORTED, "grouped_gemm: E=%d exceeds %d", E, MAX_E);
   if (max_rows == 0) return MOE_OK;
   if (max_rows > 0x7FFFFF00ll) return fail(MOE_ERR_UNSUPPORTED, "grouped_gemm: too many rows");
-  if (!A || !B || !offsets || !Y) return fail(MOE_ERR_ARG, "grouped_gemm: null pointer");
+  if (!A || !B || !Y || (!offsets && !(ga.dense_rows > 0 && E == 1))) return fail(MOE_ERR_ARG, "grouped_gemm: null pointer");
   if (epilogue == MOE_GEMM_SILU_GATE && !B2) return fail(MOE_ERR_ARG, "grouped_gemm: SILU_GATE needs the up weight");
   if (epilogue == MOE_GEMM_SCALE_SCATTER && !row_w) return fail(MOE_ERR_ARG, "grouped_gemm: SCALE_SCATTER needs row weights");
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(B2) |
@@ -1529,6 +1540,7 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
     q.row_rank = nullptr;
     for (int g = 0; g < 16; ++g) q.peer_base[g] = nullptr;
     q.a_gather = nullptr; q.a_src = nullptr; q.a_div = 1; q.a_src_rows = 0; q.a_rows = 0; q.w_by_dst = w_by_dst;
+    q.dense_rows = (int)ga.dense_rows;
     CUtensorMap tW, tW2, tX;
     rc = make_tmap(&tW, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM, f16);
     if (rc) return rc;
@@ -1567,6 +1579,7 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   p.row_rank = row_rank;
   for (int g = 0; g < 16; ++g) p.peer_base[g] = (peer_base && g < n_peers) ? peer_base[g] : nullptr;
   p.w_by_dst = w_by_dst;
+  p.dense_rows = (int)ga.dense_rows;
   p.a_gather = ga.idx; p.a_src = A; p.a_div = ga.div; p.a_src_rows = (int)ga.src_rows; p.a_rows = (int)max_rows;
 
   CUtensorMap tA, tB, tB2;

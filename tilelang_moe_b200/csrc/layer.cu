@@ -1,0 +1,158 @@
+// The whole MoE layer behind one C call: router (given logits, or x . Wr^T) -> top-k + softmax over all experts ->
+// histogram / offsets / permutation -> up GEMM (gathering its rows, SiLU gate fused) -> down GEMM (routing weight
+// and scatter fused) -> k-way combine with the shared expert.  It only sequences the library's own entry points on
+// the caller's stream; the shared expert runs on `side_stream` when one is given (fork / join by two events).
+// Same arithmetic as calling the pieces one by one, so results are bit-identical to that.
+#include "common.cuh"
+#include "../../include/moe_b200.h"
+
+#include <mutex>
+
+namespace moe {
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct LayerScratch {
+  size_t scores, idx32, counts, offsets, perm, hist, act, yk, logits, xs, wsorted, act_s, y_s, total;
+};
+
+static LayerScratch layer_layout(int64_t T, int k, int H, int I, int E, int SI) {
+  LayerScratch L;
+  const size_t n = (size_t)T * k;
+  size_t o = 0;
+  auto take = [&](size_t bytes) { const size_t at = o; o += align256(bytes); return at; };
+  L.scores = take(n * 4);
+  L.idx32 = take(n * 4);
+  L.counts = take((size_t)E * 4);
+  L.offsets = take((size_t)(E + 1) * 4);
+  L.perm = take(n * 4);
+  L.hist = take(moe_route_histogram_workspace((int64_t)n, E));
+  L.act = take(n * (size_t)I * 2);
+  L.yk = take(n * (size_t)H * 2);
+  L.logits = take((size_t)T * E * 4);                       // only written when the one-kernel router does not apply
+  const bool fused_gather = H % 64 == 0;
+  L.xs = take(fused_gather ? 0 : n * (size_t)H * 2);
+  L.wsorted = take(fused_gather ? 0 : n * 4);
+  L.act_s = take((size_t)T * SI * 2);
+  L.y_s = take(SI > 0 ? (size_t)T * H * 2 : 0);
+  L.total = o;
+  return L;
+}
+
+// two events per device for the fork / join around the shared expert; created once, never destroyed
+static int layer_events(cudaEvent_t* fork, cudaEvent_t* join) {
+  static cudaEvent_t ev[64][2];
+  static bool made[64];
+  static std::mutex mu;
+  int dev = 0;
+  MOE_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MOE_ERR_DEVICE, "layer_forward: device ordinal %d", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!made[dev]) {
+    MOE_CUDA_CHECK(cudaEventCreateWithFlags(&ev[dev][0], cudaEventDisableTiming));
+    MOE_CUDA_CHECK(cudaEventCreateWithFlags(&ev[dev][1], cudaEventDisableTiming));
+    made[dev] = true;
+  }
+  *fork = ev[dev][0];
+  *join = ev[dev][1];
+  return MOE_OK;
+}
+
+}  // namespace moe
+
+extern "C" size_t moe_layer_workspace(int64_t T, int k, int H, int I, int E, int SI) {
+  if (T < 1 || k < 1 || H < 1 || I < 1 || E < 1 || SI < 0) return 0;
+  return moe::layer_layout(T, k, H, I, E, SI).total;
+}
+
+extern "C" int moe_layer_forward(const void* x, const void* router_weight, const float* logits, const void* shared_gate,
+                                 const void* shared_up, const void* shared_down, const void* routed_gate,
+                                 const void* routed_up, const void* routed_down, int64_t T, int H, int I, int E, int k,
+                                 int SI, int dtype, void* ws, size_t ws_bytes, void* out, int32_t* status, void* stream,
+                                 void* side_stream) {
+  using namespace moe;
+  if (T < 0 || H < 8 || (H % 8) || I < 8 || (I % 8) || E < 1 || k < 1 || k > E || SI < 0 || (SI % 8))
+    return fail(MOE_ERR_ARG, "layer_forward: bad shape T=%lld H=%d I=%d E=%d k=%d SI=%d", (long long)T, H, I, E, k, SI);
+  if (T == 0) return MOE_OK;
+  if (!x || (!router_weight && !logits) || !routed_gate || !routed_up || !routed_down || !out || !ws)
+    return fail(MOE_ERR_ARG, "layer_forward: null pointer");
+  if (SI > 0 && (!shared_gate || !shared_up || !shared_down)) return fail(MOE_ERR_ARG, "layer_forward: shared expert weights missing");
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(MOE_ERR_ARG, "layer_forward: workspace must be 256-byte aligned");
+  const LayerScratch L = layer_layout(T, k, H, I, E, SI);
+  if (ws_bytes < L.total) return fail(MOE_ERR_WORKSPACE, "layer_forward: workspace %zu < %zu", ws_bytes, L.total);
+  unsigned char* base = reinterpret_cast<unsigned char*>(ws);
+  float* scores = reinterpret_cast<float*>(base + L.scores);
+  int32_t* idx32 = reinterpret_cast<int32_t*>(base + L.idx32);
+  int32_t* counts = reinterpret_cast<int32_t*>(base + L.counts);
+  int32_t* offsets = reinterpret_cast<int32_t*>(base + L.offsets);
+  int32_t* perm = reinterpret_cast<int32_t*>(base + L.perm);
+  void* act = base + L.act;
+  void* yk = base + L.yk;
+  const int64_t n = T * k;
+  int rc;
+
+  // shared expert: depends on x only, runs beside the routed path when a second stream is given
+  void* shared_out = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (SI > 0) {
+    void* sst = stream;
+    if (side_stream && side_stream != stream) {
+      rc = layer_events(&ev_fork, &ev_join);
+      if (rc) return rc;
+      MOE_CUDA_CHECK(cudaEventRecord(ev_fork, st));
+      MOE_CUDA_CHECK(cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(side_stream), ev_fork, 0));
+      sst = side_stream;
+    }
+    rc = dense_gemm(MOE_GEMM_SILU_GATE, x, shared_gate, shared_up, T, H, SI, base + L.act_s, SI, dtype, status, sst);
+    if (rc) return rc;
+    rc = dense_gemm(MOE_GEMM_PLAIN, base + L.act_s, shared_down, nullptr, T, SI, H, base + L.y_s, H, dtype, status, sst);
+    if (rc) return rc;
+    if (sst != stream) MOE_CUDA_CHECK(cudaEventRecord(ev_join, reinterpret_cast<cudaStream_t>(sst)));
+    shared_out = base + L.y_s;
+  }
+
+  // router: softmax over all experts, top-k without renormalisation (the reference layer's convention)
+  if (logits) {
+    rc = moe_topk_softmax(logits, T, E, E, k, MOE_TOPK_MODE_A, scores, nullptr, idx32, status, stream);
+    if (rc) return rc;
+  } else {
+    // one kernel when the shape allows and has enough row tiles to hide the selection, else GEMM then top-k
+    const bool small = E <= 32 && (size_t)E * H * 2 <= 200 * 1024;
+    const bool fused = small || (E % 8 == 0 && E >= 8 && E <= 256 && k <= 8 && (E <= 64 || T >= 32 * (int64_t)E));
+    if (fused) {
+      rc = moe_router_topk(x, router_weight, T, H, E, k, MOE_TOPK_MODE_A, dtype, scores, nullptr, idx32, nullptr, status, stream);
+      if (rc) return rc;
+    } else {
+      float* lg = reinterpret_cast<float*>(base + L.logits);
+      if (E % 8) return fail(MOE_ERR_UNSUPPORTED, "layer_forward: E=%d needs E %% 8 == 0 or a router weight within 200 KB", E);
+      rc = dense_gemm(MOE_GEMM_PLAIN_F32, x, router_weight, nullptr, T, H, E, lg, E, dtype, status, stream);
+      if (rc) return rc;
+      rc = moe_topk_softmax(lg, T, E, E, k, MOE_TOPK_MODE_A, scores, nullptr, idx32, status, stream);
+      if (rc) return rc;
+    }
+  }
+  rc = moe_route_histogram(idx32, 0, n, E, nullptr, counts, offsets, perm, nullptr, base + L.hist,
+                           moe_route_histogram_workspace(n, E), status, stream);
+  if (rc) return rc;
+  if (H % 64 == 0) {
+    rc = moe_grouped_gemm_gathered(MOE_GEMM_SILU_GATE, x, T, perm, k, routed_gate, routed_up, offsets, nullptr, nullptr, act, I,
+                                   n, 0, H, I, E, dtype, status, stream);
+    if (rc) return rc;
+    rc = moe_grouped_gemm(MOE_GEMM_SCALE_SCATTER_DSTW, act, routed_down, nullptr, offsets, perm, scores, yk, H, n, 0, I, H, E,
+                          dtype, status, stream);
+    if (rc) return rc;
+  } else {
+    float* wsorted = reinterpret_cast<float*>(base + L.wsorted);
+    rc = moe_gather_rows(x, perm, k, n, H, base + L.xs, scores, wsorted, stream);
+    if (rc) return rc;
+    rc = moe_grouped_gemm(MOE_GEMM_SILU_GATE, base + L.xs, routed_gate, routed_up, offsets, nullptr, nullptr, act, I, n, 0, H, I,
+                          E, dtype, status, stream);
+    if (rc) return rc;
+    rc = moe_grouped_gemm(MOE_GEMM_SCALE_SCATTER, act, routed_down, nullptr, offsets, perm, wsorted, yk, H, n, 0, I, H, E,
+                          dtype, status, stream);
+    if (rc) return rc;
+  }
+  if (ev_join) MOE_CUDA_CHECK(cudaStreamWaitEvent(st, ev_join, 0));
+  return moe_combine(yk, shared_out, nullptr, nullptr, T, k, H, dtype, out, stream);
+}

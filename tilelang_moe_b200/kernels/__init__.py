@@ -104,14 +104,15 @@ class FusedMoETileLang:
         self.n_experts_per_token = n_experts_per_token
         self.batch_size, self.seq_len = batch_size, seq_len
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self.ws = _layer.MoEWorkspace(batch_size * seq_len, n_experts_per_token, d_hidden, d_expert,
-                                      n_routed_experts, d_expert * n_shared_experts, dev, dtype)
+        self.ws = _layer.SingleCallWorkspace(batch_size * seq_len, n_experts_per_token, d_hidden, d_expert,
+                                             n_routed_experts, d_expert * n_shared_experts, dev, dtype)
 
     def forward(self, x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down,
                 logits: Optional[torch.Tensor] = None):
-        return _layer.moe_forward(x, router_weight, shared_gate if self.n_shared_experts else None, shared_up,
-                                  shared_down, routed_gate, routed_up, routed_down, self.n_experts_per_token,
-                                  ws=self.ws, logits=logits)
+        """One library call (``moe_layer_forward``) enqueues the whole layer."""
+        return _layer.moe_forward_single_call(x, router_weight, shared_gate if self.n_shared_experts else None,
+                                              shared_up, shared_down, routed_gate, routed_up, routed_down,
+                                              self.n_experts_per_token, ws=self.ws, logits=logits)
 
     __call__ = forward
 

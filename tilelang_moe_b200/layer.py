@@ -169,3 +169,58 @@ def moe_forward(x: torch.Tensor, router_weight: Optional[torch.Tensor], shared_g
     if return_routing:
         return y, scores, idx32
     return y
+
+
+class SingleCallWorkspace:
+    """Device scratch of ``moe_layer_forward`` for one (T, k, H, I, E, SI) shape: one buffer, laid out by the library."""
+
+    def __init__(self, T: int, k: int, H: int, I: int, E: int, SI: int, device: torch.device,
+                 dtype: torch.dtype = torch.bfloat16):
+        self.key = (T, k, H, I, E, SI, dtype, device)
+        need = _lib.load().moe_layer_workspace(T, k, H, I, E, SI)
+        self.buf = torch.empty(need + 256, dtype=torch.uint8, device=device)
+        self.offset = (-self.buf.data_ptr()) % 256
+        self.bytes = need
+        self.out = torch.empty(T, H, dtype=dtype, device=device)
+
+
+def moe_forward_single_call(x: torch.Tensor, router_weight: Optional[torch.Tensor], shared_gate, shared_up, shared_down,
+                            routed_gate: torch.Tensor, routed_up: torch.Tensor, routed_down: torch.Tensor, k: int,
+                            ws: Optional[SingleCallWorkspace] = None, logits: Optional[torch.Tensor] = None,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The layer through ``moe_layer_forward``: one library call enqueues every kernel (the shared expert on the
+    side stream), instead of one Python-level call per stage.  Same kernels, same results as ``moe_forward``."""
+    if x.dtype not in ops.DTYPE_CODE:
+        raise ValueError("moe_b200 computes in bfloat16 or float16; cast the activations and weights")
+    shape = x.shape
+    H = shape[-1]
+    x_flat = x.reshape(-1, H)
+    if not x_flat.is_contiguous():
+        x_flat = x_flat.contiguous()
+    T = x_flat.shape[0]
+    E, I, _ = routed_gate.shape
+    SI = 0 if shared_gate is None else shared_gate.shape[0]
+    tensors = [x_flat, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down]
+    for t in tensors:
+        if t is not None and (not t.is_cuda or t.dtype != x.dtype or not t.is_contiguous()):
+            raise ValueError("all layer tensors must be contiguous CUDA tensors of the activation dtype")
+    if logits is not None and (logits.dtype != torch.float32 or tuple(logits.shape) != (T, E) or not logits.is_contiguous()):
+        raise ValueError("logits must be a contiguous float32 [T, E] tensor")
+    if logits is None and router_weight is None:
+        raise ValueError("either router_weight or logits is needed")
+    dev = x.device
+    key = (T, k, H, I, E, SI, x.dtype, dev)
+    if ws is None or ws.key != key:
+        ws = SingleCallWorkspace(T, k, H, I, E, SI, dev, x.dtype)
+    y = ws.out if out is None else out.view(T, H)
+    side = _side_stream(dev) if SI > 0 else None
+    p = ops._ptr
+    with torch.cuda.device(dev):
+        rc = _lib.load().moe_layer_forward(
+            p(x_flat), p(router_weight) if logits is None else None, p(logits), p(shared_gate), p(shared_up), p(shared_down),
+            p(routed_gate), p(routed_up), p(routed_down), T, H, I, E, k, SI, ops.DTYPE_CODE[x.dtype],
+            ws.buf.data_ptr() + ws.offset, ws.bytes, p(y), p(ops.status_buffer(dev)), ops._stream(),
+            side.cuda_stream if side is not None else None)
+    _lib.check(rc, "moe_layer_forward")
+    ops._after(dev)
+    return y.view(*shape)
