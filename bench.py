@@ -61,6 +61,7 @@ class ClockSampler:
                ("sw_power_cap", 0x4))
 
     def __init__(self, index: int, period_s: float = 0.004):
+        period_s = float(os.environ.get("MOE_B200_CLOCK_PERIOD_MS", period_s * 1e3)) / 1e3
         self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
         self.max_mhz, self._stop, self._thread, self._nvml, self.proc = None, threading.Event(), None, None, None
 
@@ -328,14 +329,20 @@ def run_ours(args, cfg):
             dist.barrier()
             torch.cuda.synchronize()
 
+    host_ms = [0.0]
+
     def timed(fn, steps, with_timers=False):
-        sync_all()
+        # the sampler is started before the barrier: NVML initialisation takes milliseconds, and a rank that enters
+        # the timed region late makes every other rank wait for it at the first exchange
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
+        sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         stage_events = []
+        sampler.samples.clear()            # keep only what is sampled while the timed steps run
         e0.record()
+        h0 = time.perf_counter()
         for _ in range(steps):
             if with_timers:
                 tm = {}
@@ -343,6 +350,7 @@ def run_ours(args, cfg):
                 stage_events.append(tm)
             else:
                 fn()
+        host_ms[0] = (time.perf_counter() - h0) * 1e3 / max(steps, 1)     # host time to enqueue one step
         e1.record()
         sync_all()
         clocks = sampler.stop() if rank == 0 else None
@@ -356,6 +364,7 @@ def run_ours(args, cfg):
     for _ in range(max(args.warmup, 3)):
         step()
     ms, stage_events, clocks = timed(step, args.steps, with_timers=True)
+    host_enqueue_ms = host_ms[0]
     ops.check_status(dev)
     # end to end: every step uploads its inputs from pinned host memory and downloads its result; where the
     # closure takes a step count the steps are pipelined (copies of neighbouring steps overlap the compute)
@@ -449,6 +458,7 @@ def run_ours(args, cfg):
                 "how": "pinned host buffers; H2D of x and logits and D2H of the output every step, on copy streams "
                        "that overlap the neighbouring steps' compute (tilelang_moe_b200.pipeline.HostPipeline)"},
         "gpu_launches": launches_per_step * args.steps,
+        "host_enqueue_ms_per_step": round(host_enqueue_ms, 4),
         "stage_ms": stage_ms,
         "stage_ms_by_rank": stage_ms_by_rank,
         "roofline": roofline,
