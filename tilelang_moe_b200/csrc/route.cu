@@ -217,11 +217,26 @@ combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, c
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int s = 0; s < k; ++s) {
-      const int64_t f = t * k + s;
-      const int64_t r = row_of ? (int64_t)row_of[f] : f;
-      const uint4 y = __ldg(Yk + r * vec_per_row + v);
-      if (scale) fma_x8<F16>(acc, y, scale[f]); else add_x8<F16>(acc, y);
+    // four slots at a time: the loads of a group are all in flight before the first is added; the additions
+    // stay in slot order, so the sum is the same as one slot at a time
+    for (int s0 = 0; s0 < k; s0 += 4) {
+      uint4 y[4];
+      float w[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u < k) {
+          const int64_t f = t * k + s0 + u;
+          const int64_t r = row_of ? (int64_t)row_of[f] : f;
+          y[u] = __ldg(Yk + r * vec_per_row + v);
+          w[u] = scale ? scale[f] : 1.0f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u < k) {
+          if (scale) fma_x8<F16>(acc, y[u], w[u]); else add_x8<F16>(acc, y[u]);
+        }
+      }
     }
     if (shared) add_x8<F16>(acc, __ldg(shared + g));
     uint4 o;
