@@ -70,14 +70,15 @@ mhc_pre_finish_kernel(const uint4* __restrict__ residual, const float* __restric
   const int vecs = HC * hidden_vecs;
   const uint4* src = residual + t * vecs;
   float ss = 0.f;
-  // four independent 16-byte loads per thread in flight: the kernel is a stream of the residual
-  for (int v0 = tid; v0 < vecs; v0 += 4 * 256) {
-    uint4 x[4];
+  // eight independent 16-byte loads per thread in flight (a whole 32 KB row per pass of the CTA): the kernel is
+  // a stream of the residual
+  for (int v0 = tid; v0 < vecs; v0 += 8 * 256) {
+    uint4 x[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+    for (int u = 0; u < 8; ++u)
       if (v0 + u * 256 < vecs) x[u] = __ldg(src + v0 + u * 256);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       if (v0 + u * 256 < vecs) {
         row[v0 + u * 256] = x[u];
         float f[8];
@@ -89,15 +90,17 @@ mhc_pre_finish_kernel(const uint4* __restrict__ residual, const float* __restric
   }
   ss = warp_sum(ss);
   if (lane == 0) red[warp] = ss;
+  float m = 0.f;                      // the GEMM slices of this thread's mix, fetched before the barrier
+  if (tid < R) {
+    const float* pp = part + t * (int64_t)(S * 3 * R);
+    for (int s = 0; s < S; ++s) m += (pp[(s * 3 + 0) * R + tid] + pp[(s * 3 + 1) * R + tid]) + pp[(s * 3 + 2) * R + tid];
+  }
   __syncthreads();
   if (tid < R) {
     float total = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) total += red[w];
     const float rms = rsqrtf(total / (float)(vecs * 8) + rms_eps);
-    float m = 0.f;
-    const float* pp = part + t * (int64_t)(S * 3 * R);
-    for (int s = 0; s < S; ++s) m += (pp[(s * 3 + 0) * R + tid] + pp[(s * 3 + 1) * R + tid]) + pp[(s * 3 + 2) * R + tid];
     const float sc = tid < HC ? hc_scale[0] : (tid < 2 * HC ? hc_scale[1] : hc_scale[2]);
     mix[tid] = m * rms * sc + hc_base[tid];
   }
