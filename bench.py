@@ -398,7 +398,7 @@ def run_ours(args, cfg):
         achieved = flops / (stage_ms["up_gemm"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         # DRAM traffic per launch: ncu capture of the c5_shard8 workload (32 experts, 8192 rows of 1024 tokens: 2.009 GB
-        # read + 0.031 GB written, profiles/grouped_gemm_kernel_c5_shard8.md) = weights x 1.04 + the activations once +
+        # read + 0.031 GB written; summary under profiles/) = weights x 1.04 + the activations once +
         # the output once; it grows with the experts touched and the rows, so it is scaled by both to this launch.
         # On one GPU the kernel gathers its rows from the T x H activations (L2-resident, read once); with expert
         # parallelism it reads the rows x H receive buffer.

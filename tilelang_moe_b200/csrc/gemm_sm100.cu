@@ -2,14 +2,16 @@
 //
 //   Y[rows of expert e] = A[rows of expert e] . B[e]^T          (A: [rows,K], B: [E,N,K], K contiguous)
 //
-// One persistent CTA per SM, 192 threads in three roles:
+// One persistent CTA per SM, 256 threads in four roles (192 threads and the first three roles in the CTA-pair and
+// tokens-as-N kernels):
 //   warp 0      TMA producer: per k-block one A box (128 rows x 64) and the B box(es) (BN rows x 64),
 //               128-byte swizzled, into a ring of shared-memory stages guarded by mbarriers;
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) four times per
 //               k-block; tcgen05.commit releases the stage and, after the last k-block, publishes
 //               the accumulator.  Also owns the TMEM allocation;
 //   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator, apply the fused epilogue, store 16-byte
-//               vectors with row masks.
+//               vectors with row masks;
+//   warps 6..7  row gather (see below); idle otherwise.
 //
 // Two tile shapes.  MT=1: 128 rows x BN columns, accumulator double-buffered in TMEM so that the next
 // tile's main loop overlaps the epilogue.  MT=2: 256 rows x 256 columns as two M=128 MMAs per K step
@@ -26,7 +28,9 @@
 // TMA of B.  This removes the separate gather pass (one write and one read of the sorted copy of A).
 //
 // Epilogues: plain bf16 / fp32, SiLU(gate)*up with gate and up accumulated side by side in TMEM
-// by one N=256 instruction, and routing-weight scale + scatter to the (token, slot) row.
+// by one N=256 instruction, routing-weight scale + scatter to the (token, slot) row, rows stored into other
+// GPUs' buffers as 128-byte segments, and the router's top-k + softmax taken straight from the accumulator row.
+// Split-K mode (fp32 output): the N-tile index counts K slices, each slice lands in its own column block.
 //
 // Every barrier wait is bounded in time; on expiry the kernel records a status code, lets the
 // copies it issued land, frees its TMEM and returns.
