@@ -318,8 +318,10 @@ def run_ours(args, cfg):
         runner = ep.EPRunner(cfg, rank, world, dev, make_weights, exchange=args.exchange)
         step, step_e2e, launches_per_step, h2d, d2h = runner.bench_closures(x_cpu, logits_cpu)
         tokens_per_step = T
-        how = ("dispatch kernel + down-GEMM epilogue over NVLink peer memory" if args.exchange == "peer"
-               else "NCCL all-to-all")
+        how = {"peer": "dispatch kernel + down-GEMM epilogue over NVLink peer memory",
+               "peer_dedup": "de-duplicated dispatch kernel (a token row per destination rank, gathered by the up GEMM) "
+                             "+ down-GEMM epilogue over NVLink peer memory",
+               "nccl": "NCCL all-to-all"}[args.exchange]
         parallelism = f"ep{world}: {E // world} experts per GPU, tokens split {T // world} per rank, {how}"
         imbalance = {"rows": runner.imbalance, "modelled_time": runner.cost_imbalance}
 
@@ -715,7 +717,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router", "gemm_grid", "mhc"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_dedup", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--graph", action="store_true", help="c3: replay the layer as one CUDA graph")
     ap.add_argument("--only", default="", help="router / gemm_grid workloads: comma-separated point names to run")

@@ -269,6 +269,27 @@ int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx,
                     const int32_t* id_map, const int32_t* offsets, const int32_t* dst_base, int k,
                     int E_local, int slot_lo, int slot_hi, int64_t n, int64_t H,
                     void* const* peer_recv, int G, void* stream);
+/* De-duplicated dispatch: a token row travels to a destination rank once, whatever the number of its k experts
+ * there (bytes over NVLink fall by k / E[distinct ranks per token]); the destination's up GEMM then gathers its
+ * expert-major rows through an index list that the sources write beside the rows (moe_grouped_gemm_gathered with
+ * gather_div = 1 on the receive buffer).
+ *   moe_ep_unique: urank int32 [Tl, G]: u(t,d) = tokens t' < t of this rank with an expert on rank d, or -1 if token
+ *     t has none there; ucount int32 [G] = tokens per destination.  The histogram all-gather then carries
+ *     E + G integers per rank: counts, then ucount.
+ *   moe_ep_plan_dedup: moe_ep_plan on that [G][E+G] table, plus u_base int32 [G]: first row of this rank's tokens in
+ *     each destination's receive buffer.
+ *   moe_ep_dispatch_dedup: stores row x[t] to peer_recv[d] at row u_base[d] + u(t,d) for every (t,d) with u >= 0,
+ *     and for every routed entry p the received-row number into peer_gidx[d] (int32 [capacity]) at the entry's
+ *     expert-major position dst_base[v] + (p - offsets[v]).
+ */
+int moe_ep_unique(const int32_t* topk_idx, const int32_t* id_map, int64_t Tl, int k, int E_local, int G,
+                  int32_t* urank, int32_t* ucount, void* stream);
+int moe_ep_plan_dedup(const int32_t* cnt_all, int G, int E_local, int my_rank, int32_t* offsets,
+                      int32_t* dst_base, int32_t* ret_rank, int32_t* ret_row, int32_t* u_base, void* stream);
+int moe_ep_dispatch_dedup(const void* x, const int32_t* perm, const int32_t* topk_idx, const int32_t* id_map,
+                          const int32_t* offsets, const int32_t* dst_base, const int32_t* urank,
+                          const int32_t* u_base, int k, int E_local, int64_t n, int64_t Tl, int64_t H,
+                          void* const* peer_recv, void* const* peer_gidx, int G, void* stream);
 int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                   const int32_t* row_rank, const int32_t* dst_rows,
                                   void* const* peer_base, int n_peers, int64_t ldy, int64_t max_rows,

@@ -90,3 +90,67 @@ def test_ep_protocol_matches_single_process(world, placement):
     for rank, err, exc in res:
         assert exc is None, f"rank {rank}: {exc}"
         assert err < 1e-4, f"rank {rank}: max abs error {err}"
+
+
+def test_dedup_dispatch_tables_model():
+    """The arithmetic of the de-duplicated dispatch (moe_ep_unique / moe_ep_plan_dedup / moe_ep_dispatch_dedup), restated
+    in numpy for all ranks in one process: a token row is stored once per destination rank, and the index list the
+    sources write lets every destination find, for each expert-major position, the row of the right token."""
+    import numpy as np
+    rng = np.random.default_rng(0)
+    G, El, Tl, k = 4, 3, 37, 5
+    E = G * El
+    e2r = ep.balanced_placement(list(rng.integers(1, 50, E)), G)
+    plan = ep.EPPlan(E, G, e2r)
+    id_map = np.array(plan.id_map)
+    idx = np.stack([np.stack([rng.permutation(E)[:k] for _ in range(Tl)]) for _ in range(G)])     # [G, Tl, k] global ids
+    # per source: histogram in virtual-expert order, stable permutation
+    cnt = np.zeros((G, E + G), dtype=np.int64)
+    perm, offs, urank = [], [], []
+    for s in range(G):
+        v = id_map[idx[s]].reshape(-1)
+        perm.append(np.argsort(v, kind="stable"))
+        c = np.bincount(v, minlength=E)
+        cnt[s, :E] = c
+        offs.append(np.concatenate([[0], np.cumsum(c)]))
+        flags = np.zeros((Tl, G), dtype=bool)
+        for t in range(Tl):
+            flags[t, id_map[idx[s, t]] // El] = True
+        u = np.where(flags, np.cumsum(flags, axis=0) - 1, -1)                                  # moe_ep_unique
+        urank.append(u)
+        cnt[s, E:] = flags.sum(0)
+    # destination-side tables (moe_ep_plan_dedup on every rank)
+    cap = Tl * k * G
+    recv = [dict() for _ in range(G)]
+    gidx = [np.full(cap, -7, dtype=np.int64) for _ in range(G)]
+    dbase = np.zeros(E, dtype=np.int64)
+    for d in range(G):
+        run = 0
+        for j in range(El):
+            dbase[d * El + j] = run
+            run += cnt[:, d * El + j].sum()
+    for s in range(G):                                                                        # source side
+        dst_base = np.array([dbase[v] + cnt[:s, v].sum() for v in range(E)])
+        u_base = np.array([cnt[:s, E + d].sum() for d in range(G)])
+        for t in range(Tl):
+            for d in range(G):
+                if urank[s][t, d] >= 0:
+                    row = u_base[d] + urank[s][t, d]
+                    assert row not in recv[d], "two tokens share a receive row"
+                    recv[d][row] = (s, t)
+        for p in range(Tl * k):
+            f = perm[s][p]
+            v = id_map[idx[s].reshape(-1)[f]]
+            d, t = v // El, f // k
+            gidx[d][dst_base[v] + (p - offs[s][v])] = u_base[d] + urank[s][t, d]
+    for d in range(G):                                                                        # what the up GEMM of d gathers
+        assert sorted(recv[d]) == list(range(len(recv[d]))) and len(recv[d]) == cnt[:, E + d].sum() <= Tl * G
+        q = 0
+        for j in range(El):
+            v = d * El + j
+            for s in range(G):
+                for i in range(cnt[s, v]):
+                    t = perm[s][offs[s][v] + i] // k
+                    assert recv[d][gidx[d][q]] == (s, t)
+                    q += 1
+        assert (gidx[d][q:] == -7).all()

@@ -42,7 +42,8 @@ def _worker(rank, world, port, placement, q, exchange="nccl"):
         Tl = T // world
         sl = slice(rank * Tl, (rank + 1) * Tl)
         bufs = {}
-        px = ep.PeerExchange(Tl, k, H, world, dev) if exchange == "peer" else None
+        px = ep.PeerExchange(Tl, k, H, world, dev, dedup=exchange == "peer_dedup") if exchange.startswith("peer") else None
+        assert px is None or px.dedup == (exchange == "peer_dedup")
         for _ in range(3):   # later passes reuse the buffers (and, for the peer exchange, overwrite them)
             args = (x[sl].to(dev), logits[sl].to(dev), k, plan, torch.tensor(plan.id_map, dtype=torch.int32, device=dev),
                     Wg[mine].to(dev), Wu[mine].to(dev), Wd[mine].to(dev), ops)
@@ -58,11 +59,20 @@ def _worker(rank, world, port, placement, q, exchange="nccl"):
 
 
 @pytest.mark.parametrize("placement,exchange", [("contiguous", "nccl"), ("balanced", "nccl"), ("contiguous", "peer"),
-                                                ("balanced", "peer")])
+                                                ("balanced", "peer"), ("contiguous", "peer_dedup"),
+                                                ("balanced", "peer_dedup")])
 def test_ep_two_gpus_match_oracle(lib, placement, exchange):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+    _run_world(2, placement, exchange)
+
+
+@pytest.mark.parametrize("exchange", ["peer", "peer_dedup"])
+def test_ep_four_gpus_match_oracle(lib, exchange):
+    _run_world(4, "balanced", exchange)
+
+
+def _run_world(world, placement, exchange):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()

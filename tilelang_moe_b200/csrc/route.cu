@@ -590,15 +590,24 @@ extern "C" int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, in
 namespace moe {
 
 __global__ void __launch_bounds__(1024)
-ep_plan_kernel(const int32_t* __restrict__ cnt_all, int G, int El, int me, int32_t* __restrict__ offsets,
-               int32_t* __restrict__ dst_base, int32_t* __restrict__ ret_rank, int32_t* __restrict__ ret_row) {
+ep_plan_kernel(const int32_t* __restrict__ cnt_all, int ld, int G, int El, int me, int32_t* __restrict__ offsets,
+               int32_t* __restrict__ dst_base, int32_t* __restrict__ ret_rank, int32_t* __restrict__ ret_row,
+               int32_t* __restrict__ u_base) {
   extern __shared__ int32_t sh[];
   const int E = G * El;
   int32_t* cnt = sh;                 // [G][E]
   int32_t* dbase = cnt + G * E;      // [E]   expert-major start of virtual expert v on its destination
   int32_t* srcoff = dbase + E;       // [G][El] start of (source s, my expert j) in source s's sorted order
   const int tid = threadIdx.x;
-  for (int i = tid; i < G * E; i += 1024) cnt[i] = cnt_all[i];
+  for (int i = tid; i < G * E; i += 1024) cnt[i] = cnt_all[(i / E) * ld + (i % E)];
+  // de-duplicated dispatch: row s of the table also carries, after the E counts, how many distinct tokens source s
+  // sends to each destination; this rank's tokens start in destination d's buffer after those of lower ranks
+  if (u_base && tid >= 64 && tid < 64 + G) {
+    const int d = tid - 64;
+    int32_t run = 0;
+    for (int s2 = 0; s2 < me; ++s2) run += cnt_all[s2 * ld + E + d];
+    u_base[d] = run;
+  }
   __syncthreads();
   // per destination d: exclusive scan over its local experts of the rows they receive from all sources
   if (tid < G) {
@@ -667,20 +676,165 @@ ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm
   }
 }
 
+// De-duplicated dispatch, step 1: for every token t of this rank and every destination rank d, u(t,d) = the number
+// of tokens t' < t that have at least one of their k experts on d, or -1 if t itself has none there; ucount[d] =
+// how many tokens go to d.  A token row then travels to a rank once, whatever the number of its experts there.
+// One CTA: the scan over tokens is sequential in chunks of 1024.
+__global__ void __launch_bounds__(1024)
+ep_unique_kernel(const int32_t* __restrict__ topk_idx, const int32_t* __restrict__ id_map, int Tl, int k, int El, int G,
+                 int32_t* __restrict__ urank, int32_t* __restrict__ ucount) {
+  __shared__ int32_t wtot[32][16];
+  __shared__ int32_t running[16];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  if (tid < 16) running[tid] = 0;
+  __syncthreads();
+  for (int base = 0; base < Tl; base += 1024) {
+    const int t = base + tid;
+    unsigned mask = 0;
+    if (t < Tl)
+      for (int s = 0; s < k; ++s) mask |= 1u << (id_map[topk_idx[t * k + s]] / El);
+    int32_t in_warp[16];
+#pragma unroll
+    for (int d = 0; d < 16; ++d) {
+      if (d < G) {
+        const unsigned b = __ballot_sync(0xFFFFFFFFu, (mask >> d) & 1u);
+        in_warp[d] = __popc(b & lt);
+        if (lane == 0) wtot[warp][d] = __popc(b);
+      }
+    }
+    __syncthreads();
+    if (t < Tl) {
+#pragma unroll
+      for (int d = 0; d < 16; ++d) {
+        if (d < G) {
+          int32_t u = -1;
+          if ((mask >> d) & 1u) {
+            u = running[d] + in_warp[d];
+            for (int w = 0; w < warp; ++w) u += wtot[w][d];
+          }
+          urank[t * G + d] = u;
+        }
+      }
+    }
+    __syncthreads();
+    if (tid < G) {
+      int32_t add = 0;
+      for (int w = 0; w < 32; ++w) add += wtot[w][tid];
+      running[tid] += add;
+    }
+    __syncthreads();
+  }
+  if (tid < G) ucount[tid] = running[tid];
+}
+
+// De-duplicated dispatch, step 2.  Work items of one warp each: first the Tl*G (token, destination) pairs - the
+// token's row goes to row u_base[d] + u(t,d) of destination d's receive buffer, once; then the routed entries in
+// groups of 32 - entry p (this rank's sorted order) tells its destination which received row it is:
+// gidx_d[dst_base[v] + (p - offsets[v])] = u_base[d] + u(t,d).  The destination's up GEMM gathers its expert-major
+// rows through that list.  Plain stores to peer memory.
+__global__ void __launch_bounds__(256)
+ep_dispatch_dedup_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm,
+                         const int32_t* __restrict__ topk_idx, const int32_t* __restrict__ id_map,
+                         const int32_t* __restrict__ offsets, const int32_t* __restrict__ dst_base,
+                         const int32_t* __restrict__ urank, const int32_t* __restrict__ u_base, int k, int El, int G,
+                         int64_t n, int64_t Tl, int vec_per_row, PeerPtrs recv, PeerPtrs gidx) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = (int64_t)gridDim.x * 8;
+  const int64_t pairs = Tl * G, groups = (n + 31) / 32;
+  for (int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); item < pairs + groups; item += nwarps) {
+    if (item < pairs) {
+      const int32_t u = urank[item];
+      if (u < 0) continue;
+      const int64_t t = item / G;
+      const int d = (int)(item - t * G);
+      const uint4* s = x + t * vec_per_row;
+      uint4* dst = reinterpret_cast<uint4*>(recv.p[d]) + (int64_t)(u_base[d] + u) * vec_per_row;
+      int i = lane;
+      for (; i + 96 < vec_per_row; i += 128) {   // four loads in flight before the first remote store
+        const uint4 a = __ldg(s + i), b = __ldg(s + i + 32), c = __ldg(s + i + 64), e = __ldg(s + i + 96);
+        dst[i] = a; dst[i + 32] = b; dst[i + 64] = c; dst[i + 96] = e;
+      }
+      for (; i < vec_per_row; i += 32) dst[i] = __ldg(s + i);
+    } else {
+      const int64_t p = (item - pairs) * 32 + lane;
+      if (p < n) {
+        const int32_t f = perm[p];
+        const int v = id_map[topk_idx[f]];
+        const int d = v / El;
+        const int64_t t = f / k;
+        const int64_t row = (int64_t)dst_base[v] + (p - offsets[v]);
+        reinterpret_cast<int32_t*>(gidx.p[d])[row] = u_base[d] + urank[t * G + d];
+      }
+    }
+  }
+}
+
 }  // namespace moe
 
-extern "C" int moe_ep_plan(const int32_t* cnt_all, int G, int E_local, int my_rank, int32_t* offsets, int32_t* dst_base,
-                           int32_t* ret_rank, int32_t* ret_row, void* stream) {
+extern "C" int moe_ep_unique(const int32_t* topk_idx, const int32_t* id_map, int64_t Tl, int k, int E_local, int G,
+                             int32_t* urank, int32_t* ucount, void* stream) {
+  using namespace moe;
+  if (!topk_idx || !id_map || !urank || !ucount) return fail(MOE_ERR_ARG, "ep_unique: null pointer");
+  if (Tl < 0 || Tl > 0x7FFFFFFFll / 64 || k < 1 || E_local < 1 || G < 1 || G > 16)
+    return fail(MOE_ERR_ARG, "ep_unique: bad shape Tl=%lld k=%d E_local=%d G=%d", (long long)Tl, k, E_local, G);
+  ep_unique_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(topk_idx, id_map, (int)Tl, k, E_local, G, urank, ucount);
+  MOE_CHECK_LAUNCH("ep_unique_kernel");
+  return MOE_OK;
+}
+
+static int ep_plan_impl(const int32_t* cnt_all, int ld, int G, int E_local, int my_rank, int32_t* offsets,
+                        int32_t* dst_base, int32_t* ret_rank, int32_t* ret_row, int32_t* u_base, void* stream) {
   using namespace moe;
   if (!cnt_all || !offsets || !dst_base || !ret_rank || !ret_row) return fail(MOE_ERR_ARG, "ep_plan: null pointer");
   if (G < 1 || G > 16 || E_local < 1 || my_rank < 0 || my_rank >= G) return fail(MOE_ERR_ARG, "ep_plan: bad G=%d E_local=%d rank=%d", G, E_local, my_rank);
   const int E = G * E_local;
+  if (ld < E + (u_base ? G : 0)) return fail(MOE_ERR_ARG, "ep_plan: row stride %d too small", ld);
   const size_t smem = ((size_t)G * E + E + (size_t)G * E_local) * sizeof(int32_t);
   if (smem > 200 * 1024) return fail(MOE_ERR_UNSUPPORTED, "ep_plan: G*E=%d too large", G * E);
   if (smem > 48 * 1024) MOE_CUDA_CHECK(cudaFuncSetAttribute(ep_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  ep_plan_kernel<<<1, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(cnt_all, G, E_local, my_rank, offsets, dst_base, ret_rank, ret_row);
+  ep_plan_kernel<<<1, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(cnt_all, ld, G, E_local, my_rank, offsets, dst_base,
+                                                                            ret_rank, ret_row, u_base);
   MOE_CHECK_LAUNCH("ep_plan_kernel");
   return MOE_OK;
+}
+
+extern "C" int moe_ep_plan_dedup(const int32_t* cnt_all, int G, int E_local, int my_rank, int32_t* offsets,
+                                 int32_t* dst_base, int32_t* ret_rank, int32_t* ret_row, int32_t* u_base, void* stream) {
+  if (!u_base) return moe::fail(MOE_ERR_ARG, "ep_plan_dedup: null pointer");
+  return ep_plan_impl(cnt_all, G * E_local + G, G, E_local, my_rank, offsets, dst_base, ret_rank, ret_row, u_base, stream);
+}
+
+extern "C" int moe_ep_dispatch_dedup(const void* x, const int32_t* perm, const int32_t* topk_idx, const int32_t* id_map,
+                                     const int32_t* offsets, const int32_t* dst_base, const int32_t* urank,
+                                     const int32_t* u_base, int k, int E_local, int64_t n, int64_t Tl, int64_t H,
+                                     void* const* peer_recv, void* const* peer_gidx, int G, void* stream) {
+  using namespace moe;
+  if (!x || !perm || !topk_idx || !id_map || !offsets || !dst_base || !urank || !u_base || !peer_recv || !peer_gidx)
+    return fail(MOE_ERR_ARG, "ep_dispatch_dedup: null pointer");
+  if (G < 1 || G > 16 || k < 1 || E_local < 1 || H < 8 || H % 8 || n < 0 || Tl < 0) return fail(MOE_ERR_ARG, "ep_dispatch_dedup: bad shape");
+  if (n == 0) return MOE_OK;
+  PeerPtrs pr, pg;
+  for (int g = 0; g < 16; ++g) { pr.p[g] = g < G ? peer_recv[g] : nullptr; pg.p[g] = g < G ? peer_gidx[g] : nullptr; }
+  for (int g = 0; g < G; ++g)
+    if (!pr.p[g] || !pg.p[g] || (reinterpret_cast<uintptr_t>(pr.p[g]) & 15) || (reinterpret_cast<uintptr_t>(pg.p[g]) & 3))
+      return fail(MOE_ERR_ARG, "ep_dispatch_dedup: peer buffer %d null or unaligned", g);
+  DeviceInfo dev;
+  int rc = current_device_info(&dev);
+  if (rc) return rc;
+  int64_t blocks = ceil_div64(Tl * G + ceil_div64(n, 32), 8);
+  const int64_t cap = (int64_t)dev.sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  ep_dispatch_dedup_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(x), perm, topk_idx, id_map, offsets, dst_base, urank, u_base, k, E_local, G, n, Tl,
+      (int)(H / 8), pr, pg);
+  MOE_CHECK_LAUNCH("ep_dispatch_dedup_kernel");
+  return MOE_OK;
+}
+
+extern "C" int moe_ep_plan(const int32_t* cnt_all, int G, int E_local, int my_rank, int32_t* offsets, int32_t* dst_base,
+                           int32_t* ret_rank, int32_t* ret_row, void* stream) {
+  return ep_plan_impl(cnt_all, G * E_local, G, E_local, my_rank, offsets, dst_base, ret_rank, ret_row, nullptr, stream);
 }
 
 extern "C" int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t* topk_idx, const int32_t* id_map,

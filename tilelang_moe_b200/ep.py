@@ -150,7 +150,7 @@ class PeerExchange:
     """
 
     def __init__(self, t_local: int, k: int, H: int, world: int, device: torch.device, group=None,
-                 cap_rows: Optional[int] = None, overlap: bool = True):
+                 cap_rows: Optional[int] = None, overlap: bool = True, dedup: bool = False):
         import torch.distributed._symmetric_memory as symm_mem
         from . import ops
         group = dist.group.WORLD if group is None else group
@@ -165,6 +165,15 @@ class PeerExchange:
         self.plan_bufs = {}
         self.side = torch.cuda.Stream(device=device)
         self.overlap = overlap
+        # de-duplicated dispatch: a token row goes to a rank once; the sources also write, for every routed entry, which
+        # received row it is, and the destination's up GEMM gathers through that list (needs H % 64 == 0)
+        self.dedup = dedup and H % 64 == 0
+        if self.dedup:
+            self.gidx = symm_mem.empty(self.cap, dtype=torch.int32, device=device)
+            self.gidx.zero_()
+            self.h_gidx = symm_mem.rendezvous(self.gidx, group)
+            self.gidx_ptrs = ops._ptr_array(list(self.h_gidx.buffer_ptrs))
+            self.uniq_bufs = {}
 
 
 def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: EPPlan, id_map_dev: torch.Tensor,
@@ -182,15 +191,34 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
     with st("route"):
         scores, idx32 = ops.topk_softmax(logits_local, k, mode="A", index_dtype=torch.int32)
         counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map_dev, workspace=bufs.get("hist_ws"))
+        if px.dedup:
+            urank, ucount = ops.ep_unique(idx32, id_map_dev, El, G, out=px.uniq_bufs)
     with st("counts_allgather"):
-        if px.cnt_all.shape[1] != E:
-            px.cnt_all = torch.empty(G, E, dtype=torch.int32, device=x_local.device)
-        dist.all_gather_into_tensor(px.cnt_all.view(-1), counts, group=group)
-        offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(px.cnt_all, G, El, rank, px.cap, out=px.plan_bufs)
+        width = E + G if px.dedup else E
+        if px.cnt_all.shape[1] != width:
+            px.cnt_all = torch.empty(G, width, dtype=torch.int32, device=x_local.device)
+        if px.dedup:
+            dist.all_gather_into_tensor(px.cnt_all.view(-1), torch.cat([counts, ucount]), group=group)
+            offs_local, dst_base, ret_rank, ret_row, u_base = ops.ep_plan_dedup(px.cnt_all, G, El, rank, px.cap,
+                                                                                out=px.plan_bufs)
+        else:
+            dist.all_gather_into_tensor(px.cnt_all.view(-1), counts, group=group)
+            offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(px.cnt_all, G, El, rank, px.cap, out=px.plan_bufs)
     I = Wg.shape[1]
     act = _take(bufs, "act", px.cap, I, x_local)
-    split = El // 2 if (px.overlap and El >= 2) else 0
-    if split == 0:
+    split = El // 2 if (px.overlap and El >= 2 and not px.dedup) else 0
+    if px.dedup:
+        with st("dispatch"):
+            ops.ep_dispatch_dedup(x_local, perm, idx32, id_map_dev, offsets, dst_base, urank, u_base, k, El,
+                                  px.recv_ptrs, px.gidx_ptrs)
+        with st("dispatch_barrier"):
+            px.h_recv.barrier(channel=0)
+        with st("up_gemm"):   # expert-major row q is received row gidx[q]
+            ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg, offs_local, B2=Wu, out=act, gather=px.gidx,
+                                    gather_div=1, expected_rows=Tl * k)
+        with st("down_gemm"):
+            ops.grouped_gemm_peer_scatter(act, Wd, offs_local, ret_rank, ret_row, px.ret_ptrs, H, expected_rows=Tl * k)
+    elif split == 0:
         with st("dispatch"):
             ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs)
         with st("dispatch_barrier"):
@@ -292,7 +320,10 @@ class EPRunner:
         # Dispatching the second half of the local experts under the first half's GEMMs pays only where the dispatch
         # is a large share of the step: measured +2.5 % at 8 GPUs, nothing at 4, -3 % at 2 (the copy slows the GEMM).
         overlap = os.environ.get("MOE_B200_EP_OVERLAP", "1" if world >= 8 else "0") != "0"
-        self.px = PeerExchange(self.Tl, k, cfg["H"], world, device, overlap=overlap) if exchange == "peer" else None
+        # "peer": every routed row travels; "peer_dedup": a token row travels to a rank once and the up GEMM gathers
+        dedup = exchange == "peer_dedup"
+        self.px = (PeerExchange(self.Tl, k, cfg["H"], world, device, overlap=overlap and not dedup, dedup=dedup)
+                   if exchange in ("peer", "peer_dedup") else None)
 
     def _routed_counts(self, logits_cpu: torch.Tensor) -> List[int]:
         """Rows per expert when `logits_cpu` is routed top-k (through the router and histogram kernels)."""
@@ -345,4 +376,4 @@ class EPRunner:
         h2d = (x_pin.numel() * 2 + lg_pin.numel() * 4) * self.world
         d2h = out_pin.numel() * 2 * self.world
         # peer exchange: topk, 3 x histogram, plan, dispatch, up, down(+scatter), combine
-        return step, step_e2e, (9 if self.px is not None else 10), h2d, d2h
+        return step, step_e2e, ((10 if self.px.dedup else 9) if self.px is not None else 10), h2d, d2h

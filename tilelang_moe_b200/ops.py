@@ -433,6 +433,55 @@ def ep_dispatch(x: torch.Tensor, perm: torch.Tensor, idx32: torch.Tensor, id_map
     _lib.check(rc, "moe_ep_dispatch")
 
 
+def ep_unique(idx32: torch.Tensor, id_map: torch.Tensor, e_local: int, G: int, out: Optional[dict] = None):
+    """(urank int32 [Tl, G], ucount int32 [G]): per token and destination rank, how many earlier tokens of this rank
+    also go there (or -1 if the token has no expert there), and the number of tokens per destination."""
+    _need_cuda(idx32, id_map)
+    Tl, k = idx32.shape
+    out = {} if out is None else out
+    if "urank" not in out or out["urank"].shape[0] != Tl:
+        out["urank"] = torch.empty(Tl, G, dtype=torch.int32, device=idx32.device)
+        out["ucount"] = torch.empty(G, dtype=torch.int32, device=idx32.device)
+    with torch.cuda.device(idx32.device):
+        rc = _lib.load().moe_ep_unique(_ptr(idx32), _ptr(id_map), Tl, k, e_local, G, _ptr(out["urank"]), _ptr(out["ucount"]),
+                                       _stream())
+    _lib.check(rc, "moe_ep_unique")
+    return out["urank"], out["ucount"]
+
+
+def ep_plan_dedup(cnt_all: torch.Tensor, G: int, e_local: int, rank: int, cap_rows: int, out: Optional[dict] = None):
+    """ep_plan on the [G, E+G] table (counts, then tokens per destination) -> (offsets, dst_base, ret_rank, ret_row,
+    u_base [G])."""
+    _need_cuda(cnt_all)
+    dev = cnt_all.device
+    out = {} if out is None else out
+    if "offsets" not in out:
+        out["offsets"] = torch.empty(e_local + 1, dtype=torch.int32, device=dev)
+        out["dst_base"] = torch.empty(G * e_local, dtype=torch.int32, device=dev)
+        out["ret_rank"] = torch.empty(cap_rows, dtype=torch.int32, device=dev)
+        out["ret_row"] = torch.empty(cap_rows, dtype=torch.int32, device=dev)
+    if "u_base" not in out:
+        out["u_base"] = torch.empty(G, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().moe_ep_plan_dedup(_ptr(cnt_all), G, e_local, rank, _ptr(out["offsets"]), _ptr(out["dst_base"]),
+                                           _ptr(out["ret_rank"]), _ptr(out["ret_row"]), _ptr(out["u_base"]), _stream())
+    _lib.check(rc, "moe_ep_plan_dedup")
+    return out["offsets"], out["dst_base"], out["ret_rank"], out["ret_row"], out["u_base"]
+
+
+def ep_dispatch_dedup(x: torch.Tensor, perm: torch.Tensor, idx32: torch.Tensor, id_map: torch.Tensor,
+                      offsets: torch.Tensor, dst_base: torch.Tensor, urank: torch.Tensor, u_base: torch.Tensor, k: int,
+                      e_local: int, peer_recv_ptrs, peer_gidx_ptrs) -> None:
+    """De-duplicated dispatch: every (token, destination rank) row once, plus the received-row number of every
+    routed entry into the destination's index list (peer stores)."""
+    _need_cuda(x, perm, urank, u_base)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().moe_ep_dispatch_dedup(_ptr(x), _ptr(perm), _ptr(idx32), _ptr(id_map), _ptr(offsets), _ptr(dst_base),
+                                               _ptr(urank), _ptr(u_base), k, e_local, perm.numel(), x.shape[0], x.shape[1],
+                                               peer_recv_ptrs, peer_gidx_ptrs, len(peer_recv_ptrs), _stream())
+    _lib.check(rc, "moe_ep_dispatch_dedup")
+
+
 def grouped_gemm_peer_scatter(A: torch.Tensor, B: torch.Tensor, offsets: torch.Tensor, row_rank: torch.Tensor,
                               dst_rows: torch.Tensor, peer_ptrs, ldy: int, max_rows: Optional[int] = None,
                               expected_rows: int = 0) -> None:
