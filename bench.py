@@ -717,7 +717,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router", "gemm_grid", "mhc"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "peer_dedup", "nccl"],
+    ap.add_argument("--exchange", default="peer_dedup", choices=["peer", "peer_dedup", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--graph", action="store_true", help="c3: replay the layer as one CUDA graph")
     ap.add_argument("--only", default="", help="router / gemm_grid workloads: comma-separated point names to run")

@@ -85,3 +85,70 @@ def _run_world(world, placement, exchange):
     for rank, ok, err, exc in res:
         assert exc is None, f"rank {rank}: {exc}"
         assert ok, f"rank {rank}: max abs error {err}"
+
+
+@pytest.mark.parametrize("G,dedup", [(4, True), (8, True), (8, False)])
+def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedup):
+    """The peer-exchange kernels for G ranks run one after another on a single GPU: every "rank" has its own receive,
+    index and return buffers on that device, the all-gather is a torch.stack, and no barrier is needed because the
+    phases are issued in order on one stream.  Checks the whole path (unique / plan / dispatch / gathered up GEMM /
+    scattering down GEMM / combine) against the oracle for 4 and 8 ranks without needing that many GPUs."""
+    from oracle import moe_oracle as O
+    from tilelang_moe_b200 import ep, inputs, ops
+    dev = cuda
+    El, k, H, I, Tl = 4, 4, 128, 64, 96
+    E, T = G * El, G * 96
+    g = torch.Generator().manual_seed(G)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    Wg = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16()
+    Wu = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16()
+    Wd = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16()
+    logits = inputs.zipf_logits(T, E, 1.1, seed=G)
+    _, idx = O.topk_softmax(logits, k, "A")
+    plan = ep.EPPlan(E, G, ep.balanced_placement(O.route_histogram(idx, E)[0].tolist(), G))
+    id_map = torch.tensor(plan.id_map, dtype=torch.int32, device=dev)
+    cap = Tl * k * G
+    recv = [torch.zeros(cap, H, dtype=torch.bfloat16, device=dev) for _ in range(G)]
+    gidx = [torch.zeros(cap, dtype=torch.int32, device=dev) for _ in range(G)]
+    ret = [torch.zeros(Tl * k, H, dtype=torch.bfloat16, device=dev) for _ in range(G)]
+    recv_ptrs = ops._ptr_array([t.data_ptr() for t in recv])
+    gidx_ptrs = ops._ptr_array([t.data_ptr() for t in gidx])
+    ret_ptrs = ops._ptr_array([t.data_ptr() for t in ret])
+    routed = []
+    for s in range(G):                                               # route on every rank
+        sl = slice(s * Tl, (s + 1) * Tl)
+        scores, idx32 = ops.topk_softmax(logits[sl].to(dev), k, mode="A", index_dtype=torch.int32)
+        counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map)
+        urank, ucount = ops.ep_unique(idx32, id_map, El, G) if dedup else (None, None)
+        routed.append(dict(x=x[sl].to(dev), scores=scores, idx32=idx32, counts=counts, offsets=offsets, perm=perm, inv=inv,
+                           urank=urank, ucount=ucount))
+    cnt_all = torch.stack([torch.cat([r["counts"], r["ucount"]]) if dedup else r["counts"] for r in routed]).contiguous()
+    plans = []
+    for s in range(G):                                               # plan + dispatch from every rank
+        r = routed[s]
+        if dedup:
+            offs_local, dst_base, ret_rank, ret_row, u_base = ops.ep_plan_dedup(cnt_all, G, El, s, cap)
+            ops.ep_dispatch_dedup(r["x"], r["perm"], r["idx32"], id_map, r["offsets"], dst_base, r["urank"], u_base, k, El,
+                                  recv_ptrs, gidx_ptrs)
+        else:
+            offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(cnt_all, G, El, s, cap)
+            ops.ep_dispatch(r["x"], r["perm"], r["idx32"], id_map, r["offsets"], dst_base, k, El, recv_ptrs)
+        plans.append((offs_local, ret_rank, ret_row))
+    for d in range(G):                                               # expert GEMMs on every rank
+        offs_local, ret_rank, ret_row = plans[d]
+        mine = plan.local_experts[d]
+        wg, wu, wd = Wg[mine].to(dev), Wu[mine].to(dev), Wd[mine].to(dev)
+        if dedup:
+            act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, recv[d], wg, offs_local, B2=wu, gather=gidx[d], gather_div=1)
+        else:
+            act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, recv[d], wg, offs_local, B2=wu)
+        ops.grouped_gemm_peer_scatter(act, wd, offs_local, ret_rank, ret_row, ret_ptrs, H)
+    ref = O.fusedmoe(x, None, None, None, None, Wg, Wu, Wd, k, logits=logits)
+    for s in range(G):                                               # combine on every rank
+        r = routed[s]
+        out = ops.combine(ret[s], k, row_of=r["inv"], scale=r["scores"].reshape(-1), T=Tl)
+        torch.testing.assert_close(out.float().cpu(), ref[s * Tl:(s + 1) * Tl], rtol=1e-2, atol=2e-2)
+    ops.check_status(dev)
+    if dedup:   # fewer rows travelled than routed entries, and never more than one per (token, rank)
+        sent = int(cnt_all[:, E:].sum())
+        assert sent <= T * min(k, G) and sent < T * k

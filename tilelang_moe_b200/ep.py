@@ -291,7 +291,7 @@ class EPRunner:
     """Holds one rank's shard (weights of its experts, buffers) for the benchmark workload."""
 
     def __init__(self, cfg: dict, rank: int, world: int, device: torch.device, make_weights: Callable,
-                 placement: str = "balanced", calib_seed: int = 1, exchange: str = "peer"):
+                 placement: str = "balanced", calib_seed: int = 1, exchange: str = "peer_dedup"):
         from . import _lib, ops
         from .layer import _Stage
         self.ops, self._Stage = ops, _Stage
