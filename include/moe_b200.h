@@ -213,7 +213,9 @@ int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offs
  *   shared expert, pointers ignored); routed_gate, routed_up [E,I,H], routed_down [E,H,I]; out [T,H]; all
  *   16-bit of `dtype`.  ws: moe_layer_workspace(T,k,H,I,E,SI) bytes of device scratch, 256-byte aligned.
  *   side_stream: optional second stream for the shared expert (fork / join by events; NULL = same stream).
- * Results are bit-identical to issuing the calls one by one.  No host synchronisation.
+ * Results are bit-identical to issuing the calls one by one.  No host synchronisation.  With a side stream the
+ * fork / join uses two events that the library keeps per device: host threads that call this function for the
+ * same device at the same time must pass side_stream = NULL.
  */
 size_t moe_layer_workspace(int64_t T, int k, int H, int I, int E, int SI);
 int moe_layer_forward(const void* x, const void* router_weight, const float* logits, const void* shared_gate,

@@ -150,7 +150,7 @@ static int launch_warp(const float* logits, int64_t M, int N, int64_t ld, int k,
 // NaN into the canonical positive NaN, which ranks above +inf.
 // ------------------------------------------------------------------------------------
 constexpr int TILE_THREADS = 128;
-constexpr int TILE_FLOATS = 128 * 128;      // staged floats per tile (rows x row length <= this)
+
 
 template <int K, int TPR>
 __global__ void __launch_bounds__(TILE_THREADS)
