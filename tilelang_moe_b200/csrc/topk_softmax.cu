@@ -187,12 +187,20 @@ topk_tile_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld,
       for (int v = v_lo; v < v_hi; ++v) {
         const float4 x = *reinterpret_cast<const float4*>(rowp + v * 4);
         const int k0 = float_to_ikey(x.x), k1 = float_to_ikey(x.y), k2 = float_to_ikey(x.z), k3 = float_to_ikey(x.w);
-        const int m = max(max(k0, k1), max(k2, k3));
-        if (m > kv[K - 1]) {                       // some element of the vector enters the list
-          list_insert<K>(kv, ki, k0, v * 4);
-          list_insert<K>(kv, ki, k1, v * 4 + 1);
-          list_insert<K>(kv, ki, k2, v * 4 + 2);
-          list_insert<K>(kv, ki, k3, v * 4 + 3);
+        // Only elements above the list's last entry can enter it.  They are taken largest first (lowest column
+        // first among equal ones, so equal values keep column order in the list): the lanes of a warp hold
+        // different rows, and the warp pays for as many insertions as the busiest lane needs - usually one -
+        // instead of four for every vector that has a candidate in any lane.
+        int c0 = k0, c1 = k1, c2 = k2, c3 = k3;
+        int m = max(max(c0, c1), max(c2, c3));
+        while (m > kv[K - 1]) {
+          const int sel = c0 == m ? 0 : (c1 == m ? 1 : (c2 == m ? 2 : 3));
+          list_insert<K>(kv, ki, m, v * 4 + sel);
+          c0 = sel == 0 ? (int)0x80000000 : c0;
+          c1 = sel == 1 ? (int)0x80000000 : c1;
+          c2 = sel == 2 ? (int)0x80000000 : c2;
+          c3 = sel == 3 ? (int)0x80000000 : c3;
+          m = max(max(c0, c1), max(c2, c3));
         }
       }
     }
