@@ -549,7 +549,13 @@ def run_router(args):
             return ops.topk_softmax(ops.router_logits(X, W), K)
 
         row = {"name": name, "T": T, "H": H, "E": E, "k": K}
-        for label, fn in (("us_one_kernel", one), ("us_two_kernels", two)):
+        def split():
+            return ops.router_topk_softmax(X, W, K, fused="splitk")
+
+        variants = [("us_one_kernel", one), ("us_two_kernels", two)]
+        if ops.router_splits(T, H) >= 2:
+            variants.append(("us_split_k", split))
+        for label, fn in variants:
             for _ in range(3):
                 fn()
             times = []
@@ -565,6 +571,8 @@ def run_router(args):
         s1, i1 = one()
         s2, i2 = two()
         row["same_indices"] = bool(torch.equal(i1, i2))
+        row["default_rule_picks"] = ("split_k" if (ops.router_splits(T, H) >= 4 and not (E <= 32 and E * H * 2 <= 200 * 1024))
+                                     else ("one_kernel" if (E <= 64 or T >= 32 * E) else "two_kernels"))
         byts = (T * H + E * H) * 2 + T * K * 12
         row["GBps_one_kernel"] = round(byts / row["us_one_kernel"] / 1e3, 1)
         row["frac_hbm_measured"] = round(byts / row["us_one_kernel"] / 1e3 / peaks["hbm_gbs"], 3)

@@ -203,6 +203,17 @@ int moe_router_topk(const void* x, const void* Wr, int64_t T, int H, int E, int 
 int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets,
                    int32_t* src_row, void* stream);
 
+/* Router for few tokens (decode-sized batches): with only ceil(T/128) row tiles the router GEMM would keep a handful
+ * of SMs busy, so it is split along K into S slices (1..16, chosen from T and H) that give every SM a tile; a second
+ * kernel adds a token's slices in fixed order and does the top-k + softmax.  Same outputs as moe_router_topk; the
+ * logits (logits_out, optional) are the slice sums, i.e. equal to an unsplit fp32 accumulation up to summation order.
+ * E % 8 == 0, E <= 256, k <= 32.  ws: moe_router_topk_splitk_workspace(T, H, E) bytes.
+ */
+size_t moe_router_topk_splitk_workspace(int64_t T, int H, int E);
+int moe_router_topk_splitk(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype,
+                           float* scores, int64_t* indices, int32_t* indices32, float* logits_out, void* ws,
+                           size_t ws_bytes, int32_t* status, void* stream);
+
 /* ---- the whole layer in one call -----------------------------------------------------
  * FusedMoEPyTorch.forward / FusedMoETileLang.forward (kernels/fusedmoe_baseline.py:46-91,
  * kernels/fusedmoe_tilelang.py:309-417) as one C call that sequences the entry points above on

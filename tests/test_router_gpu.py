@@ -217,3 +217,27 @@ def test_one_kernel_router_falls_back_for_other_shapes(cuda, lib):
     s, i = ops.router_topk_softmax(X, W, 4)
     s2, i2 = ops.topk_softmax(ops.router_logits(X, W), 4)
     assert torch.equal(i, i2) and torch.equal(s, s2)
+
+
+@pytest.mark.parametrize("T,H,E,K,dtype", [(256, 7168, 256, 8, torch.bfloat16), (1024, 4096, 128, 8, torch.bfloat16),
+                                           (77, 5120, 160, 6, torch.float16), (1, 1024, 64, 8, torch.bfloat16),
+                                           (300, 3584, 64, 32, torch.bfloat16), (130, 512, 40, 3, torch.bfloat16)])
+@pytest.mark.parametrize("mode", ["B", "A", "A_renorm"])
+def test_few_token_router_split_along_k(cuda, lib, T, H, E, K, dtype, mode):
+    """moe_router_topk_splitk: the logits it reports are the fp32 sums of the K slices (equal to the unsplit GEMM up to
+    summation order), and its selection is exactly the oracle's on those logits - ties lowest index first."""
+    g = torch.Generator().manual_seed(T + E)
+    X = (torch.round(torch.randn(T, H, generator=g) * 2) / 2).to(dtype).to(cuda)
+    W = (torch.round(torch.randn(E, H, generator=g) * 2) / 8).to(dtype).to(cuda)
+    lg = torch.full((T, E), float("nan"), dtype=torch.float32, device=cuda)
+    s, i = ops.router_topk_softmax(X, W, K, mode=mode, logits_out=lg, fused="splitk")
+    s32, i32 = ops.router_topk_softmax(X, W, K, mode=mode, index_dtype=torch.int32, fused="splitk")
+    ops.check_status(cuda)
+    ref_logits = X.float().cpu() @ W.float().cpu().T
+    torch.testing.assert_close(lg.cpu(), ref_logits, rtol=1e-4, atol=1e-3)
+    s_ref, i_ref = O.topk_softmax(lg.cpu(), K, mode)
+    assert torch.equal(i.cpu(), i_ref) and torch.equal(i32.long().cpu(), i_ref)
+    torch.testing.assert_close(s.cpu(), s_ref, rtol=2e-6, atol=1e-30)
+    assert torch.equal(s32, s)
+    if T >= 64:   # with inputs on a coarse grid the split sums are exact, so they equal the unsplit GEMM's logits
+        assert torch.equal(lg, ops.router_logits(X, W))

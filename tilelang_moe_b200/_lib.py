@@ -46,6 +46,8 @@ SIGNATURES = {
                            _vp, _sz, _vp, _vp, _vp, _vp, _vp]),
     "moe_mhc_post": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _i64, _vp, _vp]),
     "moe_router_topk": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "moe_router_topk_splitk_workspace": (_sz, [_i64, _i32, _i32]),
+    "moe_router_topk_splitk": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
     "moe_router_logits": (_i32, [_vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _vp]),
 }
 

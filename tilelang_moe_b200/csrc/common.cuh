@@ -96,11 +96,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 int router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype, float* scores,
                      int64_t* indices, int32_t* indices32, float* logits_out, int32_t* status, void* stream);
 
-// bf16 split-K GEMM with fp32 slices (gemm_sm100.cu): Y[T, S*N], N <= 128, K % (64*S) == 0
-int gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S, float* Y, int32_t* status, void* stream);
+// split-K GEMM with fp32 slices (gemm_sm100.cu): Y[T, S*N], N <= 256, K % (64*S) == 0
+int gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S, float* Y, int32_t* status, void* stream,
+                    int dtype = MOE_DTYPE_BF16);
 
 // dense single-group GEMM through the grouped kernel, no offsets table on the device (gemm_sm100.cu)
 int dense_gemm(int epilogue, const void* A, const void* B, const void* B2, int64_t rows, int K, int N, void* Y,
                int64_t ldy, int dtype, int32_t* status, void* stream);
+
+// K slices of the few-token router GEMM (route.cu): 1..16 from the token count and the hidden size alone
+int router_splits(int64_t T, int H);
 
 }  // namespace moe

@@ -1433,31 +1433,35 @@ int moe::dense_gemm(int epilogue, const void* A, const void* B, const void* B2, 
 // Y[T, S*N] fp32: slice s of the K dimension of A[T,K] . B[N,K]^T in columns [s*N, (s+1)*N) (declared in common.cuh).
 // Split-K gives a skinny GEMM (few row tiles, long K) one tile per SM; the caller adds the S slices.
 int moe::gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S, float* Y, int32_t* status,
-                         void* stream) {
+                         void* stream, int dtype) {
   using namespace moe::gemm;
-  if (T < 1 || N < 8 || N > 128 || (N % 8) || S < 1 || K < 8 || (K % 8) || (S > 1 && (K % (64 * S))))
+  if (T < 1 || N < 8 || N > 256 || (N % 8) || S < 1 || K < 8 || (K % 8) || (S > 1 && (K % (64 * S))))
     return fail(MOE_ERR_ARG, "gemm_splitk: bad shape T=%lld K=%d N=%d S=%d", (long long)T, K, N, S);
   if (T > 0x7FFFFF00ll) return fail(MOE_ERR_UNSUPPORTED, "gemm_splitk: too many rows");
   DeviceInfo dev;
   int rc = current_device_info(&dev);
   if (rc) return rc;
+  const int f16 = dtype == MOE_DTYPE_F16;
   Params p;
   p.K = K; p.N = N; p.E = 1;
   p.num_n_tiles = S;
   p.num_k_blocks = (K / S + BK - 1) / BK;
   p.ksplit = S > 1;
   p.status = status;
+  p.f16 = f16;
   p.dense_rows = (int)T;
   p.Y = Y; p.ldy = (int64_t)S * N;
   p.b_tx_bytes = N * BK * 2;
   CUtensorMap tA, tB;
-  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)T, 0, (uint32_t)BM, 0);
+  rc = make_tmap(&tA, A, (uint64_t)K, (uint64_t)T, 0, (uint32_t)BM, f16);
   if (rc) return rc;
-  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)N, 0);
+  rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, 1, (uint32_t)N, f16);
   if (rc) return rc;
   const int64_t tiles = ((T + BM - 1) / BM) * S;
   const int grid = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
-  return launch<1, 128, MOE_GEMM_PLAIN_F32>(tA, tB, tB, p, grid, reinterpret_cast<cudaStream_t>(stream));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (N > 128) return launch<1, 256, MOE_GEMM_PLAIN_F32>(tA, tB, tB, p, grid, st);
+  return launch<1, 128, MOE_GEMM_PLAIN_F32>(tA, tB, tB, p, grid, st);
 }
 
 extern "C" int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,

@@ -29,7 +29,8 @@ static LayerScratch layer_layout(int64_t T, int k, int H, int I, int E, int SI) 
   L.hist = take(moe_route_histogram_workspace((int64_t)n, E));
   L.act = take(n * (size_t)I * 2);
   L.yk = take(n * (size_t)H * 2);
-  L.logits = take((size_t)T * E * 4);                       // only written when the one-kernel router does not apply
+  // router scratch: the logits when the one-kernel router does not apply, or the K slices of the few-token router
+  L.logits = take((size_t)T * E * 4 * (size_t)router_splits(T, H));
   const bool fused_gather = H % 64 == 0;
   L.xs = take(fused_gather ? 0 : n * (size_t)H * 2);
   L.wsorted = take(fused_gather ? 0 : n * 4);
@@ -119,6 +120,14 @@ extern "C" int moe_layer_forward(const void* x, const void* router_weight, const
   } else {
     // one kernel when the shape allows and has enough row tiles to hide the selection, else GEMM then top-k
     const bool small = E <= 32 && (size_t)E * H * 2 <= 200 * 1024;
+    const int splits = router_splits(T, H);
+    if (!small && splits >= 4 && E % 8 == 0 && E >= 8 && E <= 256 && k <= 32) {
+      // few tokens: router GEMM split along K so that every SM gets a tile, then slice sum + selection
+      rc = moe_router_topk_splitk(x, router_weight, T, H, E, k, MOE_TOPK_MODE_A, dtype, scores, nullptr, idx32, nullptr,
+                                  base + L.logits, (size_t)T * E * 4 * (size_t)splits, status, stream);
+      if (rc) return rc;
+      goto routed;
+    }
     const bool fused = small || (E % 8 == 0 && E >= 8 && E <= 256 && k <= 8 && (E <= 64 || T >= 32 * (int64_t)E));
     if (fused) {
       rc = moe_router_topk(x, router_weight, T, H, E, k, MOE_TOPK_MODE_A, dtype, scores, nullptr, idx32, nullptr, status, stream);
@@ -132,6 +141,7 @@ extern "C" int moe_layer_forward(const void* x, const void* router_weight, const
       if (rc) return rc;
     }
   }
+routed:
   rc = moe_route_histogram(idx32, 0, n, E, nullptr, counts, offsets, perm, nullptr, base + L.hist,
                            moe_route_histogram_workspace(n, E), status, stream);
   if (rc) return rc;

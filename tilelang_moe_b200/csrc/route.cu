@@ -563,6 +563,113 @@ extern "C" int moe_router_topk(const void* x, const void* Wr, int64_t T, int H, 
   return router_topk_gemm(x, Wr, T, H, E, k, mode, dtype, scores, indices, indices32, logits_out, status, stream);
 }
 
+// ------------------------------------------------------------------------------------
+// Router for few tokens: the GEMM x . Wr^T has only ceil(T/128) row tiles, so it is split along K to give every
+// SM a tile (fp32 slices [T, S, E]); this kernel adds the slices of a token (fixed order) and selects the top k
+// with softmax.  One warp per token, column c of the row in lane c % 32; each round takes the warp maximum by redux
+// and, among equal values, the lowest column.  E <= 256, k <= 32.
+// ------------------------------------------------------------------------------------
+namespace moe {
+__global__ void __launch_bounds__(256)
+router_reduce_topk_kernel(const float* __restrict__ part, int S, int64_t T, int E, int k, int mode,
+                          float* __restrict__ scores, int64_t* __restrict__ idx64, int32_t* __restrict__ idx32,
+                          float* __restrict__ logits_out) {
+  const unsigned FULL = 0xFFFFFFFFu;
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = (int64_t)gridDim.x * 8;
+  for (int64_t t = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); t < T; t += nwarps) {
+    const float* pp = part + t * (int64_t)S * E;
+    float v[8];
+    int key[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = lane + 32 * j;
+      float a = 0.f;
+      if (c < E)
+        for (int s = 0; s < S; ++s) a += pp[s * E + c];
+      v[j] = a;
+      key[j] = c < E ? float_to_ikey(a) : (int)0x80000000;
+      if (logits_out && c < E) logits_out[t * E + c] = a;
+    }
+    int win_key = (int)0x80000000, win_col = 0;
+    for (int r = 0; r < k; ++r) {
+      int lm = key[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) lm = max(lm, key[j]);
+      const int m = __reduce_max_sync(FULL, lm);
+      int lc = 0x7FFFFFFF;                       // lowest column of this lane that holds the maximum
+#pragma unroll
+      for (int j = 7; j >= 0; --j) lc = key[j] == m ? lane + 32 * j : lc;
+      const int c = __reduce_min_sync(FULL, lc);
+      if (lane == r) { win_key = m; win_col = c; }
+      if ((c & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) key[j] = (c >> 5) == j ? (int)0x80000000 : key[j];
+      }
+    }
+    const float vmax = ikey_to_float(__shfl_sync(FULL, win_key, 0));
+    const float e = lane < k ? expf(ikey_to_float(win_key) - vmax) : 0.f;
+    float denom;
+    if (mode == MOE_TOPK_MODE_B) {
+      denom = warp_sum(e);
+    } else {
+      float a = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (lane + 32 * j < E) a += expf(v[j] - vmax);
+      denom = warp_sum(a);
+    }
+    float sc = e / denom;
+    if (mode == MOE_TOPK_MODE_A_RENORM) sc = sc / warp_sum(sc);
+    if (lane < k) {
+      scores[t * k + lane] = sc;
+      if (idx64) idx64[t * k + lane] = (int64_t)win_col;
+      if (idx32) idx32[t * k + lane] = (int32_t)win_col;
+    }
+  }
+}
+
+int router_splits(int64_t T, int H) {
+  const int64_t row_tiles = (T + 127) / 128;
+  int S = 1;
+  while (S < 16 && row_tiles * S * 2 <= 148 && H % (64 * (S * 2)) == 0 && H / (S * 2) >= 256) S *= 2;
+  return S;
+}
+}  // namespace moe
+
+extern "C" size_t moe_router_topk_splitk_workspace(int64_t T, int H, int E) {
+  if (T < 1 || H < 8 || E < 1) return 0;
+  return (size_t)T * moe::router_splits(T, H) * E * sizeof(float);
+}
+
+extern "C" int moe_router_topk_splitk(const void* x, const void* Wr, int64_t T, int H, int E, int k, int mode, int dtype,
+                                      float* scores, int64_t* indices, int32_t* indices32, float* logits_out, void* ws,
+                                      size_t ws_bytes, int32_t* status, void* stream) {
+  using namespace moe;
+  if (dtype != MOE_DTYPE_BF16 && dtype != MOE_DTYPE_F16) return fail(MOE_ERR_ARG, "router_topk_splitk: unknown dtype %d", dtype);
+  if (T < 0 || H < 8 || H % 8 || E < 8 || E % 8 || k < 1 || k > E)
+    return fail(MOE_ERR_ARG, "router_topk_splitk: bad shape T=%lld H=%d E=%d k=%d", (long long)T, H, E, k);
+  if (E > 256 || k > 32) return fail(MOE_ERR_UNSUPPORTED, "router_topk_splitk: E <= 256 and k <= 32 (E=%d k=%d)", E, k);
+  if (mode < 0 || mode > 2) return fail(MOE_ERR_ARG, "router_topk_splitk: unknown mode %d", mode);
+  if (T == 0) return MOE_OK;
+  if (!x || !Wr || !scores || (!indices && !indices32) || !ws) return fail(MOE_ERR_ARG, "router_topk_splitk: null pointer");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(Wr) | reinterpret_cast<uintptr_t>(ws)) & 15)
+    return fail(MOE_ERR_ARG, "router_topk_splitk: x, Wr and ws must be 16-byte aligned");
+  const int S = router_splits(T, H);
+  if (ws_bytes < (size_t)T * S * E * sizeof(float)) return fail(MOE_ERR_WORKSPACE, "router_topk_splitk: workspace too small");
+  int rc = gemm_splitk_f32(x, Wr, T, H, E, S, reinterpret_cast<float*>(ws), status, stream, dtype);
+  if (rc) return rc;
+  DeviceInfo dev;
+  rc = current_device_info(&dev);
+  if (rc) return rc;
+  int64_t blocks = ceil_div64(T, 8);
+  if (blocks > (int64_t)dev.sm_count * 8) blocks = (int64_t)dev.sm_count * 8;
+  router_reduce_topk_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float*>(ws), S, T, E, k, mode, scores, indices, indices32, logits_out);
+  MOE_CHECK_LAUNCH("router_reduce_topk_kernel");
+  return MOE_OK;
+}
+
 extern "C" int moe_ep_regroup(const int32_t* recv_counts, int G, int E_local, int32_t* offsets, int32_t* src_row,
                               void* stream) {
   using namespace moe;

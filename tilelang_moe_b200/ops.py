@@ -276,6 +276,38 @@ def router_topk_fused_supported(H: int, E: int, k: int) -> bool:
     return E % 8 == 0 and 8 <= E <= 256 and k <= 8
 
 
+def router_splits(T: int, H: int) -> int:
+    """K slices the few-token router GEMM is cut into (the library's rule, restated for the dispatch below)."""
+    row_tiles = (T + 127) // 128
+    S = 1
+    while S < 16 and row_tiles * S * 2 <= 148 and H % (64 * S * 2) == 0 and H // (S * 2) >= 256:
+        S *= 2
+    return S
+
+
+def _router_topk_splitk(x, router_weight, k, mode, index_dtype, logits_out):
+    T, H = x.shape
+    E = router_weight.shape[0]
+    dt = _dtype_code(x, router_weight)
+    if index_dtype not in (torch.int64, torch.int32):
+        raise ValueError("index_dtype must be int64 or int32")
+    x = x.contiguous()
+    router_weight = router_weight.contiguous()
+    lib = _lib.load()
+    need = lib.moe_router_topk_splitk_workspace(T, H, E)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    scores = torch.empty(T, k, dtype=torch.float32, device=x.device)
+    idx = torch.empty(T, k, dtype=index_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.moe_router_topk_splitk(_ptr(x), _ptr(router_weight), T, H, E, k, _MODES[mode], dt, _ptr(scores),
+                                        _ptr(idx) if index_dtype == torch.int64 else None,
+                                        _ptr(idx) if index_dtype == torch.int32 else None, _ptr(logits_out), _ptr(ws),
+                                        ws.numel(), _ptr(status_buffer(x.device)), _stream())
+    _lib.check(rc, "moe_router_topk_splitk")
+    _after(x.device)
+    return scores, idx
+
+
 def router_topk_softmax(x: torch.Tensor, router_weight: torch.Tensor, k: int, mode="B",
                         index_dtype: torch.dtype = torch.int64, logits_out: Optional[torch.Tensor] = None,
                         fused: Optional[bool] = None):
@@ -283,15 +315,23 @@ def router_topk_softmax(x: torch.Tensor, router_weight: torch.Tensor, k: int, mo
     kernels/router_gemm_topk_softmax.py computes the same pair in one kernel).  One launch when the shape allows
     (CUDA cores for E <= 32, else the tcgen05 GEMM with the selection in its epilogue): the [T,E] logits are only
     written if ``logits_out`` is given.  Other shapes: router GEMM, then topk_softmax on its fp32 logits.
-    ``fused``: None = pick by shape, True / False = force the one-kernel / two-kernel path."""
+    ``fused``: None = pick by shape, True / False = force the one-kernel / two-kernel path, "splitk" = force the
+    few-token path (GEMM split along K, then a kernel that adds the slices and selects)."""
     _need_cuda(x, router_weight)
     T, H = x.shape
     E = router_weight.shape[0]
+    small_e = E <= 32 and E * H * 2 <= 200 * 1024
     if fused is None:
         # Measured on B200: with few row tiles the selection in the epilogue is not hidden behind another tile's
         # main loop, and the separate top-k kernel (all SMs) is quicker; from about 32 tokens per expert the single
         # kernel wins (T=16384: 93 vs 124 us at E=256, 44 vs 48 us at E=64).  Few experts: always one kernel.
-        fused = E <= 64 or T >= 32 * E
+        # Few tokens (at most a quarter of the SMs would get a row tile): the GEMM is split along K instead.
+        if not small_e and router_splits(T, H) >= 4 and E % 8 == 0 and 8 <= E <= 256 and k <= 32:
+            fused = "splitk"
+        else:
+            fused = E <= 64 or T >= 32 * E
+    if fused == "splitk":
+        return _router_topk_splitk(x, router_weight, k, mode, index_dtype, logits_out)
     if not fused or not router_topk_fused_supported(H, E, k) or T == 0:
         return topk_softmax(router_logits(x, router_weight, out=logits_out), k, mode=mode, index_dtype=index_dtype)
     dt = _dtype_code(x, router_weight)
