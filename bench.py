@@ -536,6 +536,8 @@ def run_router(args):
     fused = []
     fgrid = [(f"fused_{nm}_T{t}", t, H, E, K) for nm, H, E, K in (("Qwen2-57B", 3584, 64, 8), ("Qwen3-235B", 4096, 128, 8),
              ("DeepSeek-V2", 5120, 160, 6), ("DeepSeek-V3", 7168, 256, 8)) for t in (256, 1024, 4096, 16384)]
+    # prefill-sized batches: the activations (0.94 GB) are streamed once, which is where the HBM roofline shows
+    fgrid += [("fused_Qwen2-57B_T131072", 131072, 3584, 64, 8), ("fused_DeepSeek-V3_T65536", 65536, 7168, 256, 8)]
     for name, T, H, E, K in fgrid:
         if args.only and name not in args.only.split(","):
             continue
