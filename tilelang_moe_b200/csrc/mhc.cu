@@ -208,7 +208,7 @@ static int mhc_splits(int64_t T, int64_t K) {
   // workspace size is derived from it), K divisible into whole 64-element blocks per slice
   const int64_t row_tiles = (T + 127) / 128;
   int S = 1;
-  while (S < 16 && row_tiles * S < 148 && K % (64 * (S * 2)) == 0 && K / (S * 2) >= 512) S *= 2;
+  while (S < 16 && row_tiles * S * 2 <= 148 && K % (64 * (S * 2)) == 0 && K / (S * 2) >= 512) S *= 2;   // one wave of tiles
   return S;
 }
 
