@@ -87,16 +87,18 @@ def _run_world(world, placement, exchange):
         assert ok, f"rank {rank}: max abs error {err}"
 
 
+@pytest.mark.parametrize("tile_rows,H,I", [("128", 128, 64), ("pair", 256, 128)])
 @pytest.mark.parametrize("G,dedup", [(4, True), (8, True), (8, False)])
-def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedup):
+def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedup, tile_rows, H, I, monkeypatch):
     """The peer-exchange kernels for G ranks run one after another on a single GPU: every "rank" has its own receive,
     index and return buffers on that device, the all-gather is a torch.stack, and no barrier is needed because the
     phases are issued in order on one stream.  Checks the whole path (unique / plan / dispatch / gathered up GEMM /
     scattering down GEMM / combine) against the oracle for 4 and 8 ranks without needing that many GPUs."""
     from oracle import moe_oracle as O
     from tilelang_moe_b200 import ep, inputs, ops
+    monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)   # single-CTA kernel, or the CTA-pair kernel's gather / peer epilogue
     dev = cuda
-    El, k, H, I, Tl = 4, 4, 128, 64, 96
+    El, k, Tl = 4, 4, 96
     E, T = G * El, G * 96
     g = torch.Generator().manual_seed(G)
     x = torch.randn(T, H, generator=g).bfloat16()

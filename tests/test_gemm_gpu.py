@@ -96,14 +96,16 @@ def test_epilogues(cuda, lib):
     ops.check_status(cuda)
 
 
-@pytest.mark.parametrize("tile_rows", ["128", "256", "pair", "tn128", "tn256"])
-def test_both_tile_shapes_on_ragged_groups(cuda, lib, tile_rows, monkeypatch):
-    """128-row tiles, 256-row tiles (two MMAs sharing one B tile) and CTA-pair tiles (cta_group::2) on the same ragged problem: experts with
-    0, 1, 127, 128, 129, 255, 256, 257, 300 and 1000 rows exercise every tail case of both shapes."""
+@pytest.mark.parametrize("tile_rows", ["128", "pair"])
+@pytest.mark.parametrize("H,I", [(256, 256), (192, 512)])
+def test_both_tile_shapes_on_ragged_groups(cuda, lib, tile_rows, H, I, monkeypatch):
+    """The single-CTA kernel (128-row tiles) and the CTA-pair kernel (cta_group::2: 256-row tiles, and a 128-row tile
+    with 64 rows per CTA for an expert's last rows) on the same ragged problem: experts with 0, 1, 63, 64, 65, 127, 128,
+    129, 255, 256, 257, 300, 384, 385 and 1000 rows exercise every tail case of both kernels."""
     monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)
     g = torch.Generator().manual_seed(8)
-    sizes = [0, 1, 127, 128, 129, 255, 256, 257, 300, 1000, 0, 513]
-    E, H, I = len(sizes), 256, 256
+    sizes = [0, 1, 127, 128, 129, 255, 256, 257, 300, 1000, 0, 513, 63, 64, 65, 384, 385]
+    E = len(sizes)
     idx = torch.cat([torch.full((n,), e, dtype=torch.int64) for e, n in enumerate(sizes)])
     idx = idx[torch.randperm(idx.numel(), generator=g)]
     T = idx.numel()
@@ -140,12 +142,15 @@ def test_float16_inputs(cuda, lib):
     torch.testing.assert_close(y.float().cpu(), O.grouped_gemm(X, W, idx), rtol=2e-3, atol=2e-3)
 
 
+@pytest.mark.parametrize("tile_rows", ["128", "pair"])
 @pytest.mark.parametrize("T,k,H,I,E,dtype", [(300, 1, 64, 40, 3, torch.bfloat16), (1000, 2, 256, 384, 6, torch.bfloat16),
                                              (4096, 8, 1024, 512, 64, torch.bfloat16), (777, 4, 448, 264, 9, torch.float16),
-                                             (5, 2, 128, 64, 40, torch.bfloat16)])
-def test_fused_row_gather_is_bit_identical_to_gather_then_gemm(cuda, lib, T, k, H, I, E, dtype):
+                                             (5, 2, 128, 64, 40, torch.bfloat16), (2000, 4, 512, 256, 12, torch.bfloat16)])
+def test_fused_row_gather_is_bit_identical_to_gather_then_gemm(cuda, lib, T, k, H, I, E, dtype, tile_rows, monkeypatch):
     """The kernel's own row fetch (cp.async into the swizzled operand stage) must feed the tensor cores exactly
-    what the TMA path reads from a pre-gathered matrix: every output bit equal, for each epilogue."""
+    what the TMA path reads from a pre-gathered matrix: every output bit equal, for each epilogue, in the single-CTA
+    kernel and in the CTA-pair kernel (where the second CTA's rows are announced to the leader across the cluster)."""
+    monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)
     g = torch.Generator().manual_seed(T + k + H)
     x = torch.randn(T, H, generator=g).to(dtype).to(cuda)
     Wg = (torch.randn(E, I, H, generator=g) * 0.06).to(dtype).to(cuda)
@@ -178,9 +183,11 @@ def test_fused_row_gather_rejects_unsupported_k(cuda, lib):
         ops.grouped_gemm_sorted(ops.GEMM_PLAIN, x, W, offs, gather=perm)
 
 
-def test_scale_scatter_weight_read_at_destination(cuda, lib):
+@pytest.mark.parametrize("tile_rows", ["128", "pair"])
+def test_scale_scatter_weight_read_at_destination(cuda, lib, tile_rows, monkeypatch):
     """SCALE_SCATTER_DSTW reads the routing weight at the destination row (the [T,k] score matrix itself when
     dst = perm): same bits as SCALE_SCATTER fed with the weights gathered into sorted order."""
+    monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)
     g = torch.Generator().manual_seed(11)
     T, k, H, I, E = 900, 4, 256, 192, 10
     act = torch.randn(T * k, I, generator=g).bfloat16().to(cuda)
@@ -193,3 +200,29 @@ def test_scale_scatter_weight_read_at_destination(cuda, lib):
     got = ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER_DSTW, act, Wd, offsets, dst_rows=perm, row_w=scores.reshape(-1))
     ops.check_status(cuda)
     assert torch.equal(got, ref)
+
+
+def test_pair_kernel_gives_the_bits_of_the_single_cta_kernel(cuda, lib, monkeypatch):
+    """Both kernels accumulate every output element over K in the same order in fp32 and round once, so the tile
+    shape must not show in the result: SiLU-gate and scale-scatter outputs bit-equal on a ragged problem."""
+    g = torch.Generator().manual_seed(21)
+    sizes = [700, 3, 0, 130, 64, 257, 128, 1025]
+    E, H, I = len(sizes), 512, 384
+    idx = torch.cat([torch.full((n,), e, dtype=torch.int64) for e, n in enumerate(sizes)])
+    T = idx.numel()
+    x = torch.randn(T, H, generator=g).bfloat16().to(cuda)
+    Wg = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16().to(cuda)
+    Wu = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16().to(cuda)
+    Wd = (torch.randn(E, 256, I, generator=g) * 0.06).bfloat16().to(cuda)
+    offs = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device=cuda)
+    w = torch.rand(T, generator=g).to(cuda)
+    perm = torch.randperm(T, generator=g).int().to(cuda)
+    out = {}
+    for mode in ("128", "pair"):
+        monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", mode)
+        act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, x, Wg, offs, B2=Wu)
+        yk = ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER, act, Wd, offs, dst_rows=perm, row_w=w)
+        out[mode] = (act, yk)
+    ops.check_status(cuda)
+    assert torch.equal(out["128"][0], out["pair"][0])
+    assert torch.equal(out["128"][1], out["pair"][1])

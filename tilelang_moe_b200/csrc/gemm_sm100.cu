@@ -38,6 +38,7 @@
 
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <atomic>
 #include <mutex>
 #include <stdlib.h>
 
@@ -303,6 +304,24 @@ __device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const
   return t;
 }
 
+// tstart[e] = number of row tiles of the experts before e (tstart[E] = all of them); one warp, each lane a run of
+// consecutive experts
+__device__ __forceinline__ void tile_prefix(int32_t* tstart, const int32_t* offs, int E, int tile_rows, int lane) {
+  const int per = (E + 31) / 32;
+  const int e_lo = lane * per, e_hi = min(E, e_lo + per);
+  int sum = 0;
+  for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + tile_rows - 1) / tile_rows;
+  int inc = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+    if (lane >= o) inc += v;
+  }
+  int run = inc - sum;
+  for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + tile_rows - 1) / tile_rows; }
+  if (lane == 31) tstart[E] = inc;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -362,21 +381,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
   for (int e = threadIdx.x; e <= E; e += NUM_THREADS_GATHER) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
-  if (warp == 2) {  // prefix of M tiles per expert, one warp, chunks of consecutive experts per lane
-    const int per = (E + 31) / 32;
-    const int e_lo = lane * per, e_hi = min(E, e_lo + per);
-    int sum = 0;
-    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS;
-    int inc = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-      if (lane >= o) inc += v;
-    }
-    int run = inc - sum;
-    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS; }
-    if (lane == 31) tstart[E] = inc;
-  }
+  if (warp == 2) tile_prefix(tstart, offs, E, TILE_ROWS, lane);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -704,27 +709,49 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 
 // ------------------------------------------------------------------------------ CTA-pair kernel
-// The same pipeline on a cluster of two CTAs driving tcgen05 in cta_group::2 mode: one MMA covers a
-// 256-row x 256-column tile, 128 rows per CTA.  Each CTA stages only its own 128 rows of A and its own
-// half of the B tile (128 of the 256 N rows; for the SiLU-gate epilogue CTA 0 holds the gate rows and
-// CTA 1 the up rows), 32 KB per k-block instead of 48 KB.  Operand staging and operand reads share the
-// SM's shared-memory bandwidth, which is what caps the single-CTA shape; halving the B traffic lifts it.
+// The same pipeline on a cluster of two CTAs driving tcgen05 in cta_group::2 mode.  Two tile shapes in one
+// launch (a kernel may use only one cta_group, so the ragged tail has to run under cta_group::2 as well):
+//
+//   256-row tile   one M=256 x N=256 instruction per K step, 128 rows per CTA;
+//   128-row tile   the last tile of an expert when it holds no more than 128 rows: M=128 x N=256, 64 rows per
+//                  CTA.  The pair finishes it in half the time of a 256-row tile (measured: 70.8 against 133.9
+//                  clocks per K step), so row padding costs what it costs the single-CTA kernel, at most 127
+//                  rows per expert.  Its accumulator sits folded in tensor memory: lanes 0..63 of a CTA hold
+//                  its 64 rows x columns 0..127, lanes 64..127 the same rows x columns 128..255.
+//
+// Each CTA stages only its own rows of A and its own half of the B tile (128 of the 256 N rows), 32 KB per
+// k-block instead of the 48 KB of the single-CTA shape.  Operand staging (TMA writes) and operand reads (MMA)
+// share the SM's shared-memory bandwidth, 128 bytes per clock: 96 KB per k-block against 535 tensor clocks caps
+// the single-CTA shape near 70 % of the tensor pipe; 64 KB per k-block does not.
+//
+// SiLU-gate epilogue: the 256 N rows are ordered [gate f..f+63 | up f..f+63 | gate f+64..f+127 | up f+64..f+127]
+// (CTA 0 stages the first two boxes, CTA 1 the last two), so that gate and up of one output element meet in one
+// thread for both tile shapes.
 //
 //   full[s]    lives in CTA 0: its producer posts the byte count of both CTAs, both CTAs' TMA loads
 //              complete on it (cta_group::2 loads may signal the peer's barrier);
 //   empty[s]   one per CTA, released by the leader's tcgen05.commit (one commit per CTA's barrier);
 //   tfull[b]   one per CTA, same way; tempty[b] lives in CTA 0 and collects the epilogue warps of both.
+// Row gather: warps 6..7 of each CTA copy their CTA's rows with cp.async.  In CTA 0 every lane's copies complete
+// on full[s] directly; cp.async cannot signal another CTA's barrier, so in CTA 1 they complete on a local
+// barrier gfull[s], and warp 1 of CTA 1 (idle otherwise: only the leader issues MMAs) waits for it, makes the
+// rows visible to the async proxy and arrives on the leader's full[s] across the cluster.
 // No multicast load anywhere: every CTA fetches its own boxes.
 struct PairCfg {
   static constexpr int BN = 256;
-  static constexpr int A_BYTES = BM * BK * 2;            // 16 KB: this CTA's 128 rows
+  static constexpr int A_BYTES = BM * BK * 2;            // 16 KB: this CTA's rows (128, or 64 of a 128-row tile)
   static constexpr int B_BYTES = (BN / 2) * BK * 2;      // 16 KB: this CTA's half of the N rows
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = 6;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
-  static constexpr int SMEM_BYTES = TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 1024;
+  static constexpr int STAGING_OFFSET = (TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 127) & ~127;
+  static constexpr int SMEM_BYTES = STAGING_OFFSET + 1024;
+  static constexpr int STAGING_PITCH = 144;
+  static constexpr int SMEM_BYTES_PEER = SMEM_BYTES + 4 * 32 * STAGING_PITCH;
+  static_assert((3 * STAGES + 5) * 8 <= 200, "barriers fit below the tensor-memory slot");
+  static_assert(SMEM_BYTES_PEER <= 227 * 1024, "shared memory budget");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -778,22 +805,84 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc,
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__host__ __device__ constexpr uint32_t make_idesc_pair(int n, int f16 = 0) {   // M = 256 across the pair
-  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+// instruction descriptor for an M x N tile (M counted over the whole pair in cta_group::2 mode)
+__host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n, int f16 = 0) {
+  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// The leader's wait on full[s]: the gather path of CTA 1 arrives from the other SM with release.cluster.
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+__device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                               int site, uint64_t limit_ns = WAIT_LIMIT_NS) {
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > limit_ns) {
+      if (atomicExch((int*)abort_flag, 1) == 0 && status) {
+        status[0] = ST_WAIT_TIMEOUT;
+        status[1] = site;
+        status[2] = (int32_t)blockIdx.x;
+      }
+      return false;
+    }
+  }
+}
+
+// 32 consecutive output columns of one row, fp32 in registers -> 16-byte stores of the output type
+template <int EPI>
+__device__ __forceinline__ void store_row_chunk(const Params& p, void* ybase, int64_t out_row, int col, const uint32_t (&v)[32]) {
+  if (EPI == MOE_GEMM_PLAIN_F32) {
+    float* dst = reinterpret_cast<float*>(ybase) + out_row * p.ldy + col;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (col + j * 4 < p.N)
+        *reinterpret_cast<uint4*>(dst + j * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ybase) + out_row * p.ldy + col;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col + j * 8 < p.N) {
+        uint4 o;
+        o.x = pack_out(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), p.f16);
+        o.y = pack_out(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), p.f16);
+        o.z = pack_out(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), p.f16);
+        o.w = pack_out(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), p.f16);
+        *reinterpret_cast<uint4*>(dst + j * 8) = o;
+      }
+    }
+  }
 }
 
 template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const __grid_constant__ CUtensorMap tmB2, const Params p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS_GATHER, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
+                         const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
+                         const Params p) {
   using C = PairCfg;
   constexpr int STAGES = C::STAGES;
   constexpr int BN = C::BN;
   constexpr int TILE_ROWS = 2 * BM;
-  constexpr int OUT_COLS = EPI == MOE_GEMM_SILU_GATE ? BN / 2 : BN;
+  constexpr bool GATE = EPI == MOE_GEMM_SILU_GATE;
+  constexpr int OUT_COLS = GATE ? BN / 2 : BN;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain, [2S+5..3S+5) gfull
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFFSET + 200);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
   int32_t* tstart = reinterpret_cast<int32_t*>(smem + C::TABLE_OFFSET);
@@ -805,41 +894,36 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
   const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
+  const uint32_t gfull0 = smem_u32(bars + 2 * STAGES + 5);
   const uint32_t lead_full0 = map_to_cta(full0, 0), lead_tempty0 = map_to_cta(tempty0, 0);
   const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const bool gather = p.a_gather != nullptr;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    // full (used in CTA 0): the producer's arrive, + with a row gather one arrival per lane of CTA 0's two gather
+    // warps and one from CTA 1's forwarding warp
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, gather ? 66 : 1);
+      mbar_init(empty0 + 8 * s, 1);
+      mbar_init(gfull0 + 8 * s, 64);
+    }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tmA);
+    prefetch_tmap(&tmA64);
     prefetch_tmap(&tmB);
-    if (EPI == MOE_GEMM_SILU_GATE) prefetch_tmap(&tmB2);
+    if (GATE) prefetch_tmap(&tmB2);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish_pair();
   }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
+  for (int e = threadIdx.x; e <= E; e += NUM_THREADS_GATHER) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
-  if (warp == 2) {
-    const int per = (E + 31) / 32;
-    const int e_lo = lane * per, e_hi = min(E, e_lo + per);
-    int sum = 0;
-    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS;
-    int inc = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-      if (lane >= o) inc += v;
-    }
-    int run = inc - sum;
-    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + TILE_ROWS - 1) / TILE_ROWS; }
-    if (lane == 31) tstart[E] = inc;
-  }
+  if (warp == 2) tile_prefix(tstart, offs, E, TILE_ROWS, lane);
   tc_fence_before();
   __syncthreads();
   cluster_barrier();   // both CTAs' barriers are initialised before anything remote touches them
@@ -855,19 +939,24 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     bool ok = true;
     for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
       const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      const bool light = t.row_end - t.row0 <= BM;           // 128-row tile: 64 rows per CTA
       const int n0 = t.n_tile * OUT_COLS;
+      const int a_row = t.row0 + (int)rank * (light ? BM / 2 : BM);
+      const uint32_t tx = gather ? 2u * C::B_BYTES : (light ? 2u * (C::A_BYTES / 2 + C::B_BYTES) : 2u * C::STAGE_BYTES);
       for (int kb = 0; kb < NKB; ++kb) {
         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
         if (lane == 0) {
           const uint32_t lead_full = lead_full0 + 8 * stage;
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
           const uint32_t sb = sa + C::A_BYTES;
-          if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, 2 * C::STAGE_BYTES);
-          tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, t.row0 + (int)rank * BM);
-          if (EPI == MOE_GEMM_SILU_GATE)   // CTA 0 stages the gate rows, CTA 1 the up rows of the same columns
-            tma_load_3d_pair(sb, leader ? &tmB : &tmB2, lead_full, kb * BK, n0, t.e);
-          else
+          if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, tx);
+          if (!gather) tma_load_2d_pair(sa, light ? &tmA64 : &tmA, lead_full, kb * BK, a_row);
+          if (GATE) {   // this CTA's 64 gate rows, then its 64 up rows of the same output columns
+            tma_load_3d_pair(sb, &tmB, lead_full, kb * BK, n0 + (int)rank * (OUT_COLS / 2), t.e);
+            tma_load_3d_pair(sb + C::B_BYTES / 2, &tmB2, lead_full, kb * BK, n0 + (int)rank * (OUT_COLS / 2), t.e);
+          } else {
             tma_load_3d_pair(sb, &tmB, lead_full, kb * BK, n0 + (int)rank * (BN / 2), t.e);
+          }
         }
         __syncwarp();
         ++issued;
@@ -888,22 +977,25 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         mbar_wait_drain(full0 + 8 * (j % STAGES), (j / STAGES) & 1, DRAIN_LIMIT_NS);
     }
   } else if (warp == 1) {
-    // ===================================================================== MMA issuer (leader CTA only)
     if (leader) {
-      const uint32_t idesc = make_idesc_pair(BN, p.f16);
+      // ===================================================================== MMA issuer (leader CTA only)
+      const uint32_t idesc_h = make_idesc_mn(2 * BM, BN, p.f16), idesc_l = make_idesc_mn(BM, BN, p.f16);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
+        const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+        const uint32_t idesc = (t.row_end - t.row0 <= BM) ? idesc_l : idesc_h;
         if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < NKB; ++kb) {
-          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 13)) { ok = false; break; }
+          if (!mbar_wait_cluster(full0 + 8 * stage, phase, abort_flag, p.status, 13)) { ok = false; break; }
           tc_fence_after();
           if (lane == 0) {
+            if (gather) fence_proxy_async();   // this CTA's A rows were written by cp.async, not by the TMA unit
             const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
             const uint64_t adesc = make_smem_desc(sa);
             const uint64_t bdesc = make_smem_desc(sa + C::A_BYTES);
@@ -929,66 +1021,168 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         __syncwarp();
         mbar_wait_drain(drain_bar, 0, DRAIN_LIMIT_NS);
       }
+    } else if (gather) {
+      // ===================================================================== gather forwarder (CTA 1)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
+        for (int kb = 0; kb < NKB; ++kb) {
+          if (!mbar_wait(gfull0 + 8 * stage, phase, abort_flag, p.status, 16)) { ok = false; break; }
+          if (lane == 0) {
+            fence_proxy_async();                           // the rows become visible to the tensor core's reads
+            mbar_arrive_cluster(lead_full0 + 8 * stage);
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp >= 6) {
+    // ===================================================================== A-row gather (both CTAs, only when asked to)
+    // A 256-row tile: this CTA's 128 rows, 64 per warp; a 128-row tile: this CTA's 64 rows, 32 per warp.  8 lanes
+    // cover the 128 bytes of one row piece, so one cp.async instruction moves four row pieces.
+    if (gather) {
+      const unsigned char* src_base = reinterpret_cast<const unsigned char*>(p.a_src);
+      const size_t row_bytes = (size_t)p.K * 2;
+      const int chunk = lane & 7, sub = lane >> 3;
+      const uint32_t arrive0 = leader ? full0 : gfull0;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
+        const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+        const bool light = t.row_end - t.row0 <= BM;
+        const int rows_w = light ? 32 : 64;                                  // rows this warp copies
+        const int cta_row0 = (warp - 6) * rows_w;                            // first of them inside this CTA's A block
+        const int tile_row0 = t.row0 + (int)rank * (light ? BM / 2 : BM) + cta_row0;
+        uint32_t src_row[2];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          int r = tile_row0 + lane + 32 * s;
+          if (r > p.a_rows - 1) r = p.a_rows - 1;
+          const uint32_t v = (uint32_t)p.a_gather[r] / (uint32_t)p.a_div;
+          src_row[s] = v < (uint32_t)p.a_src_rows ? v : (uint32_t)(p.a_src_rows - 1);
+        }
+        const unsigned char* rp[16];
+        uint32_t live = 0;
+#pragma unroll
+        for (int it = 0; it < 16; ++it) {
+          const int row = it * 4 + sub;
+          const uint32_t sr = __shfl_sync(0xFFFFFFFFu, src_row[it >> 3], row & 31);
+          rp[it] = src_base + (size_t)sr * row_bytes + chunk * 16;
+          if (row < rows_w && tile_row0 + row < t.row_end) live |= 1u << it;
+        }
+        const int its = rows_w >> 2;
+        for (int kb = 0; kb < NKB; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES) + cta_row0 * 128;
+          const size_t koff = (size_t)kb * (BK * 2);
+#pragma unroll
+          for (int it = 0; it < 16; ++it) {
+            const int row = it * 4 + sub;
+            if (it < its)
+              cp_async_16(sa + row * 128 + ((chunk ^ (row & 7)) << 4), rp[it] + koff, (live >> it) & 1u ? 16u : 0u);
+          }
+          cp_async_arrive_noinc(arrive0 + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      cp_async_wait_all();
     }
   } else {
-    // ===================================================================== epilogue (both CTAs)
-    const int q = warp & 3;
+    // ===================================================================== epilogue (warps 2..5 of both CTAs)
+    const int q = warp & 3;                  // tensor-memory lane quarter this warp may read
+    const int l = q * 32 + lane;             // this thread's lane
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
       const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      const bool light = t.row_end - t.row0 <= BM;
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 14)) { ok = false; break; }
       tc_fence_after();
-      const int grow = t.row0 + (int)rank * BM + q * 32 + lane;
+      // 256-row tile: lane = row of this CTA's 128; 128-row tile: lanes 0..63 and 64..127 both hold this CTA's 64 rows,
+      // the upper lanes the second half of the columns
+      const int grow = t.row0 + (light ? (int)rank * (BM / 2) + (l & 63) : (int)rank * BM + l);
+      const int col_half = light ? (l >> 6) : 0;
       const bool row_ok = grow < t.row_end;
+      const bool any_rows = t.row0 + (light ? (int)rank * (BM / 2) + (q & 1) * 32 : (int)rank * BM + q * 32) < t.row_end;
       const int n0 = t.n_tile * OUT_COLS;
       int64_t out_row = grow;
       float w = 1.0f;
+      void* ybase = p.Y;
       if (row_ok) {
-        if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
+        if (!GATE && p.dst_rows) out_row = p.dst_rows[grow];
         if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[p.w_by_dst ? out_row : (int64_t)grow];
+        if (EPI == EPI_PEER) ybase = p.peer_base[p.row_rank[grow]];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      const bool any_rows = t.row0 + (int)rank * BM < t.row_end;   // warp-uniform: this CTA's half holds rows
+      if (GATE) {
+        // accumulator columns: [gate 64 | up 64] per group of 64 output columns; a 256-row tile holds two groups,
+        // a 128-row tile one per lane half
+        const int groups = light ? 1 : 2;
 #pragma unroll 1
-      for (int c = 0; any_rows && c < OUT_COLS / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(taddr + c * 32, v);
-        if (EPI == MOE_GEMM_SILU_GATE) {
-          uint32_t u[32];
-          tmem_ld32(taddr + BN / 2 + c * 32, u);
-          tmem_ld_wait();
+        for (int g = 0; any_rows && g < groups; ++g) {
+          const int cg = light ? 0 : g * 128;
+          const int fo = light ? col_half * 64 : g * 64;
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32], u[32];
+            tmem_ld32(taddr + cg + c * 32, v);
+            tmem_ld32(taddr + cg + 64 + c * 32, u);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
-        } else {
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+            const int col = n0 + fo + c * 32;
+            if (row_ok && col < p.N) store_row_chunk<MOE_GEMM_PLAIN>(p, ybase, out_row, col, v);
+          }
+        }
+      } else {
+        const int chunks = light ? 4 : 8;
+        const int cb = n0 + col_half * 128;
+#pragma unroll 1
+        for (int c = 0; any_rows && c < chunks; ++c) {
+          uint32_t v[32];
+          tmem_ld32(taddr + c * 32, v);
           tmem_ld_wait();
           if (EPI == MOE_GEMM_SCALE_SCATTER) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * w);
           }
-        }
-        const int col = n0 + c * 32;
-        if (row_ok && col < p.N) {
-          if (EPI == MOE_GEMM_PLAIN_F32) {
-            float* dst = reinterpret_cast<float*>(p.Y) + out_row * p.ldy + col;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (col + j * 4 < p.N)
-                *reinterpret_cast<uint4*>(dst + j * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.Y) + out_row * p.ldy + col;
+          const int col = cb + c * 32;
+          if (EPI == EPI_PEER) {
+            // two 32-column chunks of every row are parked in shared memory (this warp's 32 rows x 128 bytes), then
+            // written out with 8 lanes per row: each store instruction carries four 128-byte row segments
+            unsigned char* stg = smem + C::STAGING_OFFSET + (warp - 2) * 32 * C::STAGING_PITCH;
+            uint4* mine = reinterpret_cast<uint4*>(stg + lane * C::STAGING_PITCH + (c & 1) * 64);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              if (col + j * 8 < p.N) {
-                uint4 o;
-                o.x = pack_out(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), p.f16);
-                o.y = pack_out(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), p.f16);
-                o.z = pack_out(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), p.f16);
-                o.w = pack_out(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), p.f16);
-                *reinterpret_cast<uint4*>(dst + j * 8) = o;
-              }
+              uint4 o;
+              o.x = pack_out(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1]), p.f16);
+              o.y = pack_out(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]), p.f16);
+              o.z = pack_out(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]), p.f16);
+              o.w = pack_out(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]), p.f16);
+              mine[j] = o;
             }
+            if (c & 1) {
+              __syncwarp();
+              const unsigned long long row_ptr = row_ok
+                  ? reinterpret_cast<unsigned long long>(reinterpret_cast<__nv_bfloat16*>(ybase) + out_row * p.ldy) : 0ull;
+              const int col0 = col - 32;
+              const int seg = lane & 7;
+#pragma unroll
+              for (int it = 0; it < 8; ++it) {
+                const int r = it * 4 + (lane >> 3);
+                const unsigned long long rp = __shfl_sync(0xFFFFFFFFu, row_ptr, r);
+                const uint4 val = *reinterpret_cast<const uint4*>(stg + r * C::STAGING_PITCH + seg * 16);
+                if (rp != 0ull && col0 + seg * 8 < p.N)
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(rp) + col0 + seg * 8) = val;
+              }
+              __syncwarp();
+            }
+          } else if (row_ok && col < p.N) {
+            store_row_chunk<EPI>(p, ybase, out_row, col, v);
           }
         }
       }
@@ -1006,246 +1200,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
-  }
-}
-
-
-// ------------------------------------------------------------------------------ tokens-as-N kernel
-// Ragged groups waste tensor-core time when rows are padded to the 128-row M of the instruction: with a
-// Zipf expert load most experts own far fewer than 128 rows.  This kernel swaps the operands: the
-// weight tile is the M side (always 128 full rows of W[e]) and the expert's tokens are the N side, whose
-// extent may be any multiple of 16 up to TN, so padding costs at most 15 rows per group.
-//
-//   D[feature, token] (+)= W[e][feature, k] * X[token, k]^T        (both operands K-major, as stored)
-//
-// A tile = (expert, feature tile, chunk of <= TN tokens) and carries two weight tiles that share the
-// token tile: gate and up rows of the same 128 features (SiLU-gate epilogue), or features f0..f0+127 and
-// f0+128..f0+255 (plain / scale-scatter).  Accumulators are feature-major in TMEM (lane = feature,
-// column = token); the epilogue walks the token columns and stores 2-byte elements, 32 lanes covering 64
-// contiguous bytes of one output row.  TN=128 keeps two accumulator sets (epilogue overlaps the next
-// main loop), TN=256 one.
-template <int TN>
-struct TnCfg {
-  static constexpr int W_BYTES = BM * BK * 2;                 // one 128-feature weight tile, 16 KB
-  static constexpr int X_BYTES = TN * BK * 2;                 // token tile
-  static constexpr int STAGE_BYTES = 2 * W_BYTES + X_BYTES;
-  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;   // 4 (TN=128) or 3 (TN=256)
-  static constexpr int ACC_BUFS = TN == 128 ? 2 : 1;
-  static constexpr int TMEM_COLS = 512;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
-  static constexpr int SMEM_BYTES = TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 1024;
-};
-__host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n, int f16 = 0) {
-  return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-template <int TN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-grouped_gemm_tn_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmW2,
-                       const __grid_constant__ CUtensorMap tmX, const Params p) {
-  using C = TnCfg<TN>;
-  constexpr int STAGES = C::STAGES;
-  constexpr int ACC_BUFS = C::ACC_BUFS;
-  constexpr bool GATE = EPI == MOE_GEMM_SILU_GATE;
-  constexpr int FEAT_PER_TILE = GATE ? BM : 2 * BM;     // output features per tile
-  extern __shared__ unsigned char smem_dyn[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFFSET + 200);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
-  int32_t* tstart = reinterpret_cast<int32_t*>(smem + C::TABLE_OFFSET);
-  int32_t* offs = tstart + (MAX_E + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
-  const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
-  const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
-  const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
-    mbar_init(drain_bar, 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    prefetch_tmap(&tmW);
-    prefetch_tmap(&tmX);
-    if (GATE) prefetch_tmap(&tmW2);
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
-    tmem_relinquish();
-  }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
-  __syncthreads();
-  if (warp == 2) {  // prefix of token chunks per expert
-    const int per = (E + 31) / 32;
-    const int e_lo = lane * per, e_hi = min(E, e_lo + per);
-    int sum = 0;
-    for (int e = e_lo; e < e_hi; ++e) sum += (offs[e + 1] - offs[e] + TN - 1) / TN;
-    int inc = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
-      if (lane >= o) inc += v;
-    }
-    int run = inc - sum;
-    for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + TN - 1) / TN; }
-    if (lane == 31) tstart[E] = inc;
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = tstart[E] * NT;
-
-  if (warp == 0) {
-    // ===================================================================== TMA producer
-    int stage = 0;
-    uint32_t phase = 0;
-    uint32_t issued = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT, TN);
-      const int f0 = t.n_tile * FEAT_PER_TILE;
-      const bool have2 = GATE || (f0 + BM < p.N);
-      int cnt = t.row_end - t.row0;
-      if (cnt > TN) cnt = TN;
-      const int nbox = (cnt + 63) >> 6;                       // 64-token boxes actually needed
-      const uint32_t tx = (uint32_t)(C::W_BYTES * (have2 ? 2 : 1) + nbox * 64 * BK * 2);
-      for (int kb = 0; kb < NKB; ++kb) {
-        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
-        if (lane == 0) {
-          const uint32_t full = full0 + 8 * stage;
-          const uint32_t sw = smem_u32(smem + stage * C::STAGE_BYTES);
-          const uint32_t sx = sw + 2 * C::W_BYTES;
-          mbar_arrive_expect_tx(full, tx);
-          tma_load_3d(sw, &tmW, full, kb * BK, f0, t.e);
-          if (GATE) tma_load_3d(sw + C::W_BYTES, &tmW2, full, kb * BK, f0, t.e);
-          else if (have2) tma_load_3d(sw + C::W_BYTES, &tmW, full, kb * BK, f0 + BM, t.e);
-          for (int j = 0; j < nbox; ++j) tma_load_2d(sx + j * (64 * BK * 2), &tmX, full, kb * BK, t.row0 + 64 * j);
-        }
-        __syncwarp();
-        ++issued;
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
-      }
-    }
-    if (!ok) {
-      const uint32_t first = issued > (uint32_t)STAGES ? issued - STAGES : 0;
-      for (uint32_t j = first; j < issued; ++j)
-        mbar_wait_drain(full0 + 8 * (j % STAGES), (j / STAGES) & 1, DRAIN_LIMIT_NS);
-    }
-  } else if (warp == 1) {
-    // ===================================================================== MMA issuer
-    int stage = 0;
-    uint32_t phase = 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT, TN);
-      const bool have2 = GATE || (t.n_tile * FEAT_PER_TILE + BM < p.N);
-      int cnt = t.row_end - t.row0;
-      if (cnt > TN) cnt = TN;
-      const int n16 = (cnt + 15) & ~15;                        // instruction N: tokens rounded up to 16
-      const uint32_t idesc = make_idesc_mn(BM, n16, p.f16);
-      if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t d0 = tmem_base + (uint32_t)(acc * 2 * TN);
-      for (int kb = 0; kb < NKB; ++kb) {
-        if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 23)) { ok = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t sw = smem_u32(smem + stage * C::STAGE_BYTES);
-          const uint64_t w0 = make_smem_desc(sw), w1 = make_smem_desc(sw + C::W_BYTES);
-          const uint64_t xd = make_smem_desc(sw + 2 * C::W_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_bf16(d0, w0 + (uint64_t)(2 * k), xd + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
-            if (have2) umma_bf16(d0 + TN, w1 + (uint64_t)(2 * k), xd + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          umma_commit(empty0 + 8 * stage);
-        }
-        __syncwarp();
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
-      }
-      if (!ok) break;
-      if (lane == 0) umma_commit(tfull0 + 8 * acc);
-      __syncwarp();
-      if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
-    }
-    if (!ok) {
-      if (lane == 0) umma_commit(drain_bar);
-      __syncwarp();
-      mbar_wait_drain(drain_bar, 0, DRAIN_LIMIT_NS);
-    }
-  } else {
-    // ===================================================================== epilogue (warps 2..5)
-    const int q = warp & 3;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT, TN);
-      const int f0 = t.n_tile * FEAT_PER_TILE;
-      const bool have2 = GATE || (f0 + BM < p.N);
-      int cnt = t.row_end - t.row0;
-      if (cnt > TN) cnt = TN;
-      if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 24)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * TN);
-      const int n_pass = (GATE || !have2) ? 1 : 2;            // plain: second pass handles features f0+128..
-#pragma unroll 1
-      for (int pass = 0; pass < n_pass; ++pass) {
-        const int feat = f0 + pass * BM + q * 32 + lane;       // output column of this thread
-        const bool feat_ok = feat < p.N;
-#pragma unroll 1
-        for (int c = 0; c * 32 < cnt; ++c) {
-          uint32_t v[32];
-          tmem_ld32(t0 + pass * TN + c * 32, v);
-          if (GATE) {
-            uint32_t u[32];
-            tmem_ld32(t0 + TN + c * 32, u);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
-          } else {
-            tmem_ld_wait();
-          }
-          // per-token metadata: lane j holds the output row (and weight) of token column j of this chunk
-          const int tok = t.row0 + c * 32 + lane;
-          int my_dst = -1;
-          float my_w = 1.0f;
-          if (tok < t.row0 + cnt) {
-            my_dst = (!GATE && p.dst_rows) ? p.dst_rows[tok] : tok;
-            if (EPI == MOE_GEMM_SCALE_SCATTER) my_w = p.row_w[p.w_by_dst ? my_dst : tok];
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int d = __shfl_sync(0xFFFFFFFFu, my_dst, j);
-            float val = __uint_as_float(v[j]);
-            if (EPI == MOE_GEMM_SCALE_SCATTER) val *= __shfl_sync(0xFFFFFFFFu, my_w, j);
-            if (d >= 0 && feat_ok) {
-              if (EPI == MOE_GEMM_PLAIN_F32) reinterpret_cast<float*>(p.Y)[(int64_t)d * p.ldy + feat] = val;
-              else if (p.f16) reinterpret_cast<__half*>(p.Y)[(int64_t)d * p.ldy + feat] = __float2half_rn(val);
-              else reinterpret_cast<__nv_bfloat16*>(p.Y)[(int64_t)d * p.ldy + feat] = __float2bfloat16_rn(val);
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
-      if (++acc == ACC_BUFS) { acc = 0; acc_phase ^= 1; }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -1285,47 +1239,41 @@ static int make_tmap(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1,
   return MOE_OK;
 }
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel: one flag per (kernel, device)
+template <class Kernel>
+static int allow_dynamic_smem(Kernel kernel, int bytes, std::atomic<bool>* done_per_device) {
+  int dev = 0;
+  MOE_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(MOE_ERR_DEVICE, "device ordinal %d out of range", dev);
+  if (!done_per_device[dev].load(std::memory_order_acquire)) {
+    MOE_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done_per_device[dev].store(true, std::memory_order_release);
+  }
+  return MOE_OK;
+}
+
 template <int MT, int BN, int EPI>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
                   cudaStream_t st) {
   using C = Cfg<MT, BN>;
   constexpr int SMEM = EPI == EPI_PEER ? C::SMEM_BYTES_PEER : C::SMEM_BYTES;
-  static bool attr_set = false;   // per instantiation; the attribute is idempotent
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<MT, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    attr_set = true;
-  }
+  static std::atomic<bool> attr_set[64];
+  int rc = allow_dynamic_smem(grouped_gemm_kernel<MT, BN, EPI>, SMEM, attr_set);
+  if (rc) return rc;
   grouped_gemm_kernel<MT, BN, EPI><<<grid, NUM_THREADS_GATHER, SMEM, st>>>(tA, tB, tB2, p);
   MOE_CHECK_LAUNCH("grouped_gemm_kernel");
   return MOE_OK;
 }
 
 template <int EPI>
-static int launch_pair(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
-                       cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        PairCfg::SMEM_BYTES));
-    attr_set = true;
-  }
-  grouped_gemm_pair_kernel<EPI><<<grid, NUM_THREADS, PairCfg::SMEM_BYTES, st>>>(tA, tB, tB2, p);
+static int launch_pair(const CUtensorMap& tA, const CUtensorMap& tA64, const CUtensorMap& tB, const CUtensorMap& tB2,
+                       const Params& p, int grid, cudaStream_t st) {
+  constexpr int SMEM = EPI == EPI_PEER ? PairCfg::SMEM_BYTES_PEER : PairCfg::SMEM_BYTES;
+  static std::atomic<bool> attr_set[64];
+  int rc = allow_dynamic_smem(grouped_gemm_pair_kernel<EPI>, SMEM, attr_set);
+  if (rc) return rc;
+  grouped_gemm_pair_kernel<EPI><<<grid, NUM_THREADS_GATHER, SMEM, st>>>(tA, tA64, tB, tB2, p);
   MOE_CHECK_LAUNCH("grouped_gemm_pair_kernel");
-  return MOE_OK;
-}
-
-template <int TN, int EPI>
-static int launch_tn(const CUtensorMap& tW, const CUtensorMap& tW2, const CUtensorMap& tX, const Params& p, int grid,
-                     cudaStream_t st) {
-  using C = TnCfg<TN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    MOE_CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_tn_kernel<TN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        C::SMEM_BYTES));
-    attr_set = true;
-  }
-  grouped_gemm_tn_kernel<TN, EPI><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(tW, tW2, tX, p);
-  MOE_CHECK_LAUNCH("grouped_gemm_tn_kernel");
   return MOE_OK;
 }
 
@@ -1503,75 +1451,27 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   int rc = current_device_info(&dev);
   if (rc) return rc;
 
-  // Tile shape: a fixed rule on the problem size.  Ragged groups pay for row padding at the tile height, so
-  // the 128-row tile is the default; the CTA-pair kernel (256 rows over two SMs, half the B staging per SM)
-  // takes over when groups are large (>= 512 rows on average) and there are enough pair tiles for every SM.
-  // The single-CTA 256-row shape is kept for measurement (override below).
+  // Tile shape: a fixed rule on the problem size.  The CTA-pair kernel (256-row and 128-row tiles under
+  // cta_group::2, half the B staging per SM) is the default once there is enough work for every SM pair;
+  // smaller problems and narrow outputs take the single-CTA kernel with 128-row tiles, which spreads few
+  // tiles over twice as many independent CTAs.  MOE_B200_GEMM_TILE_ROWS = "128" | "pair" overrides (tests, measurement).
   const bool gate = epilogue == MOE_GEMM_SILU_GATE;
   const int n_tiles_256 = gate ? (N + 127) / 128 : (N + 255) / 256;
   const int64_t m_tiles_128 = live_rows / BM + E, m_tiles_256 = live_rows / (2 * BM) + E;
-  int MT = 1, BN = 128;
+  int BN = 128;
   if (gate || (N % 256 == 0 && m_tiles_128 * n_tiles_256 >= dev.sm_count)) BN = 256;
-  bool pair = !row_rank && !ga.idx && (gate || N % 256 == 0) && live_rows / E >= 512 &&
-              (live_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
-  if (pair) { MT = 2; BN = 256; }
-  // The tokens-as-N kernel is selected only by the override: measured on B200 it matches the rows-as-M
-  // kernel when groups are small (both stream weights at HBM speed) and loses when they are large
-  // (2-byte epilogue stores, more shared-memory reads per flop), so the default stays rows-as-M.
-  int tn = 0;
-  // peer scatter and row gather: 128-row kernel only
-  const char* force_env = (row_rank || ga.idx) ? nullptr : getenv("MOE_B200_GEMM_TILE_ROWS");
-  if (const char* force = force_env) {   // test / measurement override: "128", "256", "pair", "tn128", "tn256"
-    if (force[0] == 't') { tn = atoi(force + 2) == 128 ? 128 : 256; pair = false; }
-    else tn = 0;
-    if (force[0] == 'p' && (gate || N % 256 == 0)) { MT = 2; BN = 256; pair = true; }
-    else if (atoi(force) == 256 && (gate || N % 256 == 0)) { MT = 2; BN = 256; }
-    else if (atoi(force) == 128) { MT = 1; pair = false; if (gate) BN = 256; }
+  const bool pair_ok = (gate ? N % 64 == 0 : N % 256 == 0) && epilogue != MOE_GEMM_PLAIN_F32 && !(ga.idx && K % 64);
+  bool pair = pair_ok && (live_rows / BM) * n_tiles_256 >= 2 * (int64_t)dev.sm_count;
+  if (const char* force = getenv("MOE_B200_GEMM_TILE_ROWS")) {
+    if (force[0] == 'p') pair = pair_ok;
+    else if (atoi(force) == 128) pair = false;
   }
-  if (tn) {
-    Params q;
-    q.offsets = offsets; q.dst_rows = dst_rows; q.row_w = row_w; q.Y = Y; q.ldy = ldy;
-    q.K = K; q.N = N; q.E = E;
-    q.num_n_tiles = gate ? (N + BM - 1) / BM : (N + 2 * BM - 1) / (2 * BM);
-    q.num_k_blocks = (K + BK - 1) / BK;
-    q.status = status;
-    q.f16 = f16;
-    q.row_rank = nullptr;
-    for (int g = 0; g < 16; ++g) q.peer_base[g] = nullptr;
-    q.a_gather = nullptr; q.a_src = nullptr; q.a_div = 1; q.a_src_rows = 0; q.a_rows = 0; q.w_by_dst = w_by_dst;
-    q.dense_rows = (int)ga.dense_rows;
-    CUtensorMap tW, tW2, tX;
-    rc = make_tmap(&tW, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM, f16);
-    if (rc) return rc;
-    tW2 = tW;
-    if (gate) {
-      rc = make_tmap(&tW2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, BM, f16);
-      if (rc) return rc;
-    }
-    rc = make_tmap(&tX, A, (uint64_t)K, (uint64_t)max_rows, 0, 64, f16);
-    if (rc) return rc;
-    const int64_t tiles = (max_rows / tn + E) * q.num_n_tiles;
-    int g = (int)(tiles < dev.sm_count ? tiles : dev.sm_count);
-    if (g < 1) g = 1;
-    cudaStream_t st2 = reinterpret_cast<cudaStream_t>(stream);
-#define MOE_TN_CASE(EPI_)                                                        \
-    if (tn == 128) return launch_tn<128, EPI_>(tW, tW2, tX, q, g, st2);            \
-    return launch_tn<256, EPI_>(tW, tW2, tX, q, g, st2)
-    switch (epilogue) {
-      case MOE_GEMM_PLAIN: MOE_TN_CASE(MOE_GEMM_PLAIN);
-      case MOE_GEMM_SCALE_SCATTER: MOE_TN_CASE(MOE_GEMM_SCALE_SCATTER);
-      case MOE_GEMM_PLAIN_F32: MOE_TN_CASE(MOE_GEMM_PLAIN_F32);
-      default: MOE_TN_CASE(MOE_GEMM_SILU_GATE);
-    }
-#undef MOE_TN_CASE
-  }
-  const int64_t m_tiles_bound = MT == 2 ? m_tiles_256 : m_tiles_128;
   const int out_cols = gate ? BN / 2 : BN;
 
   Params p;
   p.offsets = offsets; p.dst_rows = dst_rows; p.row_w = row_w; p.Y = Y; p.ldy = ldy;
   p.K = K; p.N = N; p.E = E;
-  p.num_n_tiles = (N + out_cols - 1) / out_cols;
+  p.num_n_tiles = pair ? n_tiles_256 : (N + out_cols - 1) / out_cols;
   p.num_k_blocks = (K + BK - 1) / BK;
   p.status = status;
   p.f16 = f16;
@@ -1581,52 +1481,61 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   p.dense_rows = (int)ga.dense_rows;
   p.a_gather = ga.idx; p.a_src = A; p.a_div = ga.div; p.a_src_rows = (int)ga.src_rows; p.a_rows = (int)max_rows;
 
-  CUtensorMap tA, tB, tB2;
-  // with a row gather A is the un-permuted matrix (src_rows rows) and its tensor map is never used by the kernel
+  CUtensorMap tA, tA64, tB, tB2;
+  // with a row gather A is the un-permuted matrix (src_rows rows) and its tensor maps are never used by the kernel
   const uint64_t a_map_rows = ga.idx ? (uint64_t)ga.src_rows : (uint64_t)max_rows;
-  rc = make_tmap(&tA, A, (uint64_t)K, a_map_rows, 0, (uint32_t)(pair ? BM : MT * BM), f16);
+  rc = make_tmap(&tA, A, (uint64_t)K, a_map_rows, 0, (uint32_t)BM, f16);
   if (rc) return rc;
-  uint32_t b_box_rows = pair ? 128u : (uint32_t)out_cols;   // a CTA of a pair stages 128 N rows
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (pair) {
+    rc = make_tmap(&tA64, A, (uint64_t)K, a_map_rows, 0, (uint32_t)(BM / 2), f16);
+    if (rc) return rc;
+    // a CTA of the pair stages 128 of the 256 N rows: one box, or a 64-row gate box and a 64-row up box
+    const uint32_t box = gate ? 64u : 128u;
+    rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, box, f16);
+    if (rc) return rc;
+    tB2 = tB;
+    if (gate) {
+      rc = make_tmap(&tB2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, box, f16);
+      if (rc) return rc;
+    }
+    const int64_t units = m_tiles_256 * p.num_n_tiles;
+    int pgrid = (int)(2 * units < dev.sm_count ? 2 * units : dev.sm_count) & ~1;
+    if (pgrid < 2) pgrid = 2;
+    if (row_rank) return launch_pair<EPI_PEER>(tA, tA64, tB, tB2, p, pgrid, st);
+    switch (epilogue) {
+      case MOE_GEMM_PLAIN: return launch_pair<MOE_GEMM_PLAIN>(tA, tA64, tB, tB2, p, pgrid, st);
+      case MOE_GEMM_SCALE_SCATTER: return launch_pair<MOE_GEMM_SCALE_SCATTER>(tA, tA64, tB, tB2, p, pgrid, st);
+      default: return launch_pair<MOE_GEMM_SILU_GATE>(tA, tA64, tB, tB2, p, pgrid, st);
+    }
+  }
+  uint32_t b_box_rows = (uint32_t)out_cols;
   // fewer weight rows than tile columns: fetch only those (the rest of the B stage keeps whatever it held; the
   // accumulator columns it feeds are never stored)
-  if (!pair && !gate && N < out_cols) b_box_rows = (uint32_t)N;
+  if (!gate && N < out_cols) b_box_rows = (uint32_t)N;
   p.b_tx_bytes = (int)b_box_rows * BK * 2 * (gate ? 2 : 1);
   rc = make_tmap(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows, f16);
   if (rc) return rc;
   tB2 = tB;
-  if (epilogue == MOE_GEMM_SILU_GATE) {
+  if (gate) {
     rc = make_tmap(&tB2, B2, (uint64_t)K, (uint64_t)N, (uint64_t)E, b_box_rows, f16);
     if (rc) return rc;
   }
-  int64_t tiles_bound = m_tiles_bound * p.num_n_tiles;
+  const int64_t tiles_bound = m_tiles_128 * p.num_n_tiles;
   int grid = (int)(tiles_bound < dev.sm_count ? tiles_bound : dev.sm_count);
   if (grid < 1) grid = 1;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (pair) {
-    int pgrid = (int)(2 * tiles_bound < dev.sm_count ? 2 * tiles_bound : dev.sm_count) & ~1;
-    if (pgrid < 2) pgrid = 2;
-    switch (epilogue) {
-      case MOE_GEMM_PLAIN: return launch_pair<MOE_GEMM_PLAIN>(tA, tB, tB2, p, pgrid, st);
-      case MOE_GEMM_SCALE_SCATTER: return launch_pair<MOE_GEMM_SCALE_SCATTER>(tA, tB, tB2, p, pgrid, st);
-      case MOE_GEMM_PLAIN_F32: return launch_pair<MOE_GEMM_PLAIN_F32>(tA, tB, tB2, p, pgrid, st);
-      default: return launch_pair<MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, pgrid, st);
-    }
-  }
-  if (row_rank) {   // combine exchange fused into the epilogue: 128-row tiles, 256 (or 128) accumulator columns
+  if (row_rank) {   // combine exchange fused into the epilogue
     if (BN == 256) return launch<1, 256, EPI_PEER>(tA, tB, tB2, p, grid, st);
     return launch<1, 128, EPI_PEER>(tA, tB, tB2, p, grid, st);
   }
 #define MOE_GEMM_CASE(EPI_)                                                                  \
-  if (MT == 2) return launch<2, 256, EPI_>(tA, tB, tB2, p, grid, st);                          \
   if (BN == 256) return launch<1, 256, EPI_>(tA, tB, tB2, p, grid, st);                        \
   return launch<1, 128, EPI_>(tA, tB, tB2, p, grid, st)
   switch (epilogue) {
     case MOE_GEMM_PLAIN: MOE_GEMM_CASE(MOE_GEMM_PLAIN);
     case MOE_GEMM_SCALE_SCATTER: MOE_GEMM_CASE(MOE_GEMM_SCALE_SCATTER);
     case MOE_GEMM_PLAIN_F32: MOE_GEMM_CASE(MOE_GEMM_PLAIN_F32);
-    default:
-      if (MT == 2) return launch<2, 256, MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, grid, st);
-      return launch<1, 256, MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, grid, st);
+    default: return launch<1, 256, MOE_GEMM_SILU_GATE>(tA, tB, tB2, p, grid, st);
   }
 #undef MOE_GEMM_CASE
 }
