@@ -41,6 +41,12 @@ WORKLOADS = {
     "c5_shard8": dict(T=1024, H=7168, I=2048, E=32, k=8, S=0, desc="one rank's share of c5 at 8-way expert parallelism"),
     "c3": dict(T=1024, H=2048, I=512, E=8, k=2, S=1, desc="FusedMoE small, 8 routed top-2 + 1 shared"),
 }
+C2 = dict(T=4096, H=1024, I=256, E=8, k=2)   # grouped expert GEMM of the benchmark contract (--workload c2)
+
+
+def workload_name(name, cfg):
+    """The `config.workload` string: the same text in the GPU arm and in the reference arm."""
+    return f"{name}: {cfg['desc']}" + (" [diagnostic: balanced load]" if BALANCED else "")
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -163,78 +169,131 @@ def make_weights(cfg, device, experts=None, seed=1234):
 
 
 # --------------------------------------------------------------------------------------- CPU arm
-def cpu_sample(cfg, x, logits, weights_for, target_rows=4096):
-    """Time the oracle's routed-expert loop (port of the reference's PyTorch CPU path, bf16)
-    on the experts of this batch in ascending id until about `target_rows` routed rows are
-    covered; scale to the whole batch by routed rows.  Returns (tokens_per_s, description)."""
-    from oracle import moe_oracle as O
-    T, k, E = cfg["T"], cfg["k"], cfg["E"]
-    t0 = time.perf_counter()
-    scores, idx = O.topk_softmax(logits, k, "A")
-    counts, offsets, perm, _ = O.route_histogram(idx, E)
-    t_route = time.perf_counter() - t0
-    token_of = perm.long() // k
-    flat_scores = scores.reshape(-1, 1).bfloat16()
-    cache = torch.zeros(T, cfg["H"], dtype=torch.bfloat16)
-    rows_done, n_exp, t_ffn = 0, 0, 0.0
-    for e in range(E):
-        s, t = int(offsets[e]), int(offsets[e + 1])
-        if s == t:
-            continue
-        Wg, Wu, Wd = weights_for(e)
-        tok = token_of[s:t]
-        t1 = time.perf_counter()
-        out = O.expert_ffn(x[tok], Wg, Wu, Wd) * flat_scores[perm.long()[s:t]]
-        cache.index_add_(0, tok, out)
-        t_ffn += time.perf_counter() - t1
-        rows_done += t - s
-        n_exp += 1
-        if rows_done >= target_rows:
-            break
-    total_rows = T * k
-    est = t_route + t_ffn * total_rows / max(rows_done, 1)
-    desc = (f"oracle port (torch CPU, bf16), routing of all {T} tokens + first {n_exp} non-empty experts "
-            f"({rows_done} of {total_rows} routed rows, {t_ffn:.2f} s), scaled by routed rows")
-    return T / est, desc
+def load_reference():
+    """The reference's own CPU baseline modules, loaded by path from oracle/_ref (copied there, unmodified, by
+    oracle/build.py on a machine that has the reference checkout).  None where that folder is absent."""
+    import importlib.util
+    d = ROOT / "oracle" / "_ref"
+    mods = {}
+    for name in ("topk_softmax_baseline", "grouped_gemm_baseline", "fusedmoe_baseline"):
+        f = d / (name + ".py")
+        if not f.exists():
+            return None
+        spec = importlib.util.spec_from_file_location("moe_reference_" + name, f)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mods[name] = mod
+    return mods
 
 
-def run_reference_arm(args, cfg):
-    """The reference's CPU path (the oracle port: the reference checkout is not on the GPU box)."""
+CPU_SAMPLE_TOKENS = 2048   # routed workloads: tokens of the batch one CPU pass covers (every expert, same routing law)
+
+
+class CpuRouted:
+    """One CPU pass of the routed layer over the first CPU_SAMPLE_TOKENS tokens of the batch, all experts, bf16:
+    the reference's own `topk_softmax_separate` + `FusedMoEPyTorch._compute_routed_experts` when its files are
+    present (kind "reference"), else the oracle's restatement of them (kind "port").  The GPU arm's cpu_baseline leg
+    and the reference arm both time exactly this object, so the two agree."""
+
+    def __init__(self, cfg, x, logits, Wg, Wu, Wd):
+        self.cfg = cfg
+        self.ts = min(CPU_SAMPLE_TOKENS, cfg["T"])
+        self.x, self.logits = x[:self.ts].contiguous(), logits[:self.ts].contiguous()
+        self.W = (Wg, Wu, Wd)
+        self.ref = load_reference()
+        self.kind = "reference" if self.ref is not None else "port"
+        if self.ref is not None:
+            self.model = self.ref["fusedmoe_baseline"].FusedMoEPyTorch(cfg["H"], cfg["I"], cfg["E"], 0, cfg["k"])
+
+    def one_pass(self):
+        k = self.cfg["k"]
+        with torch.no_grad():
+            if self.ref is not None:
+                scores, idx = self.ref["topk_softmax_baseline"].topk_softmax_separate(self.logits, k)
+                return self.model._compute_routed_experts(self.x, idx, scores.to(self.x.dtype), *self.W)
+            from oracle import moe_oracle as O
+            scores, idx = O.topk_softmax(self.logits, k, "A")
+            return O.routed_experts(self.x, idx, scores, *self.W)
+
+    def time(self, steps, warmup):
+        for _ in range(warmup):
+            self.one_pass()
+        vals = []
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            self.one_pass()
+            vals.append(self.ts / (time.perf_counter() - t0))
+        return vals
+
+    def describe(self):
+        who = ("the reference's own kernels/topk_softmax_baseline.py + kernels/fusedmoe_baseline.py (unmodified copies)"
+               if self.kind == "reference" else "oracle port of the reference's PyTorch path")
+        return (f"{who}, torch CPU bf16; one pass = routing + routed experts + scatter-reduce of the first {self.ts} of "
+                f"{self.cfg['T']} tokens over all {self.cfg['E']} experts ({self.ts * self.cfg['k']} routed rows)")
+
+
+def host_weights(cfg, seed=1234):
+    """Stacked bf16 expert weights on the host: the GPU arm's generator (seed + expert id) run on the GPU when there is
+    one and copied back, so that both arms multiply the same numbers; on a box without a GPU one expert's weights are
+    drawn on the CPU and shared by every expert (same arithmetic, same bytes per expert)."""
+    E, H, I = cfg["E"], cfg["H"], cfg["I"]
+    if torch.cuda.is_available():
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        Wg, Wu, Wd = make_weights(cfg, dev, seed=seed)
+        out = tuple(w.cpu() for w in (Wg, Wu, Wd))
+        del Wg, Wu, Wd
+        torch.cuda.empty_cache()
+        return out
+    g = torch.Generator().manual_seed(seed)
+    one = [(torch.randn(*sh, generator=g) * 0.02).bfloat16() for sh in ((I, H), (I, H), (H, I))]
+    return tuple(w.unsqueeze(0).expand(E, *w.shape) for w in one)
+
+
+def run_reference_arm(args, name, cfg):
+    """The reference's CPU path on the host cores of this box, all threads: same metric, config and unit as the GPU arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    x, logits = make_inputs(cfg)
-    cache = {}
-
-    def weights_for(e):
-        if e not in cache:
-            g = torch.Generator().manual_seed(1234 + e)
-            H, I = cfg["H"], cfg["I"]
-            cache[e] = tuple((torch.randn(*s, generator=g) * 0.02).bfloat16() for s in ((I, H), (I, H), (H, I)))
-        return cache[e]
-
-    target = max(512, min(12288, cfg["T"] * cfg["k"]))   # bounded: CPU weight generation costs ~0.3 s per expert
-    for _ in range(args.warmup):
-        cpu_sample(cfg, x, logits, weights_for, target_rows=256)
-    vals, desc = [], ""
-    for _ in range(args.steps):
-        v, desc = cpu_sample(cfg, x, logits, weights_for, target_rows=target)
-        vals.append(v)
-    v = statistics.median(vals)
     cores = torch.get_num_threads()
+    if cfg["S"] > 0:
+        from tilelang_moe_b200 import kernels
+        xc, wc = kernels.generate_fusedmoe_inputs(1, cfg["T"], cfg["H"], cfg["I"], cfg["E"], cfg["S"], cfg["k"],
+                                                  dtype=torch.bfloat16, device="cpu", seed=42)
+        names = ["router_weight", "shared_gate", "shared_up", "shared_down", "routed_gate", "routed_up", "routed_down"]
+        ref = load_reference()
+        if ref is not None:
+            fn = lambda: ref["fusedmoe_baseline"].fusedmoe_pytorch(xc, *[wc[n] for n in names], cfg["k"])
+            kind, desc = "reference", "the reference's own kernels/fusedmoe_baseline.py fusedmoe_pytorch, whole layer, torch CPU bf16"
+        else:
+            from oracle import moe_oracle as O
+            fn = lambda: O.fusedmoe(xc, *[wc[n] for n in names], cfg["k"], compute_dtype=torch.bfloat16)
+            kind, desc = "port", "oracle port of the reference's fusedmoe_pytorch, whole layer, torch CPU bf16"
+        for _ in range(args.warmup):
+            fn()
+        vals = []
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            fn()
+            vals.append(cfg["T"] / (time.perf_counter() - t0))
+    else:
+        x, logits = make_inputs(cfg)
+        cpu = CpuRouted(cfg, x, logits, *host_weights(cfg))
+        vals = cpu.time(args.steps, args.warmup)
+        kind, desc = cpu.kind, cpu.describe()
+    v = statistics.median(vals)
     line = {"metric": METRIC, "value": v, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": cfg["T"] / v * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, **{k_: cfg[k_] for k_ in ("T", "H", "I", "E", "k")}},
-            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+            "config": {"workload": workload_name(name, cfg), **{k_: cfg[k_] for k_ in ("T", "H", "I", "E", "k")}},
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------------------------------- GPU arm
-def run_ours(args, cfg):
+def run_ours(args, wl_name, cfg):
     import torch.distributed as dist
     from tilelang_moe_b200 import _lib, ep, layer, ops
     _lib.load()   # fails loudly if the CUDA library is missing
@@ -304,7 +363,7 @@ def run_ours(args, cfg):
             layer.routed_forward(xd, sc, ix, Wg, Wu, Wd, ws, out=outd)
 
         from tilelang_moe_b200.pipeline import HostPipeline
-        pipe = HostPipeline(dev, [x_pin, lg_pin], (T, H), torch.bfloat16, compute)
+        pipe = HostPipeline(dev, [x_pin, lg_pin], (T, H), torch.bfloat16, compute, depth=3)
 
         def step_e2e(n=1):
             pipe.run(n)
@@ -368,6 +427,16 @@ def run_ours(args, cfg):
     ms, stage_events, clocks = timed(step, args.steps, with_timers=True)
     host_enqueue_ms = host_ms[0]
     ops.check_status(dev)
+    # A step of the sharded layer lasts about a millisecond: K of them are too short a sample.  The block of K steps is
+    # repeated until at least half a second has been timed and the median block is reported (every rank sees the same
+    # all-reduced time, so all of them stop after the same block).
+    block_ms = [ms]
+    if world > 1:
+        while sum(block_ms) < 500.0 and len(block_ms) < 200:
+            m2, ev2, _ = timed(step, args.steps, with_timers=True)
+            block_ms.append(m2)
+            stage_events += ev2
+        ms = statistics.median(block_ms)
     # end to end: every step uploads its inputs from pinned host memory and downloads its result; where the
     # closure takes a step count the steps are pipelined (copies of neighbouring steps overlap the compute)
     import inspect
@@ -400,16 +469,19 @@ def run_ours(args, cfg):
         achieved = flops / (stage_ms["up_gemm"] * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         # DRAM traffic per launch: ncu capture of the c5_shard8 workload (32 experts, 8192 rows of 1024 tokens: 2.009 GB
-        # read + 0.031 GB written; summary under profiles/) = weights x 1.04 + the activations once +
+        # read + 0.031 GB written) = weights x 1.04 + the activations once +
         # the output once; it grows with the experts touched and the rows, so it is scaled by both to this launch.
         # On one GPU the kernel gathers its rows from the T x H activations (L2-resident, read once); with expert
         # parallelism it reads the rows x H receive buffer.
         per_expert = 2 * I * H * 2 * 1.04
         a_bytes = T * H * 2 if world == 1 else rows * H * 2
         traffic = (E if world == 1 else E / world) * per_expert + a_bytes + rows * I * 2
-        roofline = {"kernel": "grouped_gemm_kernel<1,256,SILU_GATE> (up GEMM, tcgen05)", "bound": "tensor",
+        roofline = {"kernel": "grouped_gemm_kernel<1,256,SILU_GATE> (up GEMM, tcgen05, rows gathered by the kernel)", "bound": "tensor",
                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "peak_source": peaks["source"] + " (sustained cuBLAS bf16)", "traffic": traffic,
+                    "peak_source": peaks["source"] + " (sustained cuBLAS bf16: the kernel is timed inside back-to-back steps)",
+                    "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"], "peak_sustained": peaks["bf16_tflops_sustained"],
+                    "frac_of_burst": achieved / peaks["bf16_tflops"], "peak_burst": peaks["bf16_tflops"],
+                    "frac_of_nominal_2250": achieved / 2250.0, "traffic": traffic,
                     "traffic_source": "ncu capture of c5_shard8 scaled by experts and rows",
                     "hbm_frac_of_measured": traffic / (stage_ms["up_gemm"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
                     "ms_per_launch": stage_ms["up_gemm"]}
@@ -421,12 +493,50 @@ def run_ours(args, cfg):
                     "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                     "peak_source": peaks["source"] + " (burst cuBLAS bf16)", "traffic": None,
                     "note": "19.4 GFLOP in ~10 launches: launch latency, not the tensor pipe, bounds this size"}
+    # ---- parity on sampled tokens (after the timed regions, every rank its own tokens), routed workloads only
+    parity = None
+    if cfg["S"] == 0 and not args.no_parity:
+        n_check = 32 if world == 1 else 16
+        Tl = T // world
+        lo = rank * Tl
+        local = torch.linspace(0, Tl - 1, n_check).long().unique()
+        out_dev = step()
+        torch.cuda.synchronize()
+        got = out_dev.view(Tl, H)[local.to(dev)].float().cpu()
+        if world == 1:
+            weight_of = lambda e: (Wg[e].cpu(), Wu[e].cpu(), Wd[e].cpu())
+        else:   # any rank can regenerate any expert: the generator is seeded by the expert id
+            weight_of = lambda e: tuple(w[0].cpu() for w in make_weights(cfg, dev, experts=[e]))
+        mine, idx_ref = parity_block(cfg, x_cpu, logits_cpu, local + lo, got, weight_of)
+        _, idx_gpu = ops.topk_softmax(logits_cpu[local + lo].to(dev), k, mode="A")
+        mine["routing_bit_exact"] = bool(torch.equal(idx_gpu.cpu(), idx_ref))
+        ops.check_status(dev)
+        if world > 1:
+            allp = [None] * world
+            dist.all_gather_object(allp, mine)
+        else:
+            allp = [mine]
+        parity = {"checked_tokens": sum(p_["checked_tokens"] for p_ in allp),
+                  "max_err_over_tol": max(p_["max_err_over_tol"] for p_ in allp),
+                  "routing_bit_exact": all(p_["routing_bit_exact"] for p_ in allp),
+                  "ok": all(p_["ok"] and p_["routing_bit_exact"] for p_ in allp),
+                  "how": "CPU oracle (fp32 on the bf16 inputs) of sampled tokens of every rank, 1e-2 rel + 2e-2 abs; "
+                         "top-k indices equal to the oracle's"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    cpu_v, cpu_desc = None, None
+    # ---- the rest of the metric: TopK+softmax us, the grouped-GEMM configuration, the small fused layer (1 GPU)
+    extra = {}
+    if world == 1 and wl_name == "c5" and not args.no_extra:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        extra["router"] = router_block(dev, peaks, flush, not args.no_cpu)
+        extra["c2"] = c2_block(dev, peaks, flush, not args.no_cpu)
+        extra["c3"] = c3_block(dev)
+        del flush
+
+    cpu_v, cpu_desc, cpu_kind = None, None, "port"
     if world == 1 and cfg["S"] > 0 and not args.no_cpu:
         from oracle import moe_oracle as O
         torch.set_num_threads(os.cpu_count() or 1)
@@ -436,23 +546,21 @@ def run_ours(args, cfg):
         for _ in range(3):
             O.fusedmoe(xc, *ws_cpu, k, compute_dtype=torch.bfloat16)
         cpu_v = T / ((time.perf_counter() - t0) / 3)
-        cpu_desc = "oracle port (torch CPU, bf16) of the whole layer, mean of 3 full passes"
+        cpu_desc, cpu_kind = "oracle port (torch CPU, bf16) of the whole layer, mean of 3 full passes", "port"
     elif world == 1 and not args.no_cpu:
         torch.set_num_threads(os.cpu_count() or 1)
-
-        def weights_for(e):
-            return Wg[e].cpu(), Wu[e].cpu(), Wd[e].cpu()
-
-        # the whole batch: every expert's weights are copied back from the GPU one expert at a time (outside the
-        # timed part), so the CPU computes exactly the layer the GPU computed
-        cpu_v, cpu_desc = cpu_sample(cfg, x_cpu, logits_cpu, weights_for, target_rows=T * k)
+        # the GPU's own weights copied back (outside the timed part): the CPU multiplies the numbers the GPU multiplied
+        cpu = CpuRouted(cfg, x_cpu, logits_cpu, Wg.cpu(), Wu.cpu(), Wd.cpu())
+        cpu_v = statistics.median(cpu.time(3, 1))
+        cpu_desc, cpu_kind = cpu.describe(), cpu.kind
+        del cpu
 
     value = tokens_per_step * args.steps / (ms * 1e-3)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {cfg['desc']}" + (" [diagnostic: balanced load]" if BALANCED else ""), "T": T, "H": H, "I": I, "E": E, "k": k,
+        "config": {"workload": workload_name(wl_name, cfg), "T": T, "H": H, "I": I, "E": E, "k": k,
                    "parallelism": parallelism, "l2": "per-step inputs (weights) exceed L2 many times over; no flush",
                    "load_imbalance_max_over_mean": imbalance},
         "e2e": {"value": tokens_per_step * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
@@ -465,13 +573,181 @@ def run_ours(args, cfg):
         "stage_ms_by_rank": stage_ms_by_rank,
         "roofline": roofline,
         "clocks": clocks,
+        "parity": parity,
+        **extra,
     }
+    if world > 1:
+        line["timed_blocks"] = {"blocks": len(block_ms), "steps_per_block": args.steps, "timed_s": round(sum(block_ms) / 1e3, 3),
+                                "ms_per_step_min": min(block_ms) / args.steps, "ms_per_step_max": max(block_ms) / args.steps}
     if cpu_v is not None:
-        line["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+        line["cpu_baseline"] = {"value": cpu_v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": cpu_kind,
                                 "sample": cpu_desc}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------------------- side blocks of the default line
+def _event_us(fn, iters, flush=None):
+    """Median CUDA-event time (us) of one call of fn on the current stream, L2 flushed before each call."""
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3)
+    return statistics.median(times)
+
+
+def _graph_us(fn, n=20):
+    """Per-call time (us) of n back-to-back calls replayed as one CUDA graph: launch latency amortised."""
+    graph = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        fn()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=s):
+            for _ in range(n):
+                fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / n
+
+
+ROUTER_POINTS = [("c1", 320, 128, 6), ("c4", 64, 32768, 2048), ("c1_M1048576", 1 << 20, 128, 6), ("c4_M4096", 4096, 32768, 2048)]
+
+
+def router_block(dev, peaks, flush, with_cpu):
+    """TopK+softmax: the two fixed configurations (launch-latency bound: us eager and inside a graph) and one large
+    batch of each shape (where HBM is the limit: fraction of the measured copy bandwidth)."""
+    from tilelang_moe_b200 import ops
+    ref = load_reference() if with_cpu else None
+    out = {}
+    for name, M, N, k in ROUTER_POINTS:
+        g = torch.Generator().manual_seed(0)
+        lg_cpu = torch.randn(M, N, generator=g) if M * N <= (1 << 22) else None
+        lg = lg_cpu.to(dev) if lg_cpu is not None else torch.randn(M, N, device=dev)
+        fn = lambda: ops.topk_softmax(lg, k)
+        for _ in range(3):
+            fn()
+        us = _event_us(fn, 20, flush)
+        byts = M * N * 4 + M * k * 12
+        row = {"M": M, "N": N, "k": k, "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
+               "frac_hbm_measured": round(byts / us / 1e3 / peaks["hbm_gbs"], 3)}
+        if lg_cpu is not None:
+            row["us_in_graph"] = round(_graph_us(fn), 2)
+            if with_cpu:
+                f_cpu = (ref["topk_softmax_baseline"].topk_softmax_fused if ref is not None
+                         else __import__("oracle.moe_oracle", fromlist=["x"]).topk_softmax)
+                f_cpu(lg_cpu, k)
+                t0 = time.perf_counter()
+                for _ in range(5):
+                    f_cpu(lg_cpu, k)
+                row["cpu_us"] = round((time.perf_counter() - t0) / 5 * 1e6, 1)
+                row["cpu_kind"] = "reference" if ref is not None else "port"
+        out[name] = row
+        ops.check_status(dev)
+        del lg
+    return out
+
+
+def c2_block(dev, peaks, flush, with_cpu):
+    """Grouped expert GEMM of the contract: T=4096 tokens, top-2 of E=8, X [4096,1024] . W[e] [256,1024]^T, bf16.
+    `us_api` is kernels.grouped_gemm (histogram + row gather + tcgen05 GEMM + un-sort scatter, 5 launches);
+    `us_gemm` the GEMM launch alone on rows already sorted by expert."""
+    from tilelang_moe_b200 import kernels, ops
+    c = C2
+    g = torch.Generator().manual_seed(0)
+    X = torch.randn(c["T"], c["H"], generator=g).bfloat16()
+    W = (torch.randn(c["E"], c["I"], c["H"], generator=g) * 0.02).bfloat16()
+    idx = torch.argsort(torch.rand(c["T"], c["E"], generator=g), dim=1)[:, :c["k"]].contiguous()
+    Xd, Wd_, idxd = X.to(dev), W.to(dev), idx.to(dev)
+    api = lambda: kernels.grouped_gemm(Xd, Wd_, idxd)
+    _, offs, perm, _ = ops.route_histogram(idxd.to(torch.int32), c["E"], want_inv=False)
+    xs = ops.gather_rows(Xd, perm, div=c["k"])
+    Y = torch.empty(c["T"] * c["k"], c["I"], dtype=torch.bfloat16, device=dev)
+    gemm = lambda: ops.grouped_gemm_sorted(ops.GEMM_PLAIN, xs, Wd_, offs, out=Y)
+    for _ in range(3):
+        api(); gemm()
+    us_api, us_gemm = _event_us(api, 30, flush), _event_us(gemm, 30, flush)
+    flops = 2.0 * c["T"] * c["k"] * c["H"] * c["I"]
+    byts = (c["T"] * c["H"] + c["E"] * c["H"] * c["I"] + c["T"] * c["k"] * c["I"]) * 2
+    row = {"T": c["T"], "H": c["H"], "I": c["I"], "E": c["E"], "top_k": c["k"], "us_api": round(us_api, 2),
+           "us_gemm": round(us_gemm, 2), "us_gemm_in_graph": round(_graph_us(gemm), 2),
+           "TFLOPs_gemm": round(flops / us_gemm / 1e6, 1), "GBps_gemm": round(byts / us_gemm / 1e3, 1),
+           "frac_tensor_burst": round(flops / us_gemm / 1e6 / peaks["bf16_tflops"], 3),
+           "frac_tensor_sustained": round(flops / us_gemm / 1e6 / peaks["bf16_tflops_sustained"], 3),
+           "frac_hbm_measured": round(byts / us_gemm / 1e3 / peaks["hbm_gbs"], 3),
+           "note": "4.3 GFLOP and 16.8 MB: 2-3 us at either roof, so launch latency bounds it"}
+    if with_cpu:
+        ref = load_reference()
+        Xf, idf = X.repeat_interleave(c["k"], 0), idx.reshape(-1)
+        f_cpu = (lambda: ref["grouped_gemm_baseline"].grouped_gemm_loop(Xf, W, idf)) if ref is not None else \
+                (lambda: __import__("oracle.moe_oracle", fromlist=["x"]).grouped_gemm(X, W, idx, out_dtype=torch.bfloat16))
+        f_cpu()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            f_cpu()
+        row["cpu_us"] = round((time.perf_counter() - t0) / 3 * 1e6, 1)
+        row["cpu_kind"] = "reference" if ref is not None else "port"
+    ops.check_status(dev)
+    return row
+
+
+def c3_block(dev):
+    """FusedMoE small (T=1024, H=2048, I=512, 8 routed top-2 + 1 shared): the whole layer, eager and as one graph."""
+    from tilelang_moe_b200 import kernels, ops
+    cfg = WORKLOADS["c3"]
+    T, H, I, E, k, S = (cfg[n] for n in ("T", "H", "I", "E", "k", "S"))
+    xc, wc = kernels.generate_fusedmoe_inputs(1, T, H, I, E, S, k, dtype=torch.bfloat16, device="cpu", seed=42)
+    names = ["router_weight", "shared_gate", "shared_up", "shared_down", "routed_gate", "routed_up", "routed_down"]
+    wd = [wc[n].to(dev) for n in names]
+    x = xc.to(dev)
+    mod = kernels.FusedMoETileLang(H, I, E, S, k, 1, T, dtype=torch.bfloat16)
+    fwd = lambda: mod.forward(x, *wd)
+    for _ in range(3):
+        fwd()
+    us_eager = _event_us(fwd, 30)
+    replay = mod.capture(x, *wd)
+    for _ in range(3):
+        replay()
+    us_graph = _event_us(replay, 30)
+    ops.check_status(dev)
+    flops = 2.0 * T * H * E + (T * k + T * S) * 6.0 * H * I
+    return {"us_eager": round(us_eager, 2), "us_graph": round(us_graph, 2), "tokens_per_s_graph": round(T / us_graph * 1e6),
+            "TFLOPs_graph": round(flops / us_graph / 1e6, 1)}
+
+
+def parity_block(cfg, x_cpu, logits_cpu, tokens, got, weight_of):
+    """Sampled-token check against the CPU oracle: for the tokens given (rows of x_cpu / logits_cpu), routing by the
+    oracle's top-k, every selected expert's SiLU-gated FFN in fp32 on the bf16 inputs, weighted sum.  `got` holds the
+    GPU's output rows for those tokens, `weight_of(e)` returns expert e's bf16 weights on the host.  Tolerance of the
+    contract: 1e-2 relative + 2e-2 absolute."""
+    from oracle import moe_oracle as O
+    k = cfg["k"]
+    scores, idx = O.topk_softmax(logits_cpu[tokens], k, "A")
+    xs = x_cpu[tokens].float()
+    ref = torch.zeros(len(tokens), cfg["H"])
+    users = {}
+    for i in range(len(tokens)):
+        for s_ in range(k):
+            users.setdefault(int(idx[i, s_]), []).append((i, s_))
+    for e, lst in sorted(users.items()):
+        Wg, Wu, Wd = (w.float() for w in weight_of(e))
+        rows = torch.tensor([i for i, _ in lst])
+        w = torch.stack([scores[i, s_] for i, s_ in lst]).unsqueeze(1)
+        ref.index_add_(0, rows, O.expert_ffn(xs[rows], Wg, Wu, Wd) * w)
+    err = ((got.float() - ref).abs() / (1e-2 * ref.abs() + 2e-2)).max().item()
+    return {"checked_tokens": len(tokens), "experts_touched": len(users), "max_err_over_tol": round(err, 4), "ok": err <= 1.0}, idx
 
 
 # --------------------------------------------------------------------------------------- router arm
@@ -587,6 +863,21 @@ def run_router(args):
                       "n_gpus": 1, "dtype": "f32", "data": "synthetic", "config": {"workload": "router: c1, c4, sweeps"},
                       "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"], "best_frac_hbm": best,
                       "results": results, "router_gemm_topk": fused}), flush=True)
+
+
+def run_c2(args):
+    """The grouped-GEMM configuration alone (T=4096, H=1024, I=256, E=8, top-2)."""
+    from tilelang_moe_b200 import _lib
+    _lib.load()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    row = c2_block(dev, peaks, flush, not args.no_cpu)
+    print(json.dumps({"metric": "grouped_gemm_us", "unit": "us", "value": row["us_gemm"], "higher_is_better": False, "n_gpus": 1,
+                      "dtype": "bf16", "data": "synthetic", "config": {"workload": "c2: grouped expert GEMM, top-2 of 8 experts"},
+                      "peak_tflops_burst": peaks["bf16_tflops"], "peak_hbm_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                      **row}), flush=True)
 
 
 def run_gemm_grid(args):
@@ -725,8 +1016,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["router", "gemm_grid", "mhc"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["c2", "router", "gemm_grid", "mhc"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="c5: skip the router / c2 / c3 blocks of the line")
+    ap.add_argument("--no-parity", action="store_true", help="skip the sampled-token check against the CPU oracle")
     ap.add_argument("--exchange", default="peer_dedup", choices=["peer", "peer_dedup", "nccl"],
                     help="expert-parallel exchange: own kernels over peer memory, or NCCL all-to-all")
     ap.add_argument("--graph", action="store_true", help="c3: replay the layer as one CUDA graph")
@@ -741,11 +1034,13 @@ def main():
         return run_gemm_grid(args)
     if args.workload == "mhc":
         return run_mhc(args)
+    if args.workload == "c2":
+        return run_c2(args)
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":
-        run_reference_arm(args, cfg)
+        run_reference_arm(args, args.workload, cfg)
     else:
-        run_ours(args, cfg)
+        run_ours(args, args.workload, cfg)
 
 
 if __name__ == "__main__":

@@ -1,7 +1,11 @@
-"""Compile the C restatement of the routing oracle (test infrastructure) with gcc.
+"""Build the checker side (test infrastructure): the C restatement of the routing oracle, compiled with gcc, and -
+where the reference checkout is present - a copy of the reference's own CPU baseline files under ``oracle/_ref/``
+(git-ignored output, like the compiled library) so that the benchmark's reference arm can time the reference's
+unmodified Python on a machine where the checkout itself is absent.
 
-    python oracle/build.py        ->  oracle/libroute_oracle.so
+    python oracle/build.py        ->  oracle/libroute_oracle.so  [+ oracle/_ref/*_baseline.py]
 """
+import os
 import shutil
 import subprocess
 from pathlib import Path
@@ -21,5 +25,23 @@ def build(force: bool = False) -> Path:
     return LIB
 
 
+REF_DIR = HERE / "_ref"
+REF_FILES = ("topk_softmax_baseline.py", "grouped_gemm_baseline.py", "fusedmoe_baseline.py")
+
+
+def fetch_reference(reference_root=None):
+    """Copy the reference's PyTorch baseline files (they import nothing but torch) into ``oracle/_ref/``.
+    Returns the directory, or None where no reference checkout is reachable."""
+    root = Path(reference_root or os.environ.get("MOE_REFERENCE_DIR", "/root/reference"))
+    src = root / "kernels"
+    if not all((src / f).exists() for f in REF_FILES):
+        return None
+    REF_DIR.mkdir(exist_ok=True)
+    for f in REF_FILES:
+        shutil.copyfile(src / f, REF_DIR / f)
+    return REF_DIR
+
+
 if __name__ == "__main__":
     print(build(force=True))
+    print(fetch_reference())

@@ -337,8 +337,8 @@ __device__ __forceinline__ uint32_t pack_out(float a, float b, int f16) {
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
 
 // ------------------------------------------------------------------------------ kernel
-template <int MT, int BN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS_GATHER, 1)
+template <int MT, int BN, int EPI, bool GATHER>
+__global__ void __launch_bounds__(GATHER ? NUM_THREADS_GATHER : NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmB2, const Params p) {
   using C = Cfg<MT, BN>;
@@ -361,7 +361,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
   const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
   const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
-  const bool gather = MT == 1 && p.a_gather != nullptr;
+  constexpr bool gather = GATHER;   // its own instantiation: the copy loops cost every warp of the kernel registers
 
   // ---- set-up: barriers, TMEM, tile table
   if (threadIdx.x == 0) {
@@ -379,7 +379,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS_GATHER) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
   if (warp == 2) tile_prefix(tstart, offs, E, TILE_ROWS, lane);
   tc_fence_before();
@@ -868,8 +868,8 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, void* ybase, in
   }
 }
 
-template <int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS_GATHER, 1)
+template <int EPI, bool GATHER>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? NUM_THREADS_GATHER : NUM_THREADS, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
                          const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
                          const Params p) {
@@ -885,6 +885,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain, [2S+5..3S+5) gfull
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFFSET + 200);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
+  volatile uint32_t* tile_light = reinterpret_cast<volatile uint32_t*>(smem + C::BAR_OFFSET + 216);   // ring of 8
   int32_t* tstart = reinterpret_cast<int32_t*>(smem + C::TABLE_OFFSET);
   int32_t* offs = tstart + (MAX_E + 1);
 
@@ -898,7 +899,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const uint32_t lead_full0 = map_to_cta(full0, 0), lead_tempty0 = map_to_cta(tempty0, 0);
   const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-  const bool gather = p.a_gather != nullptr;
+  constexpr bool gather = GATHER;   // its own instantiation: the copy loops cost every warp of the kernel registers
 
   if (threadIdx.x == 0) {
     // full (used in CTA 0): the producer's arrive, + with a row gather one arrival per lane of CTA 0's two gather
@@ -921,7 +922,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
     tmem_relinquish_pair();
   }
-  for (int e = threadIdx.x; e <= E; e += NUM_THREADS_GATHER) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
   if (warp == 2) tile_prefix(tstart, offs, E, TILE_ROWS, lane);
   tc_fence_before();
@@ -936,6 +937,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int stage = 0;
     uint32_t phase = 0;
     uint32_t issued = 0;
+    uint32_t seq = 0;
     bool ok = true;
     for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
       const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
@@ -943,6 +945,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const int n0 = t.n_tile * OUT_COLS;
       const int a_row = t.row0 + (int)rank * (light ? BM / 2 : BM);
       const uint32_t tx = gather ? 2u * C::B_BYTES : (light ? 2u * (C::A_BYTES / 2 + C::B_BYTES) : 2u * C::STAGE_BYTES);
+      // read by the MMA issuer after the first full barrier of the tile; the producer runs at most STAGES (< 8) k-blocks,
+      // hence tiles, ahead of it
+      if (leader && lane == 0) tile_light[seq & 7] = light ? 1u : 0u;
+      ++seq;
       for (int kb = 0; kb < NKB; ++kb) {
         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
         if (lane == 0) {
@@ -984,16 +990,21 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      uint32_t seq = 0;                      // tiles this cluster has started
       bool ok = true;
       for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
-        const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
-        const uint32_t idesc = (t.row_end - t.row0 <= BM) ? idesc_l : idesc_h;
+        uint32_t idesc = idesc_h;
         if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < NKB; ++kb) {
-          if (!mbar_wait_cluster(full0 + 8 * stage, phase, abort_flag, p.status, 13)) { ok = false; break; }
+          // plain TMA arrivals need no more than the CTA-scope wait; the gather path of CTA 1 arrives across the cluster
+          if (!(gather ? mbar_wait_cluster(full0 + 8 * stage, phase, abort_flag, p.status, 13)
+                       : mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 13))) { ok = false; break; }
           tc_fence_after();
+          // the tile's shape comes from the producer (written before its first arrive on this barrier): a table look-up
+          // here would sit between two tiles' instruction streams with the tensor pipe idle
+          if (kb == 0) idesc = tile_light[seq & 7] ? idesc_l : idesc_h;
           if (lane == 0) {
             if (gather) fence_proxy_async();   // this CTA's A rows were written by cp.async, not by the TMA unit
             const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
@@ -1014,6 +1025,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           umma_commit_pair(map_to_cta(tfull0 + 8 * acc, 1));
         }
         __syncwarp();
+        ++seq;
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok) {
@@ -1252,29 +1264,43 @@ static int allow_dynamic_smem(Kernel kernel, int bytes, std::atomic<bool>* done_
   return MOE_OK;
 }
 
-template <int MT, int BN, int EPI>
-static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
-                  cudaStream_t st) {
+template <int MT, int BN, int EPI, bool GATHER>
+static int launch_g(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
+                    cudaStream_t st) {
   using C = Cfg<MT, BN>;
   constexpr int SMEM = EPI == EPI_PEER ? C::SMEM_BYTES_PEER : C::SMEM_BYTES;
   static std::atomic<bool> attr_set[64];
-  int rc = allow_dynamic_smem(grouped_gemm_kernel<MT, BN, EPI>, SMEM, attr_set);
+  int rc = allow_dynamic_smem(grouped_gemm_kernel<MT, BN, EPI, GATHER>, SMEM, attr_set);
   if (rc) return rc;
-  grouped_gemm_kernel<MT, BN, EPI><<<grid, NUM_THREADS_GATHER, SMEM, st>>>(tA, tB, tB2, p);
+  grouped_gemm_kernel<MT, BN, EPI, GATHER><<<grid, GATHER ? NUM_THREADS_GATHER : NUM_THREADS, SMEM, st>>>(tA, tB, tB2, p);
   MOE_CHECK_LAUNCH("grouped_gemm_kernel");
   return MOE_OK;
 }
+template <int MT, int BN, int EPI>
+static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const Params& p, int grid,
+                  cudaStream_t st) {
+  // the row gather is compiled for the matrix epilogues only (the fused router has none)
+  if (EPI != EPI_ROUTER && p.a_gather) return launch_g<MT, BN, EPI == EPI_ROUTER ? MOE_GEMM_PLAIN : EPI, true>(tA, tB, tB2, p, grid, st);
+  return launch_g<MT, BN, EPI, false>(tA, tB, tB2, p, grid, st);
+}
 
+template <int EPI, bool GATHER>
+static int launch_pair_g(const CUtensorMap& tA, const CUtensorMap& tA64, const CUtensorMap& tB, const CUtensorMap& tB2,
+                         const Params& p, int grid, cudaStream_t st) {
+  constexpr int SMEM = EPI == EPI_PEER ? PairCfg::SMEM_BYTES_PEER : PairCfg::SMEM_BYTES;
+  static std::atomic<bool> attr_set[64];
+  int rc = allow_dynamic_smem(grouped_gemm_pair_kernel<EPI, GATHER>, SMEM, attr_set);
+  if (rc) return rc;
+  // the two gather warps exist only in the instantiation that gathers
+  grouped_gemm_pair_kernel<EPI, GATHER><<<grid, GATHER ? NUM_THREADS_GATHER : NUM_THREADS, SMEM, st>>>(tA, tA64, tB, tB2, p);
+  MOE_CHECK_LAUNCH("grouped_gemm_pair_kernel");
+  return MOE_OK;
+}
 template <int EPI>
 static int launch_pair(const CUtensorMap& tA, const CUtensorMap& tA64, const CUtensorMap& tB, const CUtensorMap& tB2,
                        const Params& p, int grid, cudaStream_t st) {
-  constexpr int SMEM = EPI == EPI_PEER ? PairCfg::SMEM_BYTES_PEER : PairCfg::SMEM_BYTES;
-  static std::atomic<bool> attr_set[64];
-  int rc = allow_dynamic_smem(grouped_gemm_pair_kernel<EPI>, SMEM, attr_set);
-  if (rc) return rc;
-  grouped_gemm_pair_kernel<EPI><<<grid, NUM_THREADS_GATHER, SMEM, st>>>(tA, tA64, tB, tB2, p);
-  MOE_CHECK_LAUNCH("grouped_gemm_pair_kernel");
-  return MOE_OK;
+  if (p.a_gather) return launch_pair_g<EPI, true>(tA, tA64, tB, tB2, p, grid, st);
+  return launch_pair_g<EPI, false>(tA, tA64, tB, tB2, p, grid, st);
 }
 
 }  // namespace gemm
@@ -1461,7 +1487,9 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   int BN = 128;
   if (gate || (N % 256 == 0 && m_tiles_128 * n_tiles_256 >= dev.sm_count)) BN = 256;
   const bool pair_ok = (gate ? N % 64 == 0 : N % 256 == 0) && epilogue != MOE_GEMM_PLAIN_F32 && !(ga.idx && K % 64);
-  bool pair = pair_ok && (live_rows / BM) * n_tiles_256 >= 2 * (int64_t)dev.sm_count;
+  // measured on B200 under its power cap: the pair kernel gains 3-10 % where groups are uniformly large and loses
+  // where most experts own a single tile (their weight stream wants the deeper per-SM ring of the single-CTA kernel)
+  bool pair = pair_ok && live_rows / E >= 512 && (live_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
   if (const char* force = getenv("MOE_B200_GEMM_TILE_ROWS")) {
     if (force[0] == 'p') pair = pair_ok;
     else if (atoi(force) == 128) pair = false;

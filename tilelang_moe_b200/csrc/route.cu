@@ -163,7 +163,13 @@ gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ pe
     const int64_t srow = div > 1 ? f / div : f;
     const uint4* s = src + srow * vec_per_row;
     uint4* d = dst + p * vec_per_row;
-    for (int v = lane; v < vec_per_row; v += 32) d[v] = __ldg(s + v);
+    // four independent 16-byte loads in flight per lane before the first store
+    int v = lane;
+    for (; v + 96 < vec_per_row; v += 128) {
+      const uint4 a = __ldg(s + v), b = __ldg(s + v + 32), c = __ldg(s + v + 64), e = __ldg(s + v + 96);
+      d[v] = a; d[v + 32] = b; d[v + 64] = c; d[v + 96] = e;
+    }
+    for (; v < vec_per_row; v += 32) d[v] = __ldg(s + v);
     if (w_src && lane == 0) w_dst[p] = w_src[f];
   }
 }
@@ -464,7 +470,7 @@ extern "C" int moe_gather_rows(const void* src, const int32_t* perm, int div, in
   int rc = current_device_info(&dev);
   if (rc) return rc;
   int64_t blocks = ceil_div64(n_rows, 8);
-  const int64_t cap = (int64_t)dev.sm_count * 8;
+  const int64_t cap = (int64_t)dev.sm_count * 8;   // 64 warps per SM, each with four row pieces in flight
   if (blocks > cap) blocks = cap;
   gather_rows_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(src), perm, div, n_rows, (int)(cols / 8), reinterpret_cast<uint4*>(dst), w_src, w_dst);

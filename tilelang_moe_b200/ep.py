@@ -366,7 +366,7 @@ class EPRunner:
             self.forward(xd, lgd)
 
         from .pipeline import HostPipeline
-        pipe = HostPipeline(dev, [x_pin, lg_pin], (Tl, x_l.shape[1]), torch.bfloat16, compute)
+        pipe = HostPipeline(dev, [x_pin, lg_pin], (Tl, x_l.shape[1]), torch.bfloat16, compute, depth=3)   # uploads run two steps ahead
 
         def step_e2e(n=1):
             pipe.run(n)
