@@ -150,6 +150,7 @@ static int launch_warp(const float* logits, int64_t M, int N, int64_t ld, int k,
 // NaN into the canonical positive NaN, which ranks above +inf.
 // ------------------------------------------------------------------------------------
 constexpr int TILE_THREADS = 128;
+constexpr int MAX_PART_VECS = 32;   // 16-byte vectors one thread scans: at most 128 floats of a row per thread
 
 
 template <int K, int TPR>
@@ -157,22 +158,34 @@ __global__ void __launch_bounds__(TILE_THREADS)
 topk_tile_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld, int k, int mode, int rows_per_tile,
                  float* __restrict__ scores, int64_t* __restrict__ idx64, int32_t* __restrict__ idx32) {
   extern __shared__ __align__(16) float tile[];
+  __shared__ unsigned char queue[(2 * K - 1) * TILE_THREADS];   // per thread: vectors that can hold one of its K largest
   const int tid = threadIdx.x;
   const int pitch = N + 4;                         // floats; 16-byte aligned rows, conflict-free 16-byte reads
   const int vec_per_row = N >> 2;
   const int row_in_tile = tid / TPR, part = tid % TPR;
   const int part_vecs = (vec_per_row + TPR - 1) / TPR;
   const int64_t n_tiles = (M + rows_per_tile - 1) / rows_per_tile;
+  // staging walk of this thread: first vector, and the step of 128 vectors in rows / columns / bytes
+  const int ld_r0 = tid / vec_per_row, ld_c0 = tid % vec_per_row;
+  const int ld_dr = TILE_THREADS / vec_per_row, ld_dc = TILE_THREADS % vec_per_row;
+  const int64_t ld_dsrc = (int64_t)ld_dr * ld + ld_dc * 4;
+  const uint32_t ld_ddst = (uint32_t)(ld_dr * pitch + ld_dc * 4) * 4u;
+  const uint32_t tile_s = (uint32_t)__cvta_generic_to_shared(tile);
 
   for (int64_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
     const int64_t row0 = t * rows_per_tile;
     const int rows = (int)((M - row0) < rows_per_tile ? (M - row0) : rows_per_tile);
     __syncthreads();                               // previous tile fully consumed
-    for (int v = tid; v < rows * vec_per_row; v += TILE_THREADS) {
-      const int r = v / vec_per_row, c = v - r * vec_per_row;
-      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tile + r * pitch + c * 4);
+    {   // thread t copies vectors t, t + 128, ... of the tile; (row, column) advance by a fixed step, no division
+      int r = ld_r0, c = ld_c0;
       const float* src = logits + (row0 + r) * ld + c * 4;
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      uint32_t dst = tile_s + (uint32_t)(r * pitch + c * 4) * 4u;
+      while (r < rows) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        r += ld_dr; c += ld_dc;
+        src += ld_dsrc; dst += ld_ddst;
+        if (c >= vec_per_row) { c -= vec_per_row; r += 1; src += ld - N; dst += (uint32_t)(pitch - N) * 4u; }
+      }
     }
     asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     __syncthreads();
@@ -184,16 +197,72 @@ topk_tile_kernel(const float* __restrict__ logits, int64_t M, int N, int64_t ld,
     const float* rowp = tile + row_in_tile * pitch;
     const int v_lo = part * part_vecs, v_hi = min(vec_per_row, v_lo + part_vecs);
     if (active) {
-      for (int v = v_lo; v < v_hi; ++v) {
+      // Pass 1, branch-free: the largest key of every 4-element vector, and the K largest of those (keys only: a
+      // max / min pair per list entry).  The K largest elements of the part sit in vectors whose largest key is at
+      // least the K-th largest vector maximum V: at most K-1 vectors lie above V, and of those equal to V only the
+      // first K in column order can matter.
+      int vm[MAX_PART_VECS];
+      constexpr int CH = 2;                   // independent lists (two dependency chains in flight), one per half of the part
+      constexpr int QV = MAX_PART_VECS / CH;
+      int va[CH][K];
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int j = 0; j < K; ++j) va[c][j] = (int)0x80000000;
+#pragma unroll
+      for (int u = 0; u < QV; ++u) {
+        int m[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          m[c] = (int)0x80000000;
+          if (v_lo + u + c * QV < v_hi) {
+            const float4 x = *reinterpret_cast<const float4*>(rowp + (v_lo + u + c * QV) * 4);
+            m[c] = max(max(float_to_ikey(x.x), float_to_ikey(x.y)), max(float_to_ikey(x.z), float_to_ikey(x.w)));
+          }
+          vm[u + c * QV] = m[c];
+        }
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            const int hi = max(va[c][j], m[c]);
+            m[c] = min(va[c][j], m[c]);
+            va[c][j] = hi;
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 1; c < CH; ++c) {          // the K largest of all lists end up in va[0]
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+          int m = va[c][i];
+#pragma unroll
+          for (int j = 0; j < K; ++j) {
+            const int hi = max(va[0][j], m);
+            m = min(va[0][j], m);
+            va[0][j] = hi;
+          }
+        }
+      }
+      // Pass 2, predicated: queue the vectors that can hold a winner (this thread's slots in shared memory)
+      const int V = va[0][K - 1];
+      int cnt = 0, n_eq = 0;
+#pragma unroll
+      for (int u = 0; u < MAX_PART_VECS; ++u) {
+        const bool eq = vm[u] == V && n_eq < K && v_lo + u < v_hi;
+        const bool take = (vm[u] > V) || eq;
+        if (take) queue[cnt * TILE_THREADS + tid] = (unsigned char)u;
+        cnt += take ? 1 : 0;
+        n_eq += eq ? 1 : 0;
+      }
+      // Pass 3: the queued vectors (about K of them) go through the sorted list with their columns, largest element
+      // first, lowest column first among equal ones
+      for (int q = 0; q < cnt; ++q) {
+        const int v = v_lo + (int)queue[q * TILE_THREADS + tid];
         const float4 x = *reinterpret_cast<const float4*>(rowp + v * 4);
-        const int k0 = float_to_ikey(x.x), k1 = float_to_ikey(x.y), k2 = float_to_ikey(x.z), k3 = float_to_ikey(x.w);
-        // Only elements above the list's last entry can enter it.  They are taken largest first (lowest column
-        // first among equal ones, so equal values keep column order in the list): the lanes of a warp hold
-        // different rows, and the warp pays for as many insertions as the busiest lane needs - usually one -
-        // instead of four for every vector that has a candidate in any lane.
-        int c0 = k0, c1 = k1, c2 = k2, c3 = k3;
+        int c0 = float_to_ikey(x.x), c1 = float_to_ikey(x.y), c2 = float_to_ikey(x.z), c3 = float_to_ikey(x.w);
         int m = max(max(c0, c1), max(c2, c3));
-        while (m > kv[K - 1]) {
+        while (m >= V && m > kv[K - 1]) {     // nothing below V can be among the K largest: K vector maxima are >= V
           const int sel = c0 == m ? 0 : (c1 == m ? 1 : (c2 == m ? 2 : 3));
           list_insert<K>(kv, ki, m, v * 4 + sel);
           c0 = sel == 0 ? (int)0x80000000 : c0;
@@ -260,11 +329,8 @@ static int launch_tile(const float* logits, int64_t M, int N, int64_t ld, int k,
                        int64_t* idx64, int32_t* idx32, int sm_count, cudaStream_t st) {
   const int rows_per_tile = TILE_THREADS / TPR;
   const size_t smem = (size_t)rows_per_tile * (N + 4) * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (smem > 48 * 1024)   // per device, cheap: set on every such launch
     MOE_CUDA_CHECK(cudaFuncSetAttribute(topk_tile_kernel<K, TPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
-    attr_set = true;
-  }
   int64_t blocks = ceil_div64(M, rows_per_tile);
   const int64_t cap = (int64_t)sm_count * 3;
   if (blocks > cap) blocks = cap;
