@@ -82,7 +82,7 @@ struct Cfg {
   // layout: [stages][barriers 256 B][tile tables]
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TABLE_OFFSET = BAR_OFFSET + 256;
-  static constexpr int STAGING_OFFSET = (TABLE_OFFSET + 2 * (MAX_E + 1) * 4 + 127) & ~127;   // 16-byte accesses
+  static constexpr int STAGING_OFFSET = (TABLE_OFFSET + 3 * (MAX_E + 1) * 4 + 127) & ~127;   // 16-byte accesses
   static constexpr int SMEM_BYTES = STAGING_OFFSET + 1024;  // + alignment slack
   // peer epilogue: 4 warps x 32 rows x (128 B + 16 B pad) to turn per-thread rows into 128-byte row segments
   static constexpr int STAGING_PITCH = 144;
@@ -125,6 +125,8 @@ struct Params {
   // split-K (plain fp32 output only): the N-tile index counts K slices of num_k_blocks blocks each; slice s of
   // row r lands in columns [s*N, (s+1)*N) of Y and the caller adds the slices
   int ksplit = 0;
+  int l2_hints = 0;        // 128-row kernel: 0 none, 1 evict-first for weights read once, 2 + evict-last for shared weights
+  int mixed = 0;           // 128-row kernel: single-tile and multi-tile experts interleaved in the tile order
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -208,6 +210,24 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
       ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+// the same load with an L2 eviction-priority hint (a policy from make_policy_*)
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t make_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t make_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -216,6 +236,7 @@ __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+
 // the barrier receives one arrival once every cp.async this thread has issued so far has landed
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
@@ -283,7 +304,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int n, int f16 = 0) {
 
 // ------------------------------------------------------------------------------ tile schedule
 struct Tile {
-  int e, row0, row_end, n_tile;
+  int e, row0, row_end, n_tile, m_tiles;   // m_tiles: row tiles of the tile's expert
 };
 // tstart[e] = number of M tiles of experts < e.  Tile ids: expert-major, then N tile, then M tile.
 __device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const int32_t* offs, int E, int NT,
@@ -301,6 +322,7 @@ __device__ __forceinline__ Tile decode_tile(int id, const int32_t* tstart, const
   const int m_local = local - t.n_tile * mt;
   t.row0 = offs[lo] + m_local * tile_rows;
   t.row_end = offs[lo + 1];
+  t.m_tiles = mt;
   return t;
 }
 
@@ -320,6 +342,55 @@ __device__ __forceinline__ void tile_prefix(int32_t* tstart, const int32_t* offs
   int run = inc - sum;
   for (int e = e_lo; e < e_hi; ++e) { tstart[e] = run; run += (offs[e + 1] - offs[e] + tile_rows - 1) / tile_rows; }
   if (lane == 31) tstart[E] = inc;
+}
+
+// Mixed schedule of the 128-row kernel.  Experts with a single row tile ("light": their tiles stream the weights
+// from HBM and leave the tensor pipe waiting) and experts with several ("heavy": weights shared through L2, tensor
+// bound) form two tile sequences, each expert-major as above; position g of the launch takes the next tile of one
+// or the other in proportion to their lengths, so that at any time the SMs work on both kinds side by side and
+// neither HBM nor the tensor pipes sit idle through a run of one kind.
+//   hstart[e] = row tiles of the heavy experts before e, lstart[e] = light experts before e.
+__device__ __forceinline__ void mixed_prefix(int32_t* hstart, int32_t* lstart, const int32_t* offs, int E, int lane) {
+  const int per = (E + 31) / 32;
+  const int e_lo = lane * per, e_hi = min(E, e_lo + per);
+  int hs = 0, ls = 0;
+  for (int e = e_lo; e < e_hi; ++e) {
+    const int mt = (offs[e + 1] - offs[e] + BM - 1) / BM;
+    if (mt == 1) ++ls; else hs += mt;
+  }
+  int hi = hs, li = ls;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int a = __shfl_up_sync(0xFFFFFFFFu, hi, o), b = __shfl_up_sync(0xFFFFFFFFu, li, o);
+    if (lane >= o) { hi += a; li += b; }
+  }
+  int hr = hi - hs, lr = li - ls;
+  for (int e = e_lo; e < e_hi; ++e) {
+    const int mt = (offs[e + 1] - offs[e] + BM - 1) / BM;
+    hstart[e] = hr; lstart[e] = lr;
+    if (mt == 1) ++lr; else hr += mt;
+  }
+  if (lane == 31) { hstart[E] = hi; lstart[E] = li; }
+}
+__device__ __forceinline__ Tile decode_mixed(int g, const int32_t* hstart, const int32_t* lstart, const int32_t* offs,
+                                             int E, int NT) {
+  const unsigned long long th = (unsigned long long)hstart[E] * NT, tl = (unsigned long long)lstart[E] * NT;
+  const int hc = (int)(((unsigned long long)g * th) / (th + tl));              // heavy tiles before position g
+  const int hc1 = (int)(((unsigned long long)(g + 1) * th) / (th + tl));
+  if (hc1 > hc) return decode_tile(hc, hstart, offs, E, NT, BM);              // light experts own no tiles of this table
+  const int id = g - hc;                                                      // light tile number id
+  int lo = 0, hi = E - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (lstart[mid + 1] * NT > id) hi = mid; else lo = mid + 1;
+  }
+  Tile t;
+  t.e = lo;
+  t.n_tile = id - lstart[lo] * NT;
+  t.row0 = offs[lo];
+  t.row_end = offs[lo + 1];
+  t.m_tiles = 1;
+  return t;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -355,6 +426,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
   int32_t* tstart = reinterpret_cast<int32_t*>(smem + C::TABLE_OFFSET);
   int32_t* offs = tstart + (MAX_E + 1);
+  int32_t* lstart = offs + (MAX_E + 1);            // mixed schedule: tstart then counts the heavy experts' tiles only
+  const bool mixed = p.mixed != 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
@@ -381,12 +454,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
   for (int e = threadIdx.x; e <= E; e += blockDim.x) offs[e] = p.offsets ? p.offsets[e] : (e == 0 ? 0 : p.dense_rows);
   __syncthreads();
-  if (warp == 2) tile_prefix(tstart, offs, E, TILE_ROWS, lane);
+  if (warp == 2) { if (mixed) mixed_prefix(tstart, lstart, offs, E, lane); else tile_prefix(tstart, offs, E, TILE_ROWS, lane); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int total_tiles = tstart[E] * NT;
+  const int total_tiles = (tstart[E] + (mixed ? lstart[E] : 0)) * NT;
   MOE_TRACE(if (threadIdx.x == 0 && blockIdx.x < MOE_TRACE_MAX_CTAS) {
     g_trace_clk[blockIdx.x][0] = clock64(); g_trace_clk[blockIdx.x][1] = (long long)global_timer_ns(); })
 
@@ -396,10 +469,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t phase = 0;
     uint32_t issued = 0;
     bool ok = true;
+    const uint64_t pol_first = make_policy_evict_first(), pol_last = make_policy_evict_last();
+    uint64_t pol_normal;
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol_normal));
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      const Tile t = (mixed ? decode_mixed(tile, tstart, lstart, offs, E, NT) : decode_tile(tile, tstart, offs, E, NT, TILE_ROWS));
       const int n0 = p.ksplit ? 0 : t.n_tile * OUT_COLS;
       const int k0 = p.ksplit ? t.n_tile * NKB * BK : 0;        // first K element of this tile's slice
+      // weights of an expert with a single row tile are read exactly once: they should leave L2 first; weights that
+      // several row tiles share stay as long as L2 lets them
+      const uint64_t b_policy = p.l2_hints == 0 ? pol_normal : (t.m_tiles == 1 ? pol_first : (p.l2_hints == 2 ? pol_last : pol_normal));
       for (int kb = 0; kb < NKB; ++kb) {
         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
         if (lane == 0) {
@@ -409,10 +488,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           mbar_arrive_expect_tx(full, gather ? p.b_tx_bytes : C::A_BYTES + p.b_tx_bytes);
           if (!gather) tma_load_2d(sa, &tmA, full, k0 + kb * BK, t.row0);
           if (EPI == MOE_GEMM_SILU_GATE) {
-            tma_load_3d(sb, &tmB, full, kb * BK, n0, t.e);
-            tma_load_3d(sb + C::B_BYTES / 2, &tmB2, full, kb * BK, n0, t.e);
+            tma_load_3d_hint(sb, &tmB, full, kb * BK, n0, t.e, b_policy);
+            tma_load_3d_hint(sb + C::B_BYTES / 2, &tmB2, full, kb * BK, n0, t.e, b_policy);
           } else {
-            tma_load_3d(sb, &tmB, full, k0 + kb * BK, n0, t.e);
+            tma_load_3d_hint(sb, &tmB, full, k0 + kb * BK, n0, t.e, b_policy);
           }
         }
         __syncwarp();
@@ -435,7 +514,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      const Tile t = (mixed ? decode_mixed(tile, tstart, lstart, offs, E, NT) : decode_tile(tile, tstart, offs, E, NT, TILE_ROWS));
       const bool second_half = MT == 2 && (t.row_end - t.row0) > BM;   // rows beyond the first 128 exist
       if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
       tc_fence_after();
@@ -487,7 +566,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+        const Tile t = (mixed ? decode_mixed(tile, tstart, lstart, offs, E, NT) : decode_tile(tile, tstart, offs, E, NT, TILE_ROWS));
         // lane l reads the list entries of rows l and l + 32 of this warp's half.  Rows past the end of the
         // expert's group are filled with zeros (nothing is read for them): their products are never stored,
         // and zero operands keep the tensor cores' switching power down on the padding of ragged groups
@@ -531,7 +610,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
+      const Tile t = (mixed ? decode_mixed(tile, tstart, lstart, offs, E, NT) : decode_tile(tile, tstart, offs, E, NT, TILE_ROWS));
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
       tc_fence_after();
       MOE_TRACE(if (warp == 2 && lane == 0 && tile < MOE_TRACE_MAX_TILES) g_trace_tile[1][tile] = global_timer_ns();)
@@ -1508,6 +1587,12 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   p.w_by_dst = w_by_dst;
   p.dense_rows = (int)ga.dense_rows;
   p.a_gather = ga.idx; p.a_src = A; p.a_div = ga.div; p.a_src_rows = (int)ga.src_rows; p.a_rows = (int)max_rows;
+  // measured on the DeepSeek-V3-shaped layer: eviction hints on the weight loads 3 % of the step, the mixed tile order
+  // another 1-3 % of each GEMM; MOE_B200_L2_HINTS / MOE_B200_MIXED = 0 switch them off for such measurements
+  static const int env_hints = [] { const char* h = getenv("MOE_B200_L2_HINTS"); return h ? atoi(h) : 2; }();
+  static const int env_mixed = [] { const char* h = getenv("MOE_B200_MIXED"); return h ? atoi(h) : 1; }();
+  p.l2_hints = env_hints;
+  p.mixed = env_mixed && offsets != nullptr;
 
   CUtensorMap tA, tA64, tB, tB2;
   // with a row gather A is the un-permuted matrix (src_rows rows) and its tensor maps are never used by the kernel
