@@ -5,7 +5,7 @@
  * `kernels`); it has no FFI of its own.  Each entry point below names the
  * reference function (file:line inside the reference project) whose device work
  * it replaces.  A Python binding calls these through ctypes on the caller's
- * thread; see INTEGRATION.md for the stub.
+ * thread (tilelang_moe_b200/_lib.py is such a binding).
  *
  * Conventions
  *   - every pointer is a DEVICE pointer, borrowed for the duration of the call,
@@ -303,11 +303,30 @@ int moe_ep_dispatch_dedup(const void* x, const int32_t* perm, const int32_t* top
                           const int32_t* offsets, const int32_t* dst_base, const int32_t* urank,
                           const int32_t* u_base, int k, int E_local, int64_t n, int64_t Tl, int64_t H,
                           void* const* peer_recv, void* const* peer_gidx, int G, void* stream);
+/* Barrier between the G ranks over peer memory, with a time limit.  No counterpart in the reference.
+ *   peer_flags: host array of G device pointers; entry g addresses rank g's flag block, int32 [4][16] (channel, slot),
+ *     zero-filled once, writable by every rank (symmetric / peer-mapped memory).
+ *   epoch: the number of this barrier on `channel` (1, 2, 3, ... the same on every rank).  Each rank stores the epoch
+ *     into slot [my_rank] of every peer's block - after a system-scope fence, so the rows it wrote into peer buffers
+ *     before the call are visible first - and waits until all G slots of its own block have reached it.
+ *   A wait longer than timeout_us gives up: status = {2, 40 + channel, peer} and the kernel returns (never a hang);
+ *     kernels enqueued behind it then run on incomplete data, so the caller must check `status` before using results.
+ */
+int moe_ep_barrier(void* const* peer_flags, int G, int my_rank, int channel, int32_t epoch, int64_t timeout_us,
+                   int32_t* status, void* stream);
 int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                   const int32_t* row_rank, const int32_t* dst_rows,
                                   void* const* peer_base, int n_peers, int64_t ldy, int64_t max_rows,
                                   int64_t expected_rows, int K, int N, int E, int dtype,
                                   int32_t* status, void* stream);
+
+/* ---- self-test of the bounded waits ---------------------------------------------------------
+ * No counterpart in the reference.  Launches one warp that waits, through the GEMM kernels' own barrier-wait
+ * routine, on a barrier nobody arrives on, with a limit of limit_us microseconds (1 .. 1 000 000).  The wait runs
+ * out: status (device int32[MOE_STATUS_WORDS]) receives {2, 99, 0}, *outcome (device int32, may be NULL) 0, and
+ * the kernel returns.  Lets a test see the give-up path without a faulty GEMM; the stream stays usable.
+ */
+int moe_debug_wait_probe(int64_t limit_us, int32_t* status, int32_t* outcome, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,5 +1,6 @@
 """Expert parallelism on real GPUs (needs >= 2): each rank's slice of the sharded layer against the
-single-process fp32 oracle.  NVLS is switched off so that a failing rank cannot disturb its peers."""
+single-process fp32 oracle.  NVLS is switched off in NCCL and the symmetric buffers are kept off NVLink multicast
+objects, so that a failing rank cannot disturb its peers; workers that outlive a failure are terminated."""
 import os
 import socket
 
@@ -20,7 +21,8 @@ def _free_port():
 
 
 def _worker(rank, world, port, placement, q, exchange="nccl"):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     from oracle import moe_oracle as O
     from tilelang_moe_b200 import ep, inputs, ops
     dev = torch.device("cuda", rank)
@@ -79,9 +81,23 @@ def _run_world(world, placement, exchange):
     procs = [ctx.Process(target=_worker, args=(r, world, port, placement, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=240) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
+    res = []
+    try:
+        for _ in range(world):
+            res.append(q.get(timeout=240))
+            if res[-1][3] is not None:      # a rank raised: the others may be waiting for it (their barriers time out)
+                break
+        for p in procs:
+            p.join(timeout=60)
+    finally:                                # no worker, and no kernel of one, outlives the test
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    assert len(res) == world or any(r[3] is not None for r in res), "a rank never reported"
     for rank, ok, err, exc in res:
         assert exc is None, f"rank {rank}: {exc}"
         assert ok, f"rank {rank}: max abs error {err}"
@@ -154,3 +170,73 @@ def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedu
     if dedup:   # fewer rows travelled than routed entries, and never more than one per (token, rank)
         sent = int(cnt_all[:, E:].sum())
         assert sent <= T * min(k, G) and sent < T * k
+
+
+def test_barrier_gives_up_after_its_time_limit_and_reports_it(cuda, lib):
+    """The group barrier with a peer that never arrives: two flag blocks on one GPU stand for two ranks, nothing ever
+    writes "rank 1"'s slot.  The wait must run out (2 ms here), leave {2, 40 + channel, peer} in the status word and
+    return - the stream stays usable - and check_status must raise.  Nothing faults or spins for ever."""
+    from tilelang_moe_b200 import _lib, ops
+    flags = [torch.zeros(64, dtype=torch.int32, device=cuda) for _ in range(2)]
+    ptrs = ops._ptr_array([f.data_ptr() for f in flags])
+    ops.check_status(cuda)
+    ops.ep_barrier(ptrs, 0, 1, 7, cuda, timeout_us=2000)
+    torch.cuda.synchronize(cuda)
+    assert ops.status_buffer(cuda).tolist()[:3] == [2, 41, 1]
+    assert flags[1][16 + 0].item() == 7 and flags[0][16 + 0].item() == 7      # the arrival itself was published
+    with pytest.raises(_lib.MoeLibraryError):
+        ops.check_status(cuda)
+    ops.check_status(cuda)                                                      # the raise cleared the status word
+    # a barrier whose peers have all arrived (slots already at the epoch) passes at once and leaves no status
+    flags[0][32:34] = 3
+    ops.ep_barrier(ptrs, 0, 2, 3, cuda, timeout_us=2000)
+    torch.cuda.synchronize(cuda)
+    ops.check_status(cuda)
+    y = torch.ones(8, device=cuda) * 2                                          # later work on the stream runs normally
+    assert y.sum().item() == 16
+
+
+def test_dispatch_ignores_entries_with_an_expert_id_out_of_range(cuda, lib):
+    """One routed entry carries id -1: the histogram reports it (status 1) and leaves it out of the permutation; the
+    dispatch kernels must then stop at the live entries - nothing is read through the unwritten tail of the permutation
+    and no row beyond the live rows of any receive buffer changes (canary rows stay intact)."""
+    from tilelang_moe_b200 import _lib, ops
+    G, El, k, Tl, H = 2, 2, 2, 64, 128
+    E = G * El
+    g = torch.Generator().manual_seed(3)
+    idx = torch.argsort(torch.rand(Tl, E, generator=g), dim=1)[:, :k].contiguous().int()
+    idx[5, 1] = -1
+    idx32 = idx.to(cuda)
+    x = torch.randn(Tl, H, generator=g).bfloat16().to(cuda)
+    id_map = torch.arange(E, dtype=torch.int32, device=cuda)
+    ops.check_status(cuda)
+    counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map)
+    torch.cuda.synchronize(cuda)
+    assert ops.status_buffer(cuda).tolist()[0] == 1
+    with pytest.raises(_lib.MoeLibraryError):
+        ops.check_status(cuda)
+    n_live = int(offsets[E].item())
+    assert n_live == Tl * k - 1
+    cap = Tl * k * G
+    for dedup in (False, True):
+        canary = torch.full((cap, H), 123.0, dtype=torch.bfloat16, device=cuda)
+        recv = [canary.clone() for _ in range(G)]
+        gidx = [torch.full((cap,), -7, dtype=torch.int32, device=cuda) for _ in range(G)]
+        recv_ptrs = ops._ptr_array([t.data_ptr() for t in recv])
+        gidx_ptrs = ops._ptr_array([t.data_ptr() for t in gidx])
+        if dedup:
+            urank, ucount = ops.ep_unique(idx32, id_map, El, G)
+            cnt_all = torch.stack([torch.cat([counts, ucount]), torch.zeros(E + G, dtype=torch.int32, device=cuda)]).contiguous()
+            offs_local, dst_base, ret_rank, ret_row, u_base = ops.ep_plan_dedup(cnt_all, G, El, 0, cap)
+            ops.ep_dispatch_dedup(x, perm, idx32, id_map, offsets, dst_base, urank, u_base, k, El, recv_ptrs, gidx_ptrs)
+            sent = ucount.tolist()
+        else:
+            cnt_all = torch.stack([counts, torch.zeros(E, dtype=torch.int32, device=cuda)]).contiguous()
+            offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(cnt_all, G, El, 0, cap)
+            ops.ep_dispatch(x, perm, idx32, id_map, offsets, dst_base, k, El, recv_ptrs)
+            sent = [int(counts[d * El:(d + 1) * El].sum()) for d in range(G)]
+        torch.cuda.synchronize(cuda)
+        for d in range(G):
+            assert torch.equal(recv[d][sent[d]:], canary[sent[d]:]), f"rows past the {sent[d]} live ones of rank {d} changed"
+            assert not torch.equal(recv[d][:sent[d]], canary[:sent[d]])
+    ops.check_status(cuda)

@@ -226,3 +226,50 @@ def test_pair_kernel_gives_the_bits_of_the_single_cta_kernel(cuda, lib, monkeypa
     ops.check_status(cuda)
     assert torch.equal(out["128"][0], out["pair"][0])
     assert torch.equal(out["128"][1], out["pair"][1])
+
+
+def test_bounded_wait_runs_out_and_the_stream_stays_usable(cuda, lib):
+    """The GEMM kernels wait on their barriers with a time limit.  A one-warp kernel waits through the same routine on
+    a barrier nobody arrives on, with a 1 ms limit: it must return, leave {2, site, block} in the status word (which
+    check_status turns into an exception), and a GEMM launched afterwards on the same stream must still be right."""
+    from tilelang_moe_b200 import _lib
+    ops.check_status(cuda)
+    assert ops.debug_wait_probe(cuda, limit_us=1000) == 0
+    assert ops.status_buffer(cuda).tolist()[:3] == [2, 99, 0]
+    with pytest.raises(_lib.MoeLibraryError, match="device status"):
+        ops.check_status(cuda)
+    g = torch.Generator().manual_seed(5)
+    X = torch.randn(300, 128, generator=g).bfloat16()
+    W = (torch.randn(3, 64, 128, generator=g) * 0.05).bfloat16()
+    idx = torch.randint(0, 3, (300,), generator=g)
+    _close(kernels.grouped_gemm(X.to(cuda), W.to(cuda), idx.to(cuda)), O.grouped_gemm(X, W, idx))
+    ops.check_status(cuda)
+
+
+def test_outputs_stay_inside_their_rows(cuda, lib, monkeypatch):
+    """Canary rows before and after every output buffer of the ragged up / down GEMMs and of the permutation: a store
+    one row outside a buffer would go unseen in a freshly allocated tensor, here it changes a canary."""
+    for mode in ("128", "pair"):
+        monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", mode)
+        g = torch.Generator().manual_seed(31)
+        sizes = [0, 1, 127, 129, 255, 257, 384, 0, 65]
+        E, H, I, pad = len(sizes), 256, 256, 64
+        idx = torch.cat([torch.full((n,), e, dtype=torch.int64) for e, n in enumerate(sizes)])
+        idx = idx[torch.randperm(idx.numel(), generator=g)].to(cuda)
+        T = idx.numel()
+        x = torch.randn(T, H, generator=g).bfloat16().to(cuda)
+        Wg = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16().to(cuda)
+        Wu = (torch.randn(E, I, H, generator=g) * 0.06).bfloat16().to(cuda)
+        Wd = (torch.randn(E, H, I, generator=g) * 0.06).bfloat16().to(cuda)
+        counts, offsets, perm, _ = ops.route_histogram(idx.int(), E, want_inv=False)
+        assert sorted(perm.tolist()) == list(range(T))
+        act_buf = torch.full((T + 2 * pad, I), 77.0, dtype=torch.bfloat16, device=cuda)
+        yk_buf = torch.full((T + 2 * pad, H), 77.0, dtype=torch.bfloat16, device=cuda)
+        act, yk = act_buf[pad:pad + T], yk_buf[pad:pad + T]
+        ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, x, Wg, offsets, B2=Wu, out=act, gather=perm, gather_div=1)
+        ops.grouped_gemm_sorted(ops.GEMM_SCALE_SCATTER_DSTW, act, Wd, offsets, dst_rows=perm,
+                                row_w=torch.ones(T, device=cuda), out=yk)
+        ops.check_status(cuda)
+        for buf in (act_buf, yk_buf):
+            assert (buf[:pad] == 77.0).all() and (buf[pad + T:] == 77.0).all(), f"a store left its buffer ({mode})"
+        assert not (act == 77.0).all(dim=1).any() and not (yk == 77.0).all(dim=1).any()   # every row was written

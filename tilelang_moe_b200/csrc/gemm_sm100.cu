@@ -1653,6 +1653,35 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
 #undef MOE_GEMM_CASE
 }
 
+// Exercises the bounded barrier wait of the GEMM kernels on purpose: one warp waits, with the given limit, on an
+// mbarrier that nothing ever arrives on.  The wait runs out, records {ST_WAIT_TIMEOUT, 99, block} in status and the
+// kernel returns normally - the same path a GEMM takes when a copy it waits for never lands.  Nothing faults or hangs.
+namespace moe {
+namespace gemm {
+__global__ void __launch_bounds__(32) wait_probe_kernel(unsigned long long limit_ns, int32_t* status, int32_t* outcome) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 99, limit_ns);
+  if (threadIdx.x == 0 && outcome) *outcome = ok ? 1 : 0;
+}
+}  // namespace gemm
+}  // namespace moe
+
+extern "C" int moe_debug_wait_probe(int64_t limit_us, int32_t* status, int32_t* outcome, void* stream) {
+  using namespace moe;
+  if (limit_us < 1 || limit_us > 1000000) return fail(MOE_ERR_ARG, "wait_probe: limit_us=%lld outside [1, 1000000]", (long long)limit_us);
+  if (!status) return fail(MOE_ERR_ARG, "wait_probe: null status");
+  gemm::wait_probe_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>((unsigned long long)limit_us * 1000ull, status, outcome);
+  MOE_CHECK_LAUNCH("wait_probe_kernel");
+  return MOE_OK;
+}
+
 #ifdef MOE_GEMM_TRACE
 // tile_ns: 3 x MOE_TRACE_MAX_TILES uint64, tile_cta: MOE_TRACE_MAX_TILES int32, cta_clk: MOE_TRACE_MAX_CTAS x 4 int64
 // (host buffers); the stamps of the most recent launch of the 128-row kernel on the current device.

@@ -768,10 +768,12 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ perm, const int32_t* __restrict__ topk_idx,
                    const int32_t* __restrict__ id_map, const int32_t* __restrict__ offsets,
                    const int32_t* __restrict__ dst_base, int k, int El, int slot_lo, int slot_hi, int64_t n,
-                   int vec_per_row, PeerPtrs peers) {
+                   int vec_per_row, int E_all, PeerPtrs peers) {
   const int lane = threadIdx.x & 31;
   const int64_t nwarps = (int64_t)gridDim.x * 8;
-  for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < n; p += nwarps) {
+  // entries whose expert id was out of range were left out of the permutation: only offsets[E_all] of the n are live
+  const int64_t n_live = min(n, (int64_t)offsets[E_all]);
+  for (int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); p < n_live; p += nwarps) {
     const int32_t f = perm[p];
     const int v = id_map[topk_idx[f]];
     const int dest = v / El;
@@ -806,7 +808,10 @@ ep_unique_kernel(const int32_t* __restrict__ topk_idx, const int32_t* __restrict
     const int t = base + tid;
     unsigned mask = 0;
     if (t < Tl)
-      for (int s = 0; s < k; ++s) mask |= 1u << (id_map[topk_idx[t * k + s]] / El);
+      for (int s = 0; s < k; ++s) {
+        const int32_t id = topk_idx[t * k + s];
+        if ((uint32_t)id < (uint32_t)(G * El)) mask |= 1u << (id_map[id] / El);   // ids out of range travel nowhere
+      }
     int32_t in_warp[16];
 #pragma unroll
     for (int d = 0; d < 16; ++d) {
@@ -854,7 +859,8 @@ ep_dispatch_dedup_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
                          int64_t n, int64_t Tl, int vec_per_row, PeerPtrs recv, PeerPtrs gidx) {
   const int lane = threadIdx.x & 31;
   const int64_t nwarps = (int64_t)gridDim.x * 8;
-  const int64_t pairs = Tl * G, groups = (n + 31) / 32;
+  const int64_t n_live = min(n, (int64_t)offsets[G * El]);   // entries with an expert id out of range are not in perm
+  const int64_t pairs = Tl * G, groups = (n_live + 31) / 32;
   for (int64_t item = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); item < pairs + groups; item += nwarps) {
     if (item < pairs) {
       const int32_t u = urank[item];
@@ -871,7 +877,7 @@ ep_dispatch_dedup_kernel(const uint4* __restrict__ x, const int32_t* __restrict_
       for (; i < vec_per_row; i += 32) dst[i] = __ldg(s + i);
     } else {
       const int64_t p = (item - pairs) * 32 + lane;
-      if (p < n) {
+      if (p < n_live) {
         const int32_t f = perm[p];
         const int v = id_map[topk_idx[f]];
         const int d = v / El;
@@ -970,8 +976,62 @@ extern "C" int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t
   if (blocks > cap) blocks = cap;
   ep_dispatch_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(x), perm, topk_idx, id_map, offsets, dst_base, k, E_local, slot_lo, slot_hi, n,
-      (int)(H / 8), pp);
+      (int)(H / 8), G * E_local, pp);
   MOE_CHECK_LAUNCH("ep_dispatch_kernel");
+  return MOE_OK;
+}
+
+// ====================================================================================
+// Barrier between the ranks of an expert-parallel group over peer memory, with a time limit.
+//
+// Every rank owns a row of G 32-bit flags per channel in memory its peers can write.  Arriving = storing this
+// barrier's epoch into slot [my rank] of every peer's row (after a system-scope fence, so that the rows this rank
+// stored into peer buffers before the barrier are visible first); waiting = polling the own row until every slot has
+// reached the epoch.  One thread per peer.  A wait that outlasts the limit writes status = {ST_WAIT_TIMEOUT,
+// 40 + channel, peer} and returns: the kernels behind it run on stale data, the host sees the status word, and no
+// GPU spins for ever because a peer died.
+// ====================================================================================
+namespace moe {
+__global__ void __launch_bounds__(32)
+ep_barrier_kernel(PeerPtrs flags, int G, int me, int channel, int32_t epoch, unsigned long long limit_ns,
+                  int32_t* __restrict__ status) {
+  const int j = threadIdx.x;
+  if (j >= G) return;
+  __threadfence_system();
+  volatile int32_t* theirs = reinterpret_cast<volatile int32_t*>(flags.p[j]) + channel * 16 + me;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+  const int32_t* mine = reinterpret_cast<const int32_t*>(flags.p[me]) + channel * 16 + j;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v - epoch >= 0) break;                       // epochs only grow (wrap-safe comparison)
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > limit_ns) {
+      if (status && atomicCAS(&status[0], 0, ST_WAIT_TIMEOUT) == 0) { status[1] = 40 + channel; status[2] = j; }
+      break;
+    }
+    __nanosleep(64);
+  }
+  __threadfence_system();
+}
+}  // namespace moe
+
+extern "C" int moe_ep_barrier(void* const* peer_flags, int G, int my_rank, int channel, int32_t epoch,
+                              int64_t timeout_us, int32_t* status, void* stream) {
+  using namespace moe;
+  if (!peer_flags) return fail(MOE_ERR_ARG, "ep_barrier: null pointer");
+  if (G < 1 || G > 16 || my_rank < 0 || my_rank >= G || channel < 0 || channel >= 4 || timeout_us < 1)
+    return fail(MOE_ERR_ARG, "ep_barrier: bad G=%d rank=%d channel=%d timeout_us=%lld", G, my_rank, channel, (long long)timeout_us);
+  PeerPtrs pf;
+  for (int g = 0; g < 16; ++g) pf.p[g] = g < G ? peer_flags[g] : nullptr;
+  for (int g = 0; g < G; ++g)
+    if (!pf.p[g] || (reinterpret_cast<uintptr_t>(pf.p[g]) & 3)) return fail(MOE_ERR_ARG, "ep_barrier: flag row %d null or unaligned", g);
+  ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pf, G, my_rank, channel, epoch,
+                                                                          (unsigned long long)timeout_us * 1000ull, status);
+  MOE_CHECK_LAUNCH("ep_barrier_kernel");
   return MOE_OK;
 }
 

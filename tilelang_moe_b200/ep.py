@@ -17,11 +17,16 @@ their inverses - can be exercised on CPU ranks over gloo with stand-in ops.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
-import torch
-import torch.distributed as dist
+# The exchange buffers are only ever written with plain peer stores: keep torch's symmetric memory from binding them
+# to an NVLink multicast object (a rank that dies while its memory is bound to one can fault its peers' GPUs).
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
 
 
 # --------------------------------------------------------------------------- placement
@@ -161,6 +166,18 @@ class PeerExchange:
         self.h_ret = symm_mem.rendezvous(self.ret, group)
         self.recv_ptrs = ops._ptr_array(list(self.h_recv.buffer_ptrs))
         self.ret_ptrs = ops._ptr_array(list(self.h_ret.buffer_ptrs))
+        # phase barriers: this library's own flag barrier over peer memory, with a time limit (a peer that has died or
+        # raised makes the wait run out and leave a status code instead of spinning for ever)
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=device)     # [4 channels][16 slots]
+        self.flags.zero_()
+        self.h_flags = symm_mem.rendezvous(self.flags, group)
+        self.flag_ptrs = ops._ptr_array(list(self.h_flags.buffer_ptrs))
+        self.rank = dist.get_rank(group)
+        self.device = device
+        self.epoch = [0, 0, 0, 0]
+        self.barrier_timeout_us = int(os.environ.get("MOE_B200_EP_BARRIER_TIMEOUT_US", "2000000"))
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                                                   # every rank's flags are zero before use
         self.cnt_all = torch.empty(world, 0, dtype=torch.int32, device=device)
         self.plan_bufs = {}
         self.side = torch.cuda.Stream(device=device)
@@ -176,13 +193,19 @@ class PeerExchange:
             self.uniq_bufs = {}
 
 
+def _barrier(px: "PeerExchange", ops, channel: int) -> None:
+    """Enqueue barrier number epoch[channel] + 1 of `channel` on the current stream."""
+    px.epoch[channel] += 1
+    ops.ep_barrier(px.flag_ptrs, px.rank, channel, px.epoch[channel], px.device, px.barrier_timeout_us)
+
+
 def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: EPPlan, id_map_dev: torch.Tensor,
                     Wg: torch.Tensor, Wu: torch.Tensor, Wd: torch.Tensor, ops, px: PeerExchange, group=None,
                     bufs: Optional[dict] = None, timers: Optional[dict] = None, stage=None) -> torch.Tensor:
     """Expert-parallel forward with the exchange done by this library's own kernels over peer memory:
     the dispatch is a gather kernel that stores rows straight into the destination's expert-major
     buffer, the combine exchange is the down GEMM's epilogue storing into the owner's return buffer.
-    One small all-gather of histograms and two barriers per layer; no host synchronisation."""
+    One small all-gather of histograms and two time-limited barriers per layer; no host synchronisation."""
     G, El, E = plan.world, plan.e_local, plan.n_experts
     Tl, H = x_local.shape
     rank = dist.get_rank(group)
@@ -212,7 +235,7 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
             ops.ep_dispatch_dedup(x_local, perm, idx32, id_map_dev, offsets, dst_base, urank, u_base, k, El,
                                   px.recv_ptrs, px.gidx_ptrs)
         with st("dispatch_barrier"):
-            px.h_recv.barrier(channel=0)
+            _barrier(px, ops, 0)
         with st("up_gemm"):   # expert-major row q is received row gidx[q]
             ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg, offs_local, B2=Wu, out=act, gather=px.gidx,
                                     gather_div=1, expected_rows=Tl * k)
@@ -222,7 +245,7 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
         with st("dispatch"):
             ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs)
         with st("dispatch_barrier"):
-            px.h_recv.barrier(channel=0)
+            _barrier(px, ops, 0)
         with st("up_gemm"):
             ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, px.recv, Wg, offs_local, B2=Wu, out=act, expected_rows=Tl * k)
         with st("down_gemm"):
@@ -235,13 +258,13 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
         with st("dispatch"):
             ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs, 0, split)
         with st("dispatch_barrier"):
-            px.h_recv.barrier(channel=0)
+            _barrier(px, ops, 0)
             fork = torch.cuda.Event()
             fork.record(cur)
         with torch.cuda.stream(px.side):
             px.side.wait_event(fork)   # after the first group has landed everywhere: the links are free again
             ops.ep_dispatch(x_local, perm, idx32, id_map_dev, offsets, dst_base, k, El, px.recv_ptrs, split, El)
-            px.h_recv.barrier(channel=2)
+            _barrier(px, ops, 2)
             second_ready = torch.cuda.Event()
             second_ready.record(px.side)
         half = Tl * k // 2
@@ -260,7 +283,7 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
             ops.grouped_gemm_peer_scatter(act, Wd[split:], offs_local[split:], ret_rank, ret_row, px.ret_ptrs, H,
                                           expected_rows=half)
     with st("combine_barrier"):
-        px.h_ret.barrier(channel=1)
+        _barrier(px, ops, 1)
     with st("combine"):
         out = ops.combine(px.ret, k, row_of=inv, scale=scores.reshape(-1), T=Tl, out=bufs.get("out"))
     return out

@@ -522,6 +522,24 @@ def ep_dispatch_dedup(x: torch.Tensor, perm: torch.Tensor, idx32: torch.Tensor, 
     _lib.check(rc, "moe_ep_dispatch_dedup")
 
 
+def ep_barrier(peer_flag_ptrs, rank: int, channel: int, epoch: int, device: torch.device,
+               timeout_us: int = 1_000_000) -> None:
+    """Enqueue the time-limited barrier of the expert-parallel group on the current stream (see the header)."""
+    with torch.cuda.device(device):
+        rc = _lib.load().moe_ep_barrier(peer_flag_ptrs, len(peer_flag_ptrs), rank, channel, epoch, timeout_us,
+                                        _ptr(status_buffer(device)), _stream())
+    _lib.check(rc, "moe_ep_barrier")
+
+
+def debug_wait_probe(device: torch.device, limit_us: int = 1000) -> int:
+    """Run the bounded-wait self-test kernel; returns 1 if the wait succeeded (it cannot), 0 if it ran out."""
+    outcome = torch.full((1,), -1, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        rc = _lib.load().moe_debug_wait_probe(limit_us, _ptr(status_buffer(device)), _ptr(outcome), _stream())
+    _lib.check(rc, "moe_debug_wait_probe")
+    return int(outcome.item())
+
+
 def grouped_gemm_peer_scatter(A: torch.Tensor, B: torch.Tensor, offsets: torch.Tensor, row_rank: torch.Tensor,
                               dst_rows: torch.Tensor, peer_ptrs, ldy: int, max_rows: Optional[int] = None,
                               expected_rows: int = 0) -> None:
