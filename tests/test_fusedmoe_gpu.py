@@ -138,6 +138,13 @@ def test_single_call_layer_equals_the_staged_calls(cuda, lib, B, S, H, I, E, NS,
     y0 = layer.moe_forward(xd, *wd, k).clone()
     ops.check_status(cuda)
     assert y1.shape == x.shape and torch.equal(y1, y0)
+    # a single shared expert of the routed width ran as expert E of the routed GEMMs (stacked weights kept by the layer
+    # object); the same layer with the stacking switched off takes the side-stream form: all three agree bit for bit
+    assert (getattr(m, "_stack", None) is not None) == (NS == 1 and H % 64 == 0)
+    if NS == 1:
+        m2 = kernels.FusedMoETileLang(H, I, E, NS, k, B, S, dtype=dtype)
+        m2.STACK_LIMIT_BYTES = 0
+        assert torch.equal(m2.forward(xd, *wd), y0) and getattr(m2, "_stack", None) is None
     lg = ops.router_logits(xd.view(-1, H), wd[0])
     y1l = m.forward(xd, *wd, logits=lg).clone()
     y0l = layer.moe_forward(xd, *wd, k, logits=lg).clone()

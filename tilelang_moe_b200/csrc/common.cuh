@@ -104,6 +104,17 @@ int gemm_splitk_f32(const void* A, const void* B, int64_t T, int K, int N, int S
 int dense_gemm(int epilogue, const void* A, const void* B, const void* B2, int64_t rows, int K, int N, void* Y,
                int64_t ldy, int dtype, int32_t* status, void* stream);
 
+// moe_route_histogram over a virtual id list: every kx stored ids are followed by one entry of expert E - 1 (route.cu)
+int route_histogram_ex(const void* topk_idx, int idx_is_int64, int64_t n, int E, const int32_t* id_map, int32_t* counts,
+                       int32_t* offsets, int32_t* perm, int32_t* inv, void* ws, size_t ws_bytes, int32_t* status,
+                       void* stream, int kx);
+
+// moe_grouped_gemm(MOE_GEMM_SCALE_SCATTER_DSTW) whose destination rows come in runs of w_slots + 1 per token: the
+// first w_slots of a run read row_w[token * w_slots + slot], the last one (the shared expert's row) weighs 1 (gemm_sm100.cu)
+int grouped_gemm_scatter_slots(const void* A, const void* B, const int32_t* offsets, const int32_t* dst_rows,
+                               const float* row_w, int w_slots, void* Y, int64_t ldy, int64_t max_rows, int K, int N, int E,
+                               int dtype, int32_t* status, void* stream);
+
 // K slices of the few-token router GEMM (route.cu): 1..16 from the token count and the hidden size alone
 int router_splits(int64_t T, int H);
 

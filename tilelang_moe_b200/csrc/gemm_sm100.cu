@@ -113,6 +113,7 @@ struct Params {
   int a_src_rows = 0;
   int a_rows = 0;          // entries of a_gather
   int w_by_dst = 0;        // SCALE_SCATTER: row_w is indexed by the destination row instead of the sorted row
+  int w_slots = 0;         // > 0: destination rows come in runs of w_slots + 1 per token, row_w has w_slots entries per token
   // fused router (EPI_ROUTER): the N = n_experts accumulator columns of a row are its logits
   int dense_rows = 0;      // offsets == nullptr: one group of this many rows
   float* r_scores = nullptr;     // fp32 [rows, r_k]
@@ -625,7 +626,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       void* ybase = p.Y;
       if (row_ok) {
         if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
-        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[p.w_by_dst ? out_row : (int64_t)grow];
+        if (EPI == MOE_GEMM_SCALE_SCATTER) {
+          if (p.w_slots > 0) {   // destination rows in runs of w_slots + 1 per token; the run's last row weighs 1
+            const int64_t tok = out_row / (p.w_slots + 1);
+            const int sl = (int)(out_row - tok * (p.w_slots + 1));
+            w = sl < p.w_slots ? p.row_w[tok * p.w_slots + sl] : 1.0f;
+          } else {
+            w = p.row_w[p.w_by_dst ? out_row : (int64_t)grow];
+          }
+        }
         if (EPI == EPI_PEER) ybase = p.peer_base[p.row_rank[grow]];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * MT * BN + half * BN);
@@ -1205,7 +1214,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       void* ybase = p.Y;
       if (row_ok) {
         if (!GATE && p.dst_rows) out_row = p.dst_rows[grow];
-        if (EPI == MOE_GEMM_SCALE_SCATTER) w = p.row_w[p.w_by_dst ? out_row : (int64_t)grow];
+        if (EPI == MOE_GEMM_SCALE_SCATTER) {
+          if (p.w_slots > 0) {   // destination rows in runs of w_slots + 1 per token; the run's last row weighs 1
+            const int64_t tok = out_row / (p.w_slots + 1);
+            const int sl = (int)(out_row - tok * (p.w_slots + 1));
+            w = sl < p.w_slots ? p.row_w[tok * p.w_slots + sl] : 1.0f;
+          } else {
+            w = p.row_w[p.w_by_dst ? out_row : (int64_t)grow];
+          }
+        }
         if (EPI == EPI_PEER) ybase = p.peer_base[p.row_rank[grow]];
       }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
@@ -1390,6 +1407,7 @@ struct GatherArgs {           // A rows fetched through an index list instead of
   int div = 1;
   int64_t src_rows = 0;
   int64_t dense_rows = 0;     // > 0 with offsets == nullptr: one group of this many rows (E must be 1)
+  int w_slots = 0;            // see Params::w_slots
 };
 
 static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const void* B2, const int32_t* offsets,
@@ -1462,6 +1480,15 @@ int moe::router_topk_gemm(const void* x, const void* Wr, int64_t T, int H, int E
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (BN == 256) return launch<1, 256, EPI_ROUTER>(tA, tB, tB, p, grid, st);
   return launch<1, 128, EPI_ROUTER>(tA, tB, tB, p, grid, st);
+}
+
+int moe::grouped_gemm_scatter_slots(const void* A, const void* B, const int32_t* offsets, const int32_t* dst_rows,
+                                    const float* row_w, int w_slots, void* Y, int64_t ldy, int64_t max_rows, int K, int N,
+                                    int E, int dtype, int32_t* status, void* stream) {
+  GatherArgs ga;
+  ga.w_slots = w_slots;
+  return grouped_gemm_impl(MOE_GEMM_SCALE_SCATTER_DSTW, A, B, nullptr, offsets, dst_rows, row_w, Y, ldy, max_rows, K, N, E,
+                           status, stream, nullptr, nullptr, 0, 0, dtype, ga);
 }
 
 // One dense group: Y[rows, N] = epilogue(A[rows, K] . B[N, K]^T) without a device-side offsets table (declared in
@@ -1585,6 +1612,7 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   p.row_rank = row_rank;
   for (int g = 0; g < 16; ++g) p.peer_base[g] = (peer_base && g < n_peers) ? peer_base[g] : nullptr;
   p.w_by_dst = w_by_dst;
+  p.w_slots = ga.w_slots;
   p.dense_rows = (int)ga.dense_rows;
   p.a_gather = ga.idx; p.a_src = A; p.a_div = ga.div; p.a_src_rows = (int)ga.src_rows; p.a_rows = (int)max_rows;
   // measured on the DeepSeek-V3-shaped layer: eviction hints on the weight loads 3 % of the step, the mixed tile order

@@ -24,7 +24,16 @@ constexpr int RWPB = 8;            // warps per CTA in the count / scatter kerne
 
 // Expert id of flat entry i; with an id_map (int32 [E]) the id is translated, e.g. to the
 // destination-major numbering used by expert parallelism.  Out-of-range ids come back as -1.
-__device__ __forceinline__ int load_id(const void* ids, int is64, int64_t i, const int32_t* id_map, int E) {
+// With kx > 0 the list is virtual: every run of kx stored ids (one token's routed experts) is followed by one entry
+// that is not stored anywhere and names expert E - 1, the shared expert riding along as one more group.
+__device__ __forceinline__ int load_id(const void* ids, int is64, int64_t i, const int32_t* id_map, int E, int kx = 0) {
+  if (kx > 0) {
+    const int64_t t = i / (kx + 1);
+    const int sl = (int)(i - t * (kx + 1));
+    if (sl == kx) return E - 1;
+    i = t * kx + sl;
+    E -= 1;                          // stored ids name the routed experts only
+  }
   int e;
   if (is64) {
     const long long v = reinterpret_cast<const long long*>(ids)[i];
@@ -39,7 +48,7 @@ __device__ __forceinline__ int load_id(const void* ids, int is64, int64_t i, con
 template <int UNIT>
 __global__ void __launch_bounds__(RWPB * 32)
 route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ id_map,
-                   int32_t* __restrict__ unit_counts, int32_t* __restrict__ status) {
+                   int32_t* __restrict__ unit_counts, int32_t* __restrict__ status, int kx) {
   extern __shared__ int32_t sh[];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   int32_t* wh = sh + (size_t)w * E;
@@ -51,7 +60,7 @@ route_count_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, con
 #pragma unroll
   for (int sidx = 0; sidx < UNIT / 32; ++sidx) {
     const int64_t i = first + sidx * 32 + lane;
-    ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E) : -2;
+    ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E, kx) : -2;
   }
   for (int e = lane; e < E; e += 32) wh[e] = 0;
   __syncwarp();
@@ -112,7 +121,7 @@ route_scan_kernel(int32_t* __restrict__ unit_counts, int64_t n_units, int E, int
 template <int UNIT>
 __global__ void __launch_bounds__(RWPB * 32)
 route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, const int32_t* __restrict__ id_map,
-                     const int32_t* __restrict__ unit_base, int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+                     const int32_t* __restrict__ unit_base, int32_t* __restrict__ perm, int32_t* __restrict__ inv, int kx) {
   extern __shared__ int32_t sh[];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const unsigned lt_mask = (1u << lane) - 1u;
@@ -124,7 +133,7 @@ route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, c
 #pragma unroll
   for (int sidx = 0; sidx < UNIT / 32; ++sidx) {
     const int64_t i = first + sidx * 32 + lane;
-    ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E) : -2;
+    ev[sidx] = i < n ? load_id(ids, is64, i, id_map, E, kx) : -2;
   }
   for (int e = lane; e < E; e += 32) wh[e] = unit_base[u * E + e];
   __syncwarp();
@@ -146,6 +155,73 @@ route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, c
       if (perm) perm[pos] = (int32_t)i;
       if (inv) inv[i] = pos;
     }
+  }
+}
+
+// Small inputs (n <= RSMALL_MAX): the whole stage in one CTA and one launch.  Counts by shared-memory atomics, an
+// exclusive scan over the experts, then the stable permutation in rounds of 1024 consecutive entries: inside a
+// round an entry's place is its expert's running start + the entries of that expert in earlier warps of the round
+// (one count per warp and expert, written by the first lane of each match group) + its rank among equal ids of
+// its own warp.  Same results as the three-kernel path, two launches fewer on the latency-bound small layers.
+__global__ void __launch_bounds__(1024)
+route_small_kernel(const void* __restrict__ ids, int is64, int n, int E, const int32_t* __restrict__ id_map,
+                   int32_t* __restrict__ counts, int32_t* __restrict__ offsets, int32_t* __restrict__ perm,
+                   int32_t* __restrict__ inv, int32_t* __restrict__ status, int kx) {
+  extern __shared__ int32_t sh[];
+  int32_t* base = sh;                 // [E]   counts, then the running start of every expert
+  int32_t* wcnt = sh + E;             // [32][E]
+  __shared__ int32_t warp_tot[32];
+  __shared__ int32_t carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const unsigned lt_mask = (1u << lane) - 1u;
+  for (int i = tid; i < 33 * E; i += 1024) sh[i] = 0;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  bool bad = false;
+  for (int i = tid; i < n; i += 1024) {
+    const int e = load_id(ids, is64, i, id_map, E, kx);
+    if (e >= 0) atomicAdd(&base[e], 1); else bad = true;
+  }
+  if (bad && status) status[0] = ST_BAD_EXPERT_ID;
+  __syncthreads();
+  for (int b0 = 0; b0 < E; b0 += 1024) {          // exclusive scan, 1024 experts at a time
+    const int e = b0 + tid;
+    const int32_t total = e < E ? base[e] : 0;
+    int32_t inc = total;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+      if (lane >= o) inc += v;
+    }
+    if (lane == 31) warp_tot[w] = inc;
+    __syncthreads();
+    int32_t before = carry_s;
+    for (int w2 = 0; w2 < w; ++w2) before += warp_tot[w2];
+    const int32_t start = before + inc - total;
+    if (e < E) { counts[e] = total; offsets[e] = start; base[e] = start; }
+    __syncthreads();
+    if (tid == 1023) carry_s = before + inc;
+    __syncthreads();
+  }
+  if (tid == 0) offsets[E] = carry_s;
+  if (!perm && !inv) return;
+  for (int r0 = 0; r0 < n; r0 += 1024) {
+    const int i = r0 + tid;
+    const int e = i < n ? load_id(ids, is64, i, id_map, E, kx) : -1;
+    const bool valid = e >= 0;
+    const unsigned grp = __match_any_sync(0xFFFFFFFFu, valid ? (unsigned)e : (0x80000000u | (unsigned)lane));
+    const int rank = __popc(grp & lt_mask);
+    if (valid && rank == 0) wcnt[w * E + e] = __popc(grp);
+    __syncthreads();
+    if (valid) {
+      int32_t pos = base[e] + rank;
+      for (int w2 = 0; w2 < w; ++w2) pos += wcnt[w2 * E + e];
+      if (perm) perm[pos] = i;
+      if (inv) inv[i] = pos;
+    }
+    __syncthreads();
+    if (valid && rank == 0) { atomicAdd(&base[e], __popc(grp)); wcnt[w * E + e] = 0; }
+    __syncthreads();
   }
 }
 
@@ -422,6 +498,15 @@ extern "C" size_t moe_route_histogram_workspace(int64_t n, int E) {
 extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64_t n, int E, const int32_t* id_map,
                                    int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv, void* ws,
                                    size_t ws_bytes, int32_t* status, void* stream) {
+  return moe::route_histogram_ex(topk_idx, idx_is_int64, n, E, id_map, counts, offsets, perm, inv, ws, ws_bytes, status,
+                                 stream, 0);
+}
+
+// kx > 0: n counts a virtual list in which every kx stored ids are followed by one entry of expert E - 1 (declared in
+// common.cuh; used by the single-call layer to run the shared expert as one more group of the routed GEMMs)
+int moe::route_histogram_ex(const void* topk_idx, int idx_is_int64, int64_t n, int E, const int32_t* id_map,
+                            int32_t* counts, int32_t* offsets, int32_t* perm, int32_t* inv, void* ws, size_t ws_bytes,
+                            int32_t* status, void* stream, int kx) {
   using namespace moe;
   if (n < 0 || E < 1) return fail(MOE_ERR_ARG, "route_histogram: bad size n=%lld E=%d", (long long)n, E);
   if (!counts || !offsets) return fail(MOE_ERR_ARG, "route_histogram: null counts/offsets");
@@ -432,6 +517,14 @@ extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64
   if (need > 0 && (!ws || ws_bytes < need)) return fail(MOE_ERR_WORKSPACE, "route_histogram: workspace %zu < %zu", ws_bytes, need);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool small = n <= RSMALL_MAX;
+  if (small && n > 0 && E <= 1024) {   // one CTA, one launch
+    const size_t smem1 = (size_t)33 * E * 4;
+    if (smem1 > 48 * 1024)
+      MOE_CUDA_CHECK(cudaFuncSetAttribute(route_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
+    route_small_kernel<<<1, 1024, smem1, st>>>(topk_idx, idx_is_int64, (int)n, E, id_map, counts, offsets, perm, inv, status, kx);
+    MOE_CHECK_LAUNCH("route_small_kernel");
+    return MOE_OK;
+  }
   const int64_t units = ceil_div64(n, small ? RUNIT_SMALL : RUNIT);
   const size_t smem = (size_t)RWPB * E * 4;
   int32_t* unit_counts = reinterpret_cast<int32_t*>(ws);
@@ -443,15 +536,15 @@ extern "C" int moe_route_histogram(const void* topk_idx, int idx_is_int64, int64
   }
   const unsigned blocks = (unsigned)ceil_div64(units, RWPB);
   if (units > 0) {
-    if (small) route_count_kernel<RUNIT_SMALL><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
-    else route_count_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
+    if (small) route_count_kernel<RUNIT_SMALL><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status, kx);
+    else route_count_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status, kx);
     MOE_CHECK_LAUNCH("route_count_kernel");
   }
   route_scan_kernel<<<1, 1024, 0, st>>>(unit_counts, units, E, counts, offsets);
   MOE_CHECK_LAUNCH("route_scan_kernel");
   if (units > 0 && (perm || inv)) {
-    if (small) route_scatter_kernel<RUNIT_SMALL><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
-    else route_scatter_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
+    if (small) route_scatter_kernel<RUNIT_SMALL><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv, kx);
+    else route_scatter_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv, kx);
     MOE_CHECK_LAUNCH("route_scatter_kernel");
   }
   return MOE_OK;
@@ -1093,13 +1186,13 @@ extern "C" int moe_route_histogram_static(const void* topk_idx, int idx_is_int64
   // Nothing in the array has to start at zero: the count kernel writes every entry of the
   // units x E table it will later read, so whatever an earlier call left behind is overwritten.
   if (units > 0) {
-    route_count_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status);
+    route_count_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, status, 0);
     MOE_CHECK_LAUNCH("route_count_kernel");
   }
   route_scan_kernel<<<1, 1024, 0, st>>>(unit_counts, units, E, counts, offsets);
   MOE_CHECK_LAUNCH("route_scan_kernel");
   if (units > 0 && (perm || inv)) {
-    route_scatter_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv);
+    route_scatter_kernel<RUNIT><<<blocks, RWPB * 32, smem, st>>>(topk_idx, idx_is_int64, n, E, id_map, unit_counts, perm, inv, 0);
     MOE_CHECK_LAUNCH("route_scatter_kernel");
   }
   return MOE_OK;

@@ -107,9 +107,41 @@ class FusedMoETileLang:
         self.ws = _layer.SingleCallWorkspace(batch_size * seq_len, n_experts_per_token, d_hidden, d_expert,
                                              n_routed_experts, d_expert * n_shared_experts, dev, dtype)
 
+    # A single shared expert of the routed experts' width can run as expert E of the routed grouped GEMMs (five
+    # launches for the whole layer, no second stream): the library does so when the shared weights lie directly behind
+    # the routed ones in memory.  The layer object keeps such stacked copies of the weights it is called with, as the
+    # reference's layer keeps its stacked expert tensors (kernels/fusedmoe_tilelang.py:296-307), as long as they stay
+    # below this size; larger layers keep the side-stream form and their weights where they are.
+    STACK_LIMIT_BYTES = 2 << 30
+
+    def _stacked(self, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down):
+        ws = (shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down)
+        E, I, H = routed_gate.shape
+        if (self.n_shared_experts != 1 or H % 64 or any(w is None for w in ws)
+                or 3 * (E + 1) * I * H * routed_gate.element_size() > self.STACK_LIMIT_BYTES):
+            return None
+        key = tuple((w.data_ptr(), w._version) for w in ws)
+        if getattr(self, "_stack_key", None) != key:
+            def stack(routed, shared, shape):
+                out = torch.empty(E + 1, *shape, dtype=routed.dtype, device=routed.device)
+                out[:E].copy_(routed)
+                out[E].copy_(shared.reshape(shape))
+                return out
+            self._stack = (stack(routed_gate, shared_gate, (I, H)), stack(routed_up, shared_up, (I, H)),
+                           stack(routed_down, shared_down, (H, I)))
+            self._stack_key = key
+        return self._stack
+
     def forward(self, x, router_weight, shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down,
                 logits: Optional[torch.Tensor] = None):
         """One library call (``moe_layer_forward``) enqueues the whole layer."""
+        st = self._stacked(shared_gate, shared_up, shared_down, routed_gate, routed_up, routed_down) \
+            if self.n_shared_experts else None
+        if st is not None:
+            E = routed_gate.shape[0]
+            g, u, d = st
+            return _layer.moe_forward_single_call(x, router_weight, g[E], u[E], d[E], g[:E], u[:E], d[:E],
+                                                  self.n_experts_per_token, ws=self.ws, logits=logits)
         return _layer.moe_forward_single_call(x, router_weight, shared_gate if self.n_shared_experts else None,
                                               shared_up, shared_down, routed_gate, routed_up, routed_down,
                                               self.n_experts_per_token, ws=self.ws, logits=logits)
