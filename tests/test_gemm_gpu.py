@@ -273,3 +273,21 @@ def test_outputs_stay_inside_their_rows(cuda, lib, monkeypatch):
         for buf in (act_buf, yk_buf):
             assert (buf[:pad] == 77.0).all() and (buf[pad + T:] == 77.0).all(), f"a store left its buffer ({mode})"
         assert not (act == 77.0).all(dim=1).any() and not (yk == 77.0).all(dim=1).any()   # every row was written
+
+
+def test_two_devices_in_one_process(lib):
+    """The opt-in for large dynamic shared memory is a per-device attribute of a kernel: a process that drives two GPUs
+    must get it on each of them (a process-wide flag would make the first GEMM on the second device fail)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    g = torch.Generator().manual_seed(9)
+    X = torch.randn(700, 256, generator=g).bfloat16()
+    W = (torch.randn(4, 256, 256, generator=g) * 0.05).bfloat16()
+    idx = torch.randint(0, 4, (700,), generator=g)
+    ref = O.grouped_gemm(X, W, idx)
+    for d in (0, 1, 0):
+        dev = torch.device("cuda", d)
+        with torch.cuda.device(dev):
+            y = kernels.grouped_gemm(X.to(dev), W.to(dev), idx.to(dev))
+            ops.check_status(dev)
+        _close(y, ref)

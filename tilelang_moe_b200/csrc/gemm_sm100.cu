@@ -668,15 +668,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const float vmax = ikey_to_float(kv[0]);
         float rowsum = 0.f;
         if (p.r_mode != MOE_TOPK_MODE_B) {       // conventions that normalise over all experts: second pass over TMEM
-#pragma unroll 1
+          double total = 0.0;                    // 32-term fp32 sums added up in fp64: the denominator of up to 256 terms
+#pragma unroll 1                                  // keeps the scores within 1e-6 of an exactly summed softmax
           for (int c = 0; c < chunks; ++c) {
             uint32_t v[32];
             tmem_ld32(taddr + c * 32, v);
             tmem_ld_wait();
+            float part = 0.f;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (c * 32 + j < p.N) rowsum += expf(__uint_as_float(v[j]) - vmax);
+              if (c * 32 + j < p.N) part += expf(__uint_as_float(v[j]) - vmax);
+            total += (double)part;
           }
+          rowsum = (float)total;
         }
         if (row_ok) {
           float e[KMAX];
