@@ -226,7 +226,15 @@ int moe_router_topk_splitk(const void* x, const void* Wr, int64_t T, int H, int 
  *   side_stream: optional second stream for the shared expert (fork / join by events; NULL = same stream).
  * Results are bit-identical to issuing the calls one by one.  No host synchronisation.  With a side stream the
  * fork / join uses two events that the library keeps per device: host threads that call this function for the
- * same device at the same time must pass side_stream = NULL.
+ * same device at the same time must pass side_stream = NULL.  Every return after the fork, errors included, first
+ * makes `stream` wait for the side stream again, so a stream capture around the call is never left unjoined.
+ * Shared expert as one more group: when SI == I, H % 64 == 0 and the shared weights lie directly behind the routed
+ * ones in memory (shared_gate == routed_gate + E*I*H elements, likewise up and down: one [E+1, ...] tensor per
+ * projection), the shared expert runs as expert E of the routed grouped GEMMs - every token gets k + 1 entries, the
+ * last with weight 1 - and the whole layer is five launches on `stream` (the reference overlaps its shared and
+ * routed kernels on two streams instead, kernels/fusedmoe_tilelang.py:428-553).  Same bits as the other form.
+ * The router kernel (one kernel, split along K, or GEMM then top-k) is chosen from T, H and E: fp32 logits of one
+ * token can differ in summation order between batch sizes, so a near-tie may route differently in another batch size.
  */
 size_t moe_layer_workspace(int64_t T, int k, int H, int I, int E, int SI);
 int moe_layer_forward(const void* x, const void* router_weight, const float* logits, const void* shared_gate,
