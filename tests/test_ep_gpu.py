@@ -112,7 +112,7 @@ def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedu
     scattering down GEMM / combine) against the oracle for 4 and 8 ranks without needing that many GPUs."""
     from oracle import moe_oracle as O
     from tilelang_moe_b200 import ep, inputs, ops
-    monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)   # single-CTA kernel, or the CTA-pair kernel's gather / peer epilogue
+    monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)   # single-CTA kernel, or the CTA-pair kernel's peer epilogue
     dev = cuda
     El, k, Tl = 4, 4, 96
     E, T = G * El, G * 96

@@ -901,39 +901,6 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc,
 __host__ __device__ constexpr uint32_t make_idesc_mn(int m, int n, int f16 = 0) {
   return (1u << 4) | ((f16 ? 0u : 1u) << 7) | ((f16 ? 0u : 1u) << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-// The leader's wait on full[s]: the gather path of CTA 1 arrives from the other SM with release.cluster.
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done;
-}
-__device__ __noinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                               int site, uint64_t limit_ns = WAIT_LIMIT_NS) {
-#pragma unroll 1
-  for (int i = 0; i < 32; ++i)
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > limit_ns) {
-      if (atomicExch((int*)abort_flag, 1) == 0 && status) {
-        status[0] = ST_WAIT_TIMEOUT;
-        status[1] = site;
-        status[2] = (int32_t)blockIdx.x;
-      }
-      return false;
-    }
-  }
-}
 
 // 32 consecutive output columns of one row, fp32 in registers -> 16-byte stores of the output type
 template <int EPI>
@@ -960,8 +927,8 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, void* ybase, in
   }
 }
 
-template <int EPI, bool GATHER>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? NUM_THREADS_GATHER : NUM_THREADS, 1)
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA64,
                          const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
                          const Params p) {
@@ -974,7 +941,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
-  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain, [2S+5..3S+5) gfull
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::BAR_OFFSET + 200);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::BAR_OFFSET + 208);
   volatile uint32_t* tile_light = reinterpret_cast<volatile uint32_t*>(smem + C::BAR_OFFSET + 216);   // ring of 8
@@ -987,19 +954,15 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
   const uint32_t tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
   const uint32_t drain_bar = smem_u32(bars + 2 * STAGES + 4);
-  const uint32_t gfull0 = smem_u32(bars + 2 * STAGES + 5);
   const uint32_t lead_full0 = map_to_cta(full0, 0), lead_tempty0 = map_to_cta(tempty0, 0);
   const int E = p.E, NT = p.num_n_tiles, NKB = p.num_k_blocks;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-  constexpr bool gather = GATHER;   // its own instantiation: the copy loops cost every warp of the kernel registers
 
   if (threadIdx.x == 0) {
-    // full (used in CTA 0): the producer's arrive, + with a row gather one arrival per lane of CTA 0's two gather
-    // warps and one from CTA 1's forwarding warp
+    // full (used in CTA 0): the producer's arrive; the copies of both CTAs count their bytes on it
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full0 + 8 * s, gather ? 66 : 1);
+      mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
-      mbar_init(gfull0 + 8 * s, 64);
     }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
     mbar_init(drain_bar, 1);
@@ -1036,7 +999,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       const bool light = t.row_end - t.row0 <= BM;           // 128-row tile: 64 rows per CTA
       const int n0 = t.n_tile * OUT_COLS;
       const int a_row = t.row0 + (int)rank * (light ? BM / 2 : BM);
-      const uint32_t tx = gather ? 2u * C::B_BYTES : (light ? 2u * (C::A_BYTES / 2 + C::B_BYTES) : 2u * C::STAGE_BYTES);
+      const uint32_t tx = light ? 2u * (C::A_BYTES / 2 + C::B_BYTES) : 2u * C::STAGE_BYTES;
       // read by the MMA issuer after the first full barrier of the tile; the producer runs at most STAGES (< 8) k-blocks,
       // hence tiles, ahead of it
       if (leader && lane == 0) tile_light[seq & 7] = light ? 1u : 0u;
@@ -1048,7 +1011,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
           const uint32_t sb = sa + C::A_BYTES;
           if (leader) mbar_arrive_expect_tx(full0 + 8 * stage, tx);
-          if (!gather) tma_load_2d_pair(sa, light ? &tmA64 : &tmA, lead_full, kb * BK, a_row);
+          tma_load_2d_pair(sa, light ? &tmA64 : &tmA, lead_full, kb * BK, a_row);
           if (GATE) {   // this CTA's 64 gate rows, then its 64 up rows of the same output columns
             tma_load_3d_pair(sb, &tmB, lead_full, kb * BK, n0 + (int)rank * (OUT_COLS / 2), t.e);
             tma_load_3d_pair(sb + C::B_BYTES / 2, &tmB2, lead_full, kb * BK, n0 + (int)rank * (OUT_COLS / 2), t.e);
@@ -1090,15 +1053,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < NKB; ++kb) {
-          // plain TMA arrivals need no more than the CTA-scope wait; the gather path of CTA 1 arrives across the cluster
-          if (!(gather ? mbar_wait_cluster(full0 + 8 * stage, phase, abort_flag, p.status, 13)
-                       : mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 13))) { ok = false; break; }
+          // the peer's copies count their bytes on this barrier through the TMA unit: the CTA-scope wait is enough
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, p.status, 13)) { ok = false; break; }
           tc_fence_after();
           // the tile's shape comes from the producer (written before its first arrive on this barrier): a table look-up
           // here would sit between two tiles' instruction streams with the tensor pipe idle
           if (kb == 0) idesc = tile_light[seq & 7] ? idesc_l : idesc_h;
           if (lane == 0) {
-            if (gather) fence_proxy_async();   // this CTA's A rows were written by cp.async, not by the TMA unit
             const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
             const uint64_t adesc = make_smem_desc(sa);
             const uint64_t bdesc = make_smem_desc(sa + C::A_BYTES);
@@ -1125,74 +1086,6 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         __syncwarp();
         mbar_wait_drain(drain_bar, 0, DRAIN_LIMIT_NS);
       }
-    } else if (gather) {
-      // ===================================================================== gather forwarder (CTA 1)
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
-        for (int kb = 0; kb < NKB; ++kb) {
-          if (!mbar_wait(gfull0 + 8 * stage, phase, abort_flag, p.status, 16)) { ok = false; break; }
-          if (lane == 0) {
-            fence_proxy_async();                           // the rows become visible to the tensor core's reads
-            mbar_arrive_cluster(lead_full0 + 8 * stage);
-          }
-          __syncwarp();
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-      }
-    }
-  } else if (warp >= 6) {
-    // ===================================================================== A-row gather (both CTAs, only when asked to)
-    // A 256-row tile: this CTA's 128 rows, 64 per warp; a 128-row tile: this CTA's 64 rows, 32 per warp.  8 lanes
-    // cover the 128 bytes of one row piece, so one cp.async instruction moves four row pieces.
-    if (gather) {
-      const unsigned char* src_base = reinterpret_cast<const unsigned char*>(p.a_src);
-      const size_t row_bytes = (size_t)p.K * 2;
-      const int chunk = lane & 7, sub = lane >> 3;
-      const uint32_t arrive0 = leader ? full0 : gfull0;
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cluster_id; ok && tile < total_tiles; tile += n_clusters) {
-        const Tile t = decode_tile(tile, tstart, offs, E, NT, TILE_ROWS);
-        const bool light = t.row_end - t.row0 <= BM;
-        const int rows_w = light ? 32 : 64;                                  // rows this warp copies
-        const int cta_row0 = (warp - 6) * rows_w;                            // first of them inside this CTA's A block
-        const int tile_row0 = t.row0 + (int)rank * (light ? BM / 2 : BM) + cta_row0;
-        uint32_t src_row[2];
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          int r = tile_row0 + lane + 32 * s;
-          if (r > p.a_rows - 1) r = p.a_rows - 1;
-          const uint32_t v = (uint32_t)p.a_gather[r] / (uint32_t)p.a_div;
-          src_row[s] = v < (uint32_t)p.a_src_rows ? v : (uint32_t)(p.a_src_rows - 1);
-        }
-        const unsigned char* rp[16];
-        uint32_t live = 0;
-#pragma unroll
-        for (int it = 0; it < 16; ++it) {
-          const int row = it * 4 + sub;
-          const uint32_t sr = __shfl_sync(0xFFFFFFFFu, src_row[it >> 3], row & 31);
-          rp[it] = src_base + (size_t)sr * row_bytes + chunk * 16;
-          if (row < rows_w && tile_row0 + row < t.row_end) live |= 1u << it;
-        }
-        const int its = rows_w >> 2;
-        for (int kb = 0; kb < NKB; ++kb) {
-          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
-          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES) + cta_row0 * 128;
-          const size_t koff = (size_t)kb * (BK * 2);
-#pragma unroll
-          for (int it = 0; it < 16; ++it) {
-            const int row = it * 4 + sub;
-            if (it < its)
-              cp_async_16(sa + row * 128 + ((chunk ^ (row & 7)) << 4), rp[it] + koff, (live >> it) & 1u ? 16u : 0u);
-          }
-          cp_async_arrive_noinc(arrive0 + 8 * stage);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-      }
-      cp_async_wait_all();
     }
   } else {
     // ===================================================================== epilogue (warps 2..5 of both CTAs)
@@ -1384,23 +1277,16 @@ static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
   return launch_g<MT, BN, EPI, false>(tA, tB, tB2, p, grid, st);
 }
 
-template <int EPI, bool GATHER>
-static int launch_pair_g(const CUtensorMap& tA, const CUtensorMap& tA64, const CUtensorMap& tB, const CUtensorMap& tB2,
-                         const Params& p, int grid, cudaStream_t st) {
-  constexpr int SMEM = EPI == EPI_PEER ? PairCfg::SMEM_BYTES_PEER : PairCfg::SMEM_BYTES;
-  static std::atomic<bool> attr_set[64];
-  int rc = allow_dynamic_smem(grouped_gemm_pair_kernel<EPI, GATHER>, SMEM, attr_set);
-  if (rc) return rc;
-  // the two gather warps exist only in the instantiation that gathers
-  grouped_gemm_pair_kernel<EPI, GATHER><<<grid, GATHER ? NUM_THREADS_GATHER : NUM_THREADS, SMEM, st>>>(tA, tA64, tB, tB2, p);
-  MOE_CHECK_LAUNCH("grouped_gemm_pair_kernel");
-  return MOE_OK;
-}
 template <int EPI>
 static int launch_pair(const CUtensorMap& tA, const CUtensorMap& tA64, const CUtensorMap& tB, const CUtensorMap& tB2,
                        const Params& p, int grid, cudaStream_t st) {
-  if (p.a_gather) return launch_pair_g<EPI, true>(tA, tA64, tB, tB2, p, grid, st);
-  return launch_pair_g<EPI, false>(tA, tA64, tB, tB2, p, grid, st);
+  constexpr int SMEM = EPI == EPI_PEER ? PairCfg::SMEM_BYTES_PEER : PairCfg::SMEM_BYTES;
+  static std::atomic<bool> attr_set[64];
+  int rc = allow_dynamic_smem(grouped_gemm_pair_kernel<EPI>, SMEM, attr_set);
+  if (rc) return rc;
+  grouped_gemm_pair_kernel<EPI><<<grid, NUM_THREADS, SMEM, st>>>(tA, tA64, tB, tB2, p);
+  MOE_CHECK_LAUNCH("grouped_gemm_pair_kernel");
+  return MOE_OK;
 }
 
 }  // namespace gemm
@@ -1596,7 +1482,9 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   const int64_t m_tiles_128 = live_rows / BM + E, m_tiles_256 = live_rows / (2 * BM) + E;
   int BN = 128;
   if (gate || (N % 256 == 0 && m_tiles_128 * n_tiles_256 >= dev.sm_count)) BN = 256;
-  const bool pair_ok = (gate ? N % 64 == 0 : N % 256 == 0) && epilogue != MOE_GEMM_PLAIN_F32 && !(ga.idx && K % 64);
+  // the pair kernel reads its A rows through TMA only: a row gather by cp.async needs a relay from the second CTA to the
+  // leader's barrier (measured: 15 % behind the 128-row kernel with a relaxed arrive, 2.4x behind with a releasing one)
+  const bool pair_ok = (gate ? N % 64 == 0 : N % 256 == 0) && epilogue != MOE_GEMM_PLAIN_F32 && !ga.idx;
   // measured on B200 under its power cap: the pair kernel gains 3-10 % where groups are uniformly large and loses
   // where most experts own a single tile (their weight stream wants the deeper per-SM ring of the single-CTA kernel)
   bool pair = pair_ok && live_rows / E >= 512 && (live_rows / (2 * BM)) * n_tiles_256 * 2 >= (int64_t)dev.sm_count;
