@@ -92,6 +92,120 @@ def test_ep_protocol_matches_single_process(world, placement):
         assert err < 1e-4, f"rank {rank}: max abs error {err}"
 
 
+def _run_ranks(target, world, *args, timeout=120):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, *args, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = dict(q.get(timeout=timeout) for _ in range(world))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+    return res
+
+
+def _small_case(rank, world):
+    T, H, I, E, k = 64, 32, 16, 8, 3
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(T, H, generator=g)
+    Wg = torch.randn(E, I, H, generator=g) * 0.2
+    Wu = torch.randn(E, I, H, generator=g) * 0.2
+    Wd = torch.randn(E, H, I, generator=g) * 0.2
+    logits = inputs.zipf_logits(T, E, 1.1, seed=1)
+    plan = ep.EPPlan(E, world, ep.contiguous_placement(E, world))
+    mine = plan.local_experts[rank]
+    Tl = T // world
+    sl = slice(rank * Tl, (rank + 1) * Tl)
+    return (x[sl], logits[sl], k, plan, torch.tensor(plan.id_map, dtype=torch.int32), Wg[mine], Wu[mine], Wd[mine])
+
+
+def _worker_damaged_counts(rank, world, port, q):
+    """Rank 1's histogram is damaged after routing: every rank must raise EPProtocolError, none may wait."""
+    import sys
+    import types
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import cpu_ops
+    from datetime import timedelta
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=20))
+    try:
+        ops = types.SimpleNamespace(**{n: getattr(cpu_ops, n) for n in dir(cpu_ops) if not n.startswith("_")})
+        if rank == 1:
+            def damaged(*a, **kw):
+                counts, offsets, perm, inv = cpu_ops.route_histogram(*a, **kw)
+                counts = counts.clone()
+                counts[2] += 5
+                return counts, offsets, perm, inv
+            ops.route_histogram = damaged
+        try:
+            ep.ep_forward(*_small_case(rank, world), ops)
+            q.put((rank, "returned"))
+        except ep.EPProtocolError as e:
+            q.put((rank, "protocol error: " + str(e)))
+        except Exception as e:
+            q.put((rank, "other: " + repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_damaged_counts_table_makes_every_rank_raise():
+    res = _run_ranks(_worker_damaged_counts, 2)
+    for rank in range(2):
+        assert res[rank].startswith("protocol error"), res
+        assert "rank 1 reports 101 routed rows, 96 expected" in res[rank], res
+
+
+def _put_and_flush(q, item):
+    q.put(item)
+    q.close()
+    q.join_thread()      # os._exit would drop what the queue's feeder thread has not written yet
+
+
+def _worker_rank_leaves(rank, world, port, q):
+    """Both ranks run one step; rank 1 then leaves (between steps, nothing in flight).  Rank 0's next step must end
+    with an error within the process group's time limit instead of waiting for good."""
+    import sys
+    import time
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import cpu_ops
+    from datetime import timedelta
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=5))
+    case = _small_case(rank, world)
+    ep.ep_forward(*case, cpu_ops)                    # step 1: everyone is there
+    if rank == 1:
+        _put_and_flush(q, (rank, "left"))
+        os._exit(0)                                  # gone without a word
+    t0 = time.time()
+    try:
+        ep.ep_forward(*case, cpu_ops)                # step 2: the peer never joins
+        _put_and_flush(q, (rank, "returned"))
+    except Exception as e:
+        _put_and_flush(q, (rank, f"raised after {time.time() - t0:.1f} s: {type(e).__name__}"))
+    os._exit(0)                                      # the group cannot be torn down in order any more
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_collective_with_an_error():
+    res = _run_ranks(_worker_rank_leaves, 2, timeout=90)
+    assert res[1] == "left"
+    assert res[0].startswith("raised after"), res
+    assert float(res[0].split()[2]) < 60.0, res
+
+
+def test_check_counts_table_accepts_and_rejects():
+    ok = torch.tensor([[3, 0, 5], [1, 7, 0]], dtype=torch.int32)
+    ep.check_counts_table(ok, 8)
+    with pytest.raises(ep.EPProtocolError, match="rank 1 reports 9 routed rows"):
+        ep.check_counts_table(torch.tensor([[3, 0, 5], [1, 8, 0]]), 8)
+    with pytest.raises(ep.EPProtocolError, match="reports -1 rows for expert slot 1"):
+        ep.check_counts_table(torch.tensor([[3, -1, 6], [1, 7, 0]]), 8)
+
+
 def test_dedup_dispatch_tables_model():
     """The arithmetic of the de-duplicated dispatch (moe_ep_unique / moe_ep_plan_dedup / moe_ep_dispatch_dedup), restated
     in numpy for all ranks in one process: a token row is stored once per destination rank, and the index list the

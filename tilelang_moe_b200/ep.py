@@ -2,7 +2,7 @@
 data-parallel, one exchange each way.
 
     rank r owns T/G tokens and E/G experts (placement table expert -> rank).
-    route locally -> sort rows by (destination rank, local expert) -> counts all-to-all
+    route locally -> sort rows by (destination rank, local expert) -> all-gather of the histograms (checked)
     -> dispatch all-to-all-v of bf16 rows -> regroup expert-major -> up / down GEMMs
     -> combine all-to-all-v back -> weighted k-way sum on the owner.
 
@@ -100,6 +100,25 @@ class EPPlan:
 
 
 # --------------------------------------------------------------------------- protocol
+class EPProtocolError(RuntimeError):
+    """The ranks' histograms do not describe a possible exchange (a damaged or mismatched counts table)."""
+
+
+def check_counts_table(table: torch.Tensor, rows_per_rank: int) -> None:
+    """table int [G,E] on the host: row g = rank g's rows per expert (placement order).  Every rank routes the same
+    number of rows, so each row must be non-negative and sum to rows_per_rank; anything else would size the row
+    exchange wrongly on some rank.  Every rank holds the same table and therefore raises, or passes, with the others."""
+    t = table.long()
+    if bool((t < 0).any()):
+        g, e = [int(v[0]) for v in torch.nonzero(t < 0, as_tuple=True)]
+        raise EPProtocolError(f"counts table: rank {g} reports {int(t[g, e])} rows for expert slot {e}")
+    sums = t.sum(1)
+    bad = torch.nonzero(sums != rows_per_rank).flatten()
+    if bad.numel():
+        g = int(bad[0])
+        raise EPProtocolError(f"counts table: rank {g} reports {int(sums[g])} routed rows, {rows_per_rank} expected")
+
+
 def ep_forward(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: EPPlan, id_map_dev: torch.Tensor,
                Wg: torch.Tensor, Wu: torch.Tensor, Wd: torch.Tensor, ops, group=None, bufs: Optional[dict] = None,
                timers: Optional[dict] = None, stage=None) -> torch.Tensor:
@@ -119,10 +138,17 @@ def ep_forward(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: 
         counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map_dev, workspace=bufs.get("hist_ws"))
         xs = ops.gather_rows(x_local, perm, div=k, out=bufs.get("xs"))
     with st("counts_a2a"):
-        recv_counts = torch.empty_like(counts)
-        dist.all_to_all_single(recv_counts, counts, group=group)      # equal splits of E_local ints
-        sizes = torch.stack([counts.view(G, El).sum(1), recv_counts.view(G, El).sum(1)]).cpu()   # one D2H sync
-        in_splits, out_splits = sizes[0].tolist(), sizes[1].tolist()
+        # every rank sees every rank's histogram (G x E ints) and checks all of it, so that a damaged table makes all
+        # ranks raise together instead of leaving some of them waiting in the row exchange
+        rank = dist.get_rank(group)
+        table = torch.empty(G, E, dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(table.view(-1), counts.contiguous(), group=group)
+        table_host = table.cpu()                                       # the one device-to-host wait of the layer
+        check_counts_table(table_host, n)
+        mine = table_host[:, rank * El:(rank + 1) * El]                # rows sent to this rank's experts, per source
+        recv_counts = table[:, rank * El:(rank + 1) * El].contiguous().view(-1)
+        in_splits = table_host[rank].view(G, El).sum(1).tolist()
+        out_splits = mine.sum(1).tolist()
         n_recv = int(sum(out_splits))
     with st("dispatch_a2a"):
         recv = _take(bufs, "recv", n_recv, H, x_local)
