@@ -535,6 +535,8 @@ def run_ours(args, wl_name, cfg):
         extra["c2"] = c2_block(dev, peaks, flush, not args.no_cpu)
         extra["c3"] = c3_block(dev)
         del flush
+        if not args.no_cpu:
+            extra["reference_gpu"] = reference_gpu_block(dev, cfg, x, logits, Wg, Wu, Wd, step())
 
     cpu_v, cpu_desc, cpu_kind = None, None, "port"
     if world == 1 and cfg["S"] > 0 and not args.no_cpu:
@@ -725,6 +727,60 @@ def c3_block(dev):
     flops = 2.0 * T * H * E + (T * k + T * S) * 6.0 * H * I
     return {"us_eager": round(us_eager, 2), "us_graph": round(us_graph, 2), "tokens_per_s_graph": round(T / us_graph * 1e6),
             "TFLOPs_graph": round(flops / us_graph / 1e6, 1)}
+
+
+def reference_gpu_block(dev, cfg, x, logits, Wg, Wu, Wd, ours):
+    """The reference's own PyTorch baseline (the unmodified copies under oracle/_ref: torch.topk / softmax and one
+    cuBLAS matmul per expert) run on this GPU beside the library: the layer of the headline workload on the same
+    device tensors, and its routing, grouped-GEMM and small fused-layer baselines on the fixed configurations.  A
+    comparator only: nothing of it is on the library's path."""
+    ref = load_reference()
+    if ref is None:
+        return {"unavailable": "oracle/_ref is absent (built by oracle/build.py where the reference checkout exists)"}
+    tk, gg, fm = ref["topk_softmax_baseline"], ref["grouped_gemm_baseline"], ref["fusedmoe_baseline"]
+    out = {"kind": "the reference's PyTorch baseline files, unmodified, with their tensors on this GPU (library kernels "
+                   "of torch: top-k, softmax, one cuBLAS GEMM per expert)"}
+    T, H, I, E, k = (cfg[n] for n in ("T", "H", "I", "E", "k"))
+    with torch.no_grad():
+        model = fm.FusedMoEPyTorch(H, I, E, 0, k)
+
+        def layer_ref():
+            sc, ix = tk.topk_softmax_separate(logits, k)
+            return model._compute_routed_experts(x, ix, sc.to(x.dtype), Wg, Wu, Wd)
+
+        y = layer_ref()
+        ms = _event_us(layer_ref, 5) / 1e3
+        out["layer"] = {"workload": "c5", "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3),
+                        "max_abs_diff_to_library": round((y.float() - ours.float()).abs().max().item(), 5),
+                        "max_abs_value": round(y.float().abs().max().item(), 4)}
+        del y
+        for name, M, N, kk in ROUTER_POINTS:
+            if M * N > (1 << 22):
+                continue
+            lg = torch.randn(M, N, generator=torch.Generator().manual_seed(0)).to(dev)
+            f = lambda: tk.topk_softmax_separate(lg, kk)
+            f()
+            out[name] = {"us": round(_event_us(f, 20), 2), "us_fused_variant": round(_event_us(lambda: tk.topk_softmax_fused(lg, kk), 20), 2)}
+        c = C2
+        g = torch.Generator().manual_seed(0)
+        X = torch.randn(c["T"], c["H"], generator=g).bfloat16()
+        W = (torch.randn(c["E"], c["I"], c["H"], generator=g) * 0.02).bfloat16().to(dev)
+        idx = torch.argsort(torch.rand(c["T"], c["E"], generator=g), dim=1)[:, :c["k"]].contiguous()
+        Xf, idf = X.repeat_interleave(c["k"], 0).to(dev), idx.reshape(-1).to(dev)
+        f = lambda: gg.grouped_gemm_loop(Xf, W, idf)
+        f()
+        out["c2"] = {"us_loop": round(_event_us(f, 10), 2)}
+        from tilelang_moe_b200 import kernels
+        c3 = WORKLOADS["c3"]
+        xc, wc = kernels.generate_fusedmoe_inputs(1, c3["T"], c3["H"], c3["I"], c3["E"], c3["S"], c3["k"],
+                                                  dtype=torch.bfloat16, device="cpu", seed=42)
+        names = ["router_weight", "shared_gate", "shared_up", "shared_down", "routed_gate", "routed_up", "routed_down"]
+        wd = [wc[n].to(dev) for n in names]
+        xd = xc.to(dev)
+        f = lambda: fm.fusedmoe_pytorch(xd, *wd, c3["k"])
+        f()
+        out["c3"] = {"us": round(_event_us(f, 10), 2)}
+    return out
 
 
 def parity_block(cfg, x_cpu, logits_cpu, tokens, got, weight_of):
