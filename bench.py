@@ -448,6 +448,38 @@ def run_ours(args, wl_name, cfg):
             step_e2e()
         ms_e2e, _, _ = timed(step_e2e, args.steps)
 
+    # what the box's host link gives all ranks at once: every rank moves one step's worth of its inputs down and of its
+    # output up, both directions together as in the pipelined steps, five times; the slowest rank's time counts
+    host_link = None
+    if not args.no_extra:
+        hb, db = h2d // world, d2h // world
+        src = torch.empty(hb, dtype=torch.uint8).pin_memory()
+        dst = torch.empty(db, dtype=torch.uint8).pin_memory()
+        din, dout = torch.empty(hb, dtype=torch.uint8, device=dev), torch.empty(db, dtype=torch.uint8, device=dev)
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+        def link_pass():
+            cur = torch.cuda.current_stream(dev)
+            s_in.wait_stream(cur)
+            s_out.wait_stream(cur)
+            for _ in range(5):
+                with torch.cuda.stream(s_in):
+                    din.copy_(src, non_blocking=True)
+                with torch.cuda.stream(s_out):
+                    dst.copy_(dout, non_blocking=True)
+            cur.wait_stream(s_in)
+            cur.wait_stream(s_out)
+
+        link_pass()
+        link_ms, _, _ = timed(link_pass, 1)
+        per_step = link_ms / 5
+        host_link = {"ms_per_step_of_copies_alone": round(per_step, 4),
+                     "h2d_GBps_all_ranks": round(h2d / per_step / 1e6, 1), "d2h_GBps_all_ranks": round(d2h / per_step / 1e6, 1),
+                     "how": "all ranks copy one step's inputs down and one step's output up at the same time (pinned "
+                            "memory, both directions together), nothing else running: the time below which no "
+                            "arrangement of the steps can bring e2e on this box"}
+        del src, dst, din, dout
+
     # per-stage device time from the events recorded inside the timed steps
     stages = {}
     for tm in stage_events:
@@ -568,7 +600,8 @@ def run_ours(args, wl_name, cfg):
         "e2e": {"value": tokens_per_step * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps,
                 "how": "pinned host buffers; H2D of x and logits and D2H of the output every step, on copy streams "
-                       "that overlap the neighbouring steps' compute (tilelang_moe_b200.pipeline.HostPipeline)"},
+                       "that overlap the neighbouring steps' compute (tilelang_moe_b200.pipeline.HostPipeline)",
+                "host_link": host_link},
         "gpu_launches": launches_per_step * args.steps,
         "host_enqueue_ms_per_step": round(host_enqueue_ms, 4),
         "stage_ms": stage_ms,

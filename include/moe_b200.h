@@ -322,6 +322,18 @@ int moe_ep_dispatch_dedup(const void* x, const int32_t* perm, const int32_t* top
  */
 int moe_ep_barrier(void* const* peer_flags, int G, int my_rank, int channel, int32_t epoch, int64_t timeout_us,
                    int32_t* status, void* stream);
+/* All-gather of the ranks' routing histograms over peer memory, closed by the same time-limited barrier: one launch
+ * instead of a collective library call.  No counterpart in the reference.
+ *   counts [n_counts] (+ extra [n_extra], may be null with n_extra = 0): this rank's vector, on the device.
+ *   peer_tables: host array of G device pointers; entry g addresses rank g's table, int32 [2][G][n_counts + n_extra],
+ *     writable by every rank.  The kernel stores this rank's vector into row [slot][my_rank] of every table, then
+ *     runs barrier `epoch` of `channel` (see moe_ep_barrier); behind it, table [slot] of this rank holds every rank's
+ *     vector.  slot alternates 0, 1 from step to step so that a rank one step ahead does not overwrite rows in use.
+ *   A wait that runs out leaves status = {2, 40 + channel, peer}, as in moe_ep_barrier.
+ */
+int moe_ep_share_counts(const int32_t* counts, int n_counts, const int32_t* extra, int n_extra,
+                        void* const* peer_tables, int slot, void* const* peer_flags, int G, int my_rank,
+                        int channel, int32_t epoch, int64_t timeout_us, int32_t* status, void* stream);
 int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* offsets,
                                   const int32_t* row_rank, const int32_t* dst_rows,
                                   void* const* peer_base, int n_peers, int64_t ldy, int64_t max_rows,

@@ -196,6 +196,38 @@ def test_barrier_gives_up_after_its_time_limit_and_reports_it(cuda, lib):
     assert y.sum().item() == 16
 
 
+def test_share_counts_fills_every_table_and_its_wait_is_limited(cuda, lib):
+    """The histogram exchange over peer memory on one GPU: two tables stand for two ranks.  "Rank 0"'s vector must land
+    in row [slot][0] of both tables; with the peer's arrival already published the barrier behind it passes, and with a
+    peer that never arrives the wait runs out (2 ms) and reports {2, 40 + channel, peer}."""
+    from tilelang_moe_b200 import _lib, ops
+    counts = torch.arange(1, 9, dtype=torch.int32, device=cuda)
+    extra = torch.tensor([70, 80], dtype=torch.int32, device=cuda)
+    width = 10
+    tables = [torch.full((2 * 2 * width,), -1, dtype=torch.int32, device=cuda) for _ in range(2)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=cuda) for _ in range(2)]
+    tptrs = ops._ptr_array([t.data_ptr() for t in tables])
+    fptrs = ops._ptr_array([f.data_ptr() for f in flags])
+    ops.check_status(cuda)
+    flags[0][3 * 16 + 1] = 5                       # "rank 1" has already arrived at barrier 5 of channel 3
+    ops.ep_share_counts(counts, extra, tptrs, 1, fptrs, 0, 3, 5, timeout_us=2000)
+    torch.cuda.synchronize(cuda)
+    ops.check_status(cuda)
+    want = torch.cat([counts, extra])
+    for t in tables:
+        v = t.view(2, 2, width)
+        assert torch.equal(v[1, 0], want)
+        assert bool((v[0] == -1).all()) and bool((v[1, 1] == -1).all())      # nothing else was touched
+    assert flags[1][3 * 16 + 0].item() == 5 and flags[0][3 * 16 + 0].item() == 5
+    # without the extra vector, other slot; the peer never reaches barrier 6
+    ops.ep_share_counts(counts, None, ops._ptr_array([t.data_ptr() for t in tables]), 0, fptrs, 0, 3, 6, timeout_us=2000)
+    torch.cuda.synchronize(cuda)
+    assert ops.status_buffer(cuda).tolist()[:3] == [2, 43, 1]
+    with pytest.raises(_lib.MoeLibraryError):
+        ops.check_status(cuda)
+    assert torch.equal(tables[1][:8], counts)       # row [0][0] at the narrower width of this call
+
+
 def test_dispatch_ignores_entries_with_an_expert_id_out_of_range(cuda, lib):
     """One routed entry carries id -1: the histogram reports it (status 1) and leaves it out of the permutation; the
     dispatch kernels must then stop at the live entries - nothing is read through the unwritten tail of the permutation

@@ -36,6 +36,8 @@ SIGNATURES = {
     "moe_ep_dispatch_dedup": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64,
                                      C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _i32, _vp]),
     "moe_ep_barrier": (_i32, [C.POINTER(C.c_void_p), _i32, _i32, _i32, _i32, _i64, _vp, _vp]),
+    "moe_ep_share_counts": (_i32, [_vp, _i32, _vp, _i32, C.POINTER(C.c_void_p), _i32, C.POINTER(C.c_void_p), _i32, _i32,
+                                   _i32, _i32, _i64, _vp, _vp]),
     "moe_debug_wait_probe": (_i32, [_i64, _vp, _vp, _vp]),
     "moe_grouped_gemm_peer_scatter": (_i32, [_vp, _vp, _vp, _vp, _vp, C.POINTER(C.c_void_p), _i32, _i64, _i64, _i64,
                                              _i32, _i32, _i32, _i32, _vp, _vp]),

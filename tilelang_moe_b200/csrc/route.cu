@@ -1085,11 +1085,20 @@ extern "C" int moe_ep_dispatch(const void* x, const int32_t* perm, const int32_t
 // GPU spins for ever because a peer died.
 // ====================================================================================
 namespace moe {
+// thread j's part of barrier `epoch` on `channel`: tell peer j that this rank has arrived, wait (time-limited) for peer j
+__device__ __forceinline__ void ep_barrier_thread(const PeerPtrs& flags, int j, int me, int channel, int32_t epoch,
+                                                  unsigned long long limit_ns, int32_t* __restrict__ status);
+
 __global__ void __launch_bounds__(32)
 ep_barrier_kernel(PeerPtrs flags, int G, int me, int channel, int32_t epoch, unsigned long long limit_ns,
                   int32_t* __restrict__ status) {
   const int j = threadIdx.x;
   if (j >= G) return;
+  ep_barrier_thread(flags, j, me, channel, epoch, limit_ns, status);
+}
+
+__device__ __forceinline__ void ep_barrier_thread(const PeerPtrs& flags, int j, int me, int channel, int32_t epoch,
+                                                  unsigned long long limit_ns, int32_t* __restrict__ status) {
   __threadfence_system();
   volatile int32_t* theirs = reinterpret_cast<volatile int32_t*>(flags.p[j]) + channel * 16 + me;
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
@@ -1110,6 +1119,23 @@ ep_barrier_kernel(PeerPtrs flags, int G, int me, int channel, int32_t epoch, uns
   }
   __threadfence_system();
 }
+
+// All-gather of every rank's small histogram over peer memory, closed by the barrier: this rank's `na + nb` ints go into
+// row `me` of table `slot` on every rank; once the barrier has passed, every rank's row is in this rank's own table.
+// Two tables (slot = step parity) so that a rank that is a step ahead never overwrites a row still being read.
+__global__ void __launch_bounds__(256)
+ep_share_counts_kernel(const int32_t* __restrict__ a, int na, const int32_t* __restrict__ b, int nb, PeerPtrs tables,
+                       int slot, PeerPtrs flags, int G, int me, int channel, int32_t epoch, unsigned long long limit_ns,
+                       int32_t* __restrict__ status) {
+  const int width = na + nb;
+  for (int g = 0; g < G; ++g) {
+    int32_t* dst = reinterpret_cast<int32_t*>(tables.p[g]) + ((int64_t)slot * G + me) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = i < na ? a[i] : b[i - na];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < G) ep_barrier_thread(flags, threadIdx.x, me, channel, epoch, limit_ns, status);
+}
 }  // namespace moe
 
 extern "C" int moe_ep_barrier(void* const* peer_flags, int G, int my_rank, int channel, int32_t epoch,
@@ -1125,6 +1151,26 @@ extern "C" int moe_ep_barrier(void* const* peer_flags, int G, int my_rank, int c
   ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pf, G, my_rank, channel, epoch,
                                                                           (unsigned long long)timeout_us * 1000ull, status);
   MOE_CHECK_LAUNCH("ep_barrier_kernel");
+  return MOE_OK;
+}
+
+extern "C" int moe_ep_share_counts(const int32_t* counts, int n_counts, const int32_t* extra, int n_extra,
+                                   void* const* peer_tables, int slot, void* const* peer_flags, int G, int my_rank,
+                                   int channel, int32_t epoch, int64_t timeout_us, int32_t* status, void* stream) {
+  using namespace moe;
+  if (!counts || !peer_tables || !peer_flags || (n_extra > 0 && !extra)) return fail(MOE_ERR_ARG, "ep_share_counts: null pointer");
+  if (G < 1 || G > 16 || my_rank < 0 || my_rank >= G || channel < 0 || channel >= 4 || timeout_us < 1 || slot < 0 || slot > 1 ||
+      n_counts < 1 || n_extra < 0)
+    return fail(MOE_ERR_ARG, "ep_share_counts: bad G=%d rank=%d channel=%d slot=%d n=%d+%d timeout_us=%lld", G, my_rank, channel,
+                slot, n_counts, n_extra, (long long)timeout_us);
+  PeerPtrs pt, pf;
+  for (int g = 0; g < 16; ++g) { pt.p[g] = g < G ? peer_tables[g] : nullptr; pf.p[g] = g < G ? peer_flags[g] : nullptr; }
+  for (int g = 0; g < G; ++g)
+    if (!pt.p[g] || !pf.p[g] || ((reinterpret_cast<uintptr_t>(pt.p[g]) | reinterpret_cast<uintptr_t>(pf.p[g])) & 3))
+      return fail(MOE_ERR_ARG, "ep_share_counts: table or flag row %d null or unaligned", g);
+  ep_share_counts_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      counts, n_counts, extra, n_extra, pt, slot, pf, G, my_rank, channel, epoch, (unsigned long long)timeout_us * 1000ull, status);
+  MOE_CHECK_LAUNCH("ep_share_counts_kernel");
   return MOE_OK;
 }
 

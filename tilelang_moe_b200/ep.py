@@ -204,7 +204,13 @@ class PeerExchange:
         self.barrier_timeout_us = int(os.environ.get("MOE_B200_EP_BARRIER_TIMEOUT_US", "2000000"))
         torch.cuda.synchronize(device)
         dist.barrier(group)                                                   # every rank's flags are zero before use
-        self.cnt_all = torch.empty(world, 0, dtype=torch.int32, device=device)
+        # the ranks' histograms travel over peer memory too: two tables [world, E + world] (step parity)
+        self.cnt_width = 0
+        self.cnt_sym = None
+        self.cnt_ptrs = None
+        self.step_parity = 0
+        self.group = group
+        self.world = world
         self.plan_bufs = {}
         self.side = torch.cuda.Stream(device=device)
         self.overlap = overlap
@@ -219,6 +225,26 @@ class PeerExchange:
             self.uniq_bufs = {}
 
 
+def _share_counts(px: "PeerExchange", ops, counts: torch.Tensor, extra: Optional[torch.Tensor]) -> torch.Tensor:
+    """All ranks' (counts, extra) vectors as an int32 [world, width] table on this device: one kernel that stores this
+    rank's row into every rank's table and runs the time-limited barrier (channel 3)."""
+    import torch.distributed._symmetric_memory as symm_mem
+    width = counts.numel() + (0 if extra is None else extra.numel())
+    if px.cnt_sym is None or px.cnt_width != width:      # first step of a shape: collective allocation
+        px.cnt_sym = symm_mem.empty(2 * px.world * width, dtype=torch.int32, device=px.device)
+        px.cnt_sym.zero_()
+        px.h_cnt = symm_mem.rendezvous(px.cnt_sym, px.group)
+        px.cnt_ptrs = ops._ptr_array(list(px.h_cnt.buffer_ptrs))
+        px.cnt_width = width
+        torch.cuda.synchronize(px.device)
+        dist.barrier(px.group)
+    px.step_parity ^= 1
+    px.epoch[3] += 1
+    ops.ep_share_counts(counts, extra, px.cnt_ptrs, px.step_parity, px.flag_ptrs, px.rank, 3, px.epoch[3],
+                        px.barrier_timeout_us)
+    return px.cnt_sym.view(2, px.world, width)[px.step_parity]
+
+
 def _barrier(px: "PeerExchange", ops, channel: int) -> None:
     """Enqueue barrier number epoch[channel] + 1 of `channel` on the current stream."""
     px.epoch[channel] += 1
@@ -231,7 +257,8 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
     """Expert-parallel forward with the exchange done by this library's own kernels over peer memory:
     the dispatch is a gather kernel that stores rows straight into the destination's expert-major
     buffer, the combine exchange is the down GEMM's epilogue storing into the owner's return buffer.
-    One small all-gather of histograms and two time-limited barriers per layer; no host synchronisation."""
+    The histograms are exchanged by a kernel over peer memory as well; three time-limited barriers per layer, no
+    collective-library call and no host synchronisation."""
     G, El, E = plan.world, plan.e_local, plan.n_experts
     Tl, H = x_local.shape
     rank = dist.get_rank(group)
@@ -243,16 +270,13 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
         if px.dedup:
             urank, ucount = ops.ep_unique(idx32, id_map_dev, El, G, out=px.uniq_bufs)
     with st("counts_allgather"):
-        width = E + G if px.dedup else E
-        if px.cnt_all.shape[1] != width:
-            px.cnt_all = torch.empty(G, width, dtype=torch.int32, device=x_local.device)
         if px.dedup:
-            dist.all_gather_into_tensor(px.cnt_all.view(-1), torch.cat([counts, ucount]), group=group)
-            offs_local, dst_base, ret_rank, ret_row, u_base = ops.ep_plan_dedup(px.cnt_all, G, El, rank, px.cap,
+            cnt_all = _share_counts(px, ops, counts, ucount)
+            offs_local, dst_base, ret_rank, ret_row, u_base = ops.ep_plan_dedup(cnt_all, G, El, rank, px.cap,
                                                                                 out=px.plan_bufs)
         else:
-            dist.all_gather_into_tensor(px.cnt_all.view(-1), counts, group=group)
-            offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(px.cnt_all, G, El, rank, px.cap, out=px.plan_bufs)
+            cnt_all = _share_counts(px, ops, counts, None)
+            offs_local, dst_base, ret_rank, ret_row = ops.ep_plan(cnt_all, G, El, rank, px.cap, out=px.plan_bufs)
     I = Wg.shape[1]
     act = _take(bufs, "act", px.cap, I, x_local)
     split = El // 2 if (px.overlap and El >= 2 and not px.dedup) else 0

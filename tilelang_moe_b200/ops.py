@@ -531,6 +531,22 @@ def ep_barrier(peer_flag_ptrs, rank: int, channel: int, epoch: int, device: torc
     _lib.check(rc, "moe_ep_barrier")
 
 
+def ep_share_counts(counts: torch.Tensor, extra: Optional[torch.Tensor], peer_table_ptrs, slot: int, peer_flag_ptrs,
+                    rank: int, channel: int, epoch: int, timeout_us: int = 1_000_000) -> None:
+    """Store this rank's histogram (counts, then extra) into row [slot][rank] of every rank's table over peer memory
+    and run the time-limited barrier behind it: an all-gather of a few hundred ints in one launch."""
+    _need_cuda(counts)
+    if counts.dtype != torch.int32 or not counts.is_contiguous():
+        raise ValueError("counts must be a contiguous int32 vector")
+    if extra is not None and (extra.dtype != torch.int32 or not extra.is_contiguous() or extra.device != counts.device):
+        raise ValueError("extra must be a contiguous int32 vector on the same device")
+    with torch.cuda.device(counts.device):
+        rc = _lib.load().moe_ep_share_counts(_ptr(counts), counts.numel(), _ptr(extra), 0 if extra is None else extra.numel(),
+                                             peer_table_ptrs, slot, peer_flag_ptrs, len(peer_flag_ptrs), rank, channel,
+                                             epoch, timeout_us, _ptr(status_buffer(counts.device)), _stream())
+    _lib.check(rc, "moe_ep_share_counts")
+
+
 def debug_wait_probe(device: torch.device, limit_us: int = 1000) -> int:
     """Run the bounded-wait self-test kernel; returns 1 if the wait succeeded (it cannot), 0 if it ran out."""
     outcome = torch.full((1,), -1, dtype=torch.int32, device=device)
