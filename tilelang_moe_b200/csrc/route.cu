@@ -177,11 +177,20 @@ route_small_kernel(const void* __restrict__ ids, int is64, int n, int E, const i
   for (int i = tid; i < 33 * E; i += 1024) sh[i] = 0;
   if (tid == 0) carry_s = 0;
   __syncthreads();
+  // a thread owns entries tid, tid + 1024, ...: at most RSMALL_MAX / 1024 of them, kept in registers for the
+  // permutation rounds below (the loads are independent, so they are all in flight together)
+  constexpr int ROUNDS = RSMALL_MAX / 1024;
+  int32_t ereg[ROUNDS];
   bool bad = false;
-  for (int i = tid; i < n; i += 1024) {
-    const int e = load_id(ids, is64, i, id_map, E, kx);
-    if (e >= 0) atomicAdd(&base[e], 1); else bad = true;
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) {
+    const int i = r * 1024 + tid;
+    ereg[r] = i < n ? load_id(ids, is64, i, id_map, E, kx) : -1;
+    if (i < n && ereg[r] < 0) bad = true;
   }
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r)
+    if (ereg[r] >= 0) atomicAdd(&base[ereg[r]], 1);
   if (bad && status) status[0] = ST_BAD_EXPERT_ID;
   __syncthreads();
   for (int b0 = 0; b0 < E; b0 += 1024) {          // exclusive scan, 1024 experts at a time
@@ -205,9 +214,11 @@ route_small_kernel(const void* __restrict__ ids, int is64, int n, int E, const i
   }
   if (tid == 0) offsets[E] = carry_s;
   if (!perm && !inv) return;
-  for (int r0 = 0; r0 < n; r0 += 1024) {
-    const int i = r0 + tid;
-    const int e = i < n ? load_id(ids, is64, i, id_map, E, kx) : -1;
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) {
+    if (r * 1024 >= n) break;
+    const int i = r * 1024 + tid;
+    const int e = ereg[r];
     const bool valid = e >= 0;
     const unsigned grp = __match_any_sync(0xFFFFFFFFu, valid ? (unsigned)e : (0x80000000u | (unsigned)lane));
     const int rank = __popc(grp & lt_mask);
@@ -348,25 +359,38 @@ router_logits_kernel(const uint4* __restrict__ x, const uint4* __restrict__ Wr, 
     float acc[EMAX];
 #pragma unroll
     for (int j = 0; j < EMAX; ++j) acc[j] = 0.f;
-    for (int v = lane; v < vec_per_row; v += 32) {
-      const uint4 xv = __ldg(xr + v);
-      const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xv);
-      float xf[8];
+    // the row is fetched eight vectors per lane at a time, all eight loads in flight before the first is used: a
+    // 4 KB row costs one memory round trip instead of eight in a row
+    for (int v0 = lane; v0 < vec_per_row; v0 += 256) {
+      uint4 xq[8];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack2<F16>(xu[j]);
-        xf[2 * j] = f.x; xf[2 * j + 1] = f.y;
+      for (int u = 0; u < 8; ++u) {
+        const int v = v0 + 32 * u;
+        xq[u] = v < vec_per_row ? __ldg(xr + v) : make_uint4(0u, 0u, 0u, 0u);
       }
 #pragma unroll
-      for (int j = 0; j < EMAX; ++j) {
-        if (j < E) {
-          const uint4 wv = wsh[j * vec_per_row + v];
-          const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+      for (int u = 0; u < 8; ++u) {
+        const int v = v0 + 32 * u;
+        if (v < vec_per_row) {
+          const uint32_t* xu = reinterpret_cast<const uint32_t*>(&xq[u]);
+          float xf[8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 f = unpack2<F16>(wu[q]);
-            acc[j] = fmaf(xf[2 * q], f.x, acc[j]);
-            acc[j] = fmaf(xf[2 * q + 1], f.y, acc[j]);
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack2<F16>(xu[j]);
+            xf[2 * j] = f.x; xf[2 * j + 1] = f.y;
+          }
+#pragma unroll
+          for (int j = 0; j < EMAX; ++j) {
+            if (j < E) {
+              const uint4 wv = wsh[j * vec_per_row + v];
+              const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wv);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float2 f = unpack2<F16>(wu[q]);
+                acc[j] = fmaf(xf[2 * q], f.x, acc[j]);
+                acc[j] = fmaf(xf[2 * q + 1], f.y, acc[j]);
+              }
+            }
           }
         }
       }
@@ -608,7 +632,7 @@ static int router_small(const void* x, const void* Wr, int64_t T, int H, int E, 
   if (rc) return rc;
   // one CTA per SM at most: every CTA stages the whole router weight
   const size_t smem = (size_t)E * H * 2;
-  int64_t blocks = ceil_div64(T, 16);
+  int64_t blocks = ceil_div64(T, 8);      // a token per warp while the SMs last
   if (blocks > dev.sm_count) blocks = dev.sm_count;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define MOE_RL_LAUNCH(F16_, EMAX_)                                                                                       \

@@ -422,6 +422,8 @@ class EPRunner:
         rc = self._routed_counts(logits_cpu)
         self.imbalance = self.plan.imbalance(rc)
         self.cost_imbalance = self.plan.imbalance(rc, cost=expert_cost)
+        naive = EPPlan(self.plan.n_experts, self.world, contiguous_placement(self.plan.n_experts, self.world))
+        self.contiguous_imbalance = (naive.imbalance(rc), naive.imbalance(rc, cost=expert_cost))   # experts in id order
         x_l = x_cpu[r * Tl:(r + 1) * Tl].contiguous()
         lg_l = logits_cpu[r * Tl:(r + 1) * Tl].contiguous()
         x, lg = x_l.to(dev), lg_l.to(dev)
