@@ -57,6 +57,26 @@ def test_signed_zero_and_nan_rule():
     assert i.tolist() == [[3, 2, 0, 1, 4, 5]]
 
 
+def test_selecting_on_logits_is_a_valid_selection_on_softmax_scores():
+    """The reference's convention A takes torch.topk of the fp32 softmax scores; the oracle and the kernels select on
+    the logits.  Softmax is monotone, so the two can differ only where distinct logits round to equal scores, and there
+    any of the tied experts is a top-k of the scores.  Checked beyond the fixtures: ordinary rows, rows quantised to
+    a few levels (many exact ties) and rows whose entries differ by single units in the last place."""
+    g = torch.Generator().manual_seed(11)
+    base = torch.randn(2000, 128, generator=g)
+    quant = (torch.randn(2000, 128, generator=g) * 2).round() / 2
+    near = 3.0 + torch.randint(0, 6, (2000, 128), generator=g).float() * 2.0 ** -21     # ulp-spaced around 3
+    for logits in (base, quant, near):
+        for k in (1, 6, 8):
+            ref_scores = torch.softmax(logits, dim=-1, dtype=torch.float32)
+            want, _ = torch.topk(ref_scores, k, dim=-1)
+            s, idx = O.topk_softmax(logits, k, "A")
+            got = torch.gather(ref_scores, 1, idx)
+            assert torch.equal(torch.sort(got, dim=-1, descending=True).values, want)
+            # and the scores reported are those values, to the tolerance of the contract
+            torch.testing.assert_close(torch.sort(s, dim=-1, descending=True).values, want, rtol=1e-6, atol=1e-30)
+
+
 def test_histogram_fixture():
     g = np.load(GOLDEN / "histogram.npz")
     idx = torch.from_numpy(g["topk_idx"].astype(np.int64))
