@@ -381,9 +381,11 @@ def run_ours(args, wl_name, cfg):
                "peer_dedup": "de-duplicated dispatch kernel (a token row per destination rank, gathered by the up GEMM) "
                              "+ down-GEMM epilogue over NVLink peer memory",
                "nccl": "NCCL all-to-all"}[args.exchange]
-        parallelism = f"ep{world}: {E // world} experts per GPU, tokens split {T // world} per rank, {how}"
+        per = runner.experts_per_rank
+        parallelism = (f"ep{world}: {min(per)}-{max(per)} experts per GPU (placed by row tiles of a calibration batch), "
+                       f"tokens split {T // world} per rank, {how}")
         imbalance = {"rows": runner.imbalance, "modelled_time": runner.cost_imbalance,
-                     "placement": "load-aware (rows of a calibration batch of the same popularity law), equal expert count per rank",
+                     "placement": "load-aware (row tiles of a calibration batch of the same popularity law; a rank may hold up to a quarter more experts than E / ranks)",
                      "contiguous_placement_would_give": {"rows": runner.contiguous_imbalance[0],
                                                          "modelled_time": runner.contiguous_imbalance[1]}}
 

@@ -27,6 +27,24 @@ def test_balanced_placement_properties():
         ep.EPPlan(8, 2, [0] * 8)
 
 
+def test_uneven_placement_gives_the_rank_of_a_hot_expert_fewer_experts():
+    load = [4000, 100, 100, 100, 100, 100, 100, 100]              # expert 0: 32 row tiles, the others 1 each
+    e2r = ep.balanced_placement(load, 2, cost=ep.tile_cost, max_per_rank=7)
+    plan = ep.EPPlan(8, 2, e2r, 7)
+    hot = e2r[0]
+    assert len(plan.local_experts[hot]) == 1 and len(plan.local_experts[1 - hot]) == 7
+    assert plan.e_local == 7 and plan.n_slots == 14 and len(plan.id_map) == 14
+    assert sorted(v for v in plan.id_map if v >= 0) == sorted([hot * 7] + [(1 - hot) * 7 + j for j in range(7)])
+    assert plan.id_map[8:] == [-1] * 6                             # ids past the real experts map to no slot
+    assert plan.padded_local_experts(hot) == [0] * 7
+    with pytest.raises(ValueError):
+        ep.balanced_placement(load, 2, max_per_rank=3)             # 2 x 3 slots cannot hold 8 experts
+    with pytest.raises(ValueError):
+        ep.EPPlan(8, 2, [0] * 8, 7)                                # more experts on a rank than it has slots
+    # every rank the same count when no slack is given, as before
+    assert sorted(ep.balanced_placement(load, 2).count(r) for r in range(2)) == [4, 4]
+
+
 def test_zipf_placement_reduces_imbalance():
     lg = inputs.zipf_logits(4096, 256, 1.1, seed=0)
     _, idx = O.topk_softmax(lg, 8, "A")
@@ -62,9 +80,16 @@ def _worker(rank, world, port, placement, q):
         logits = inputs.zipf_logits(T, E, 1.1, seed=1)
         _, idx = O.topk_softmax(logits, k, "A")
         load = O.route_histogram(idx, E)[0].tolist()
-        e2r = ep.balanced_placement(load, world) if placement == "balanced" else ep.contiguous_placement(E, world)
-        plan = ep.EPPlan(E, world, e2r)
-        mine = plan.local_experts[rank]
+        if placement == "tiles":     # by row tiles (of 8 rows here), a rank may hold more experts than E / world
+            cost = lambda rows: ep.tile_cost(rows, 8)
+            skewed = [v * 8 if v == max(load) else v for v in load]     # a calibration batch with one very popular expert
+            e2r = ep.balanced_placement(skewed, world, cost=cost, max_per_rank=E // world + 2)
+            plan = ep.EPPlan(E, world, e2r, E // world + 2)
+            assert len({len(l) for l in plan.local_experts}) > 1, "the case is meant to be uneven"
+        else:
+            e2r = ep.balanced_placement(load, world) if placement == "balanced" else ep.contiguous_placement(E, world)
+            plan = ep.EPPlan(E, world, e2r)
+        mine = plan.padded_local_experts(rank)
         Tl = T // world
         out = ep.ep_forward(x[rank * Tl:(rank + 1) * Tl], logits[rank * Tl:(rank + 1) * Tl], k, plan,
                             torch.tensor(plan.id_map, dtype=torch.int32), Wg[mine], Wu[mine], Wd[mine], cpu_ops)
@@ -76,7 +101,7 @@ def _worker(rank, world, port, placement, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,placement", [(2, "contiguous"), (2, "balanced"), (4, "balanced")])
+@pytest.mark.parametrize("world,placement", [(2, "contiguous"), (2, "balanced"), (4, "balanced"), (2, "tiles")])
 def test_ep_protocol_matches_single_process(world, placement):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -118,7 +143,7 @@ def _small_case(rank, world):
     Wd = torch.randn(E, H, I, generator=g) * 0.2
     logits = inputs.zipf_logits(T, E, 1.1, seed=1)
     plan = ep.EPPlan(E, world, ep.contiguous_placement(E, world))
-    mine = plan.local_experts[rank]
+    mine = plan.padded_local_experts(rank)
     Tl = T // world
     sl = slice(rank * Tl, (rank + 1) * Tl)
     return (x[sl], logits[sl], k, plan, torch.tensor(plan.id_map, dtype=torch.int32), Wg[mine], Wu[mine], Wd[mine])

@@ -38,9 +38,15 @@ def _worker(rank, world, port, placement, q, exchange="nccl"):
         logits = inputs.zipf_logits(T, E, 1.1, seed=1)
         _, idx = O.topk_softmax(logits, k, "A")
         load = O.route_histogram(idx, E)[0].tolist()
-        e2r = ep.balanced_placement(load, world) if placement == "balanced" else ep.contiguous_placement(E, world)
-        plan = ep.EPPlan(E, world, e2r)
-        mine = plan.local_experts[rank]
+        if placement == "tiles":     # by row tiles, ranks may hold different numbers of experts
+            skewed = [v * 6 if v == max(load) else v for v in load]
+            e2r = ep.balanced_placement(skewed, world, cost=ep.tile_cost, max_per_rank=E // world + 3)
+            plan = ep.EPPlan(E, world, e2r, E // world + 3)
+            assert len({len(l) for l in plan.local_experts}) > 1
+        else:
+            e2r = ep.balanced_placement(load, world) if placement == "balanced" else ep.contiguous_placement(E, world)
+            plan = ep.EPPlan(E, world, e2r)
+        mine = plan.padded_local_experts(rank)
         Tl = T // world
         sl = slice(rank * Tl, (rank + 1) * Tl)
         bufs = {}
@@ -62,7 +68,8 @@ def _worker(rank, world, port, placement, q, exchange="nccl"):
 
 @pytest.mark.parametrize("placement,exchange", [("contiguous", "nccl"), ("balanced", "nccl"), ("contiguous", "peer"),
                                                 ("balanced", "peer"), ("contiguous", "peer_dedup"),
-                                                ("balanced", "peer_dedup")])
+                                                ("balanced", "peer_dedup"), ("tiles", "peer_dedup"), ("tiles", "peer"),
+                                                ("tiles", "nccl")])
 def test_ep_two_gpus_match_oracle(lib, placement, exchange):
     _run_world(2, placement, exchange)
 
@@ -104,8 +111,9 @@ def _run_world(world, placement, exchange):
 
 
 @pytest.mark.parametrize("tile_rows,H,I", [("128", 128, 64), ("pair", 256, 128)])
-@pytest.mark.parametrize("G,dedup", [(4, True), (8, True), (8, False)])
-def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedup, tile_rows, H, I, monkeypatch):
+@pytest.mark.parametrize("G,dedup,uneven", [(4, True, False), (8, True, False), (8, False, False), (8, True, True),
+                                            (4, False, True)])
+def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedup, uneven, tile_rows, H, I, monkeypatch):
     """The peer-exchange kernels for G ranks run one after another on a single GPU: every "rank" has its own receive,
     index and return buffers on that device, the all-gather is a torch.stack, and no barrier is needed because the
     phases are issued in order on one stream.  Checks the whole path (unique / plan / dispatch / gathered up GEMM /
@@ -114,8 +122,8 @@ def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedu
     from tilelang_moe_b200 import ep, inputs, ops
     monkeypatch.setenv("MOE_B200_GEMM_TILE_ROWS", tile_rows)   # single-CTA kernel, or the CTA-pair kernel's peer epilogue
     dev = cuda
-    El, k, Tl = 4, 4, 96
-    E, T = G * El, G * 96
+    k, Tl = 4, 96
+    E, T = G * 4, G * 96
     g = torch.Generator().manual_seed(G)
     x = torch.randn(T, H, generator=g).bfloat16()
     Wg = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16()
@@ -123,7 +131,14 @@ def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedu
     Wd = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16()
     logits = inputs.zipf_logits(T, E, 1.1, seed=G)
     _, idx = O.topk_softmax(logits, k, "A")
-    plan = ep.EPPlan(E, G, ep.balanced_placement(O.route_histogram(idx, E)[0].tolist(), G))
+    load = O.route_histogram(idx, E)[0].tolist()
+    if uneven:   # placed by row tiles with two spare slots per rank: ranks hold different numbers of experts
+        cost = lambda rows: ep.tile_cost(rows, 32)
+        plan = ep.EPPlan(E, G, ep.balanced_placement(load, G, cost=cost, max_per_rank=6), 6)
+        assert len({len(l) for l in plan.local_experts}) > 1
+    else:
+        plan = ep.EPPlan(E, G, ep.balanced_placement(load, G))
+    El, NS = plan.e_local, plan.n_slots          # expert slots per rank, histogram bins
     id_map = torch.tensor(plan.id_map, dtype=torch.int32, device=dev)
     cap = Tl * k * G
     recv = [torch.zeros(cap, H, dtype=torch.bfloat16, device=dev) for _ in range(G)]
@@ -136,7 +151,7 @@ def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedu
     for s in range(G):                                               # route on every rank
         sl = slice(s * Tl, (s + 1) * Tl)
         scores, idx32 = ops.topk_softmax(logits[sl].to(dev), k, mode="A", index_dtype=torch.int32)
-        counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map)
+        counts, offsets, perm, inv = ops.route_histogram(idx32, NS, id_map=id_map)
         urank, ucount = ops.ep_unique(idx32, id_map, El, G) if dedup else (None, None)
         routed.append(dict(x=x[sl].to(dev), scores=scores, idx32=idx32, counts=counts, offsets=offsets, perm=perm, inv=inv,
                            urank=urank, ucount=ucount))
@@ -154,7 +169,7 @@ def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedu
         plans.append((offs_local, ret_rank, ret_row))
     for d in range(G):                                               # expert GEMMs on every rank
         offs_local, ret_rank, ret_row = plans[d]
-        mine = plan.local_experts[d]
+        mine = plan.padded_local_experts(d)
         wg, wu, wd = Wg[mine].to(dev), Wu[mine].to(dev), Wd[mine].to(dev)
         if dedup:
             act = ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, recv[d], wg, offs_local, B2=wu, gather=gidx[d], gather_div=1)
@@ -168,7 +183,7 @@ def test_peer_exchange_kernels_with_emulated_ranks_on_one_gpu(cuda, lib, G, dedu
         torch.testing.assert_close(out.float().cpu(), ref[s * Tl:(s + 1) * Tl], rtol=1e-2, atol=2e-2)
     ops.check_status(dev)
     if dedup:   # fewer rows travelled than routed entries, and never more than one per (token, rank)
-        sent = int(cnt_all[:, E:].sum())
+        sent = int(cnt_all[:, NS:].sum())
         assert sent <= T * min(k, G) and sent < T * k
 
 

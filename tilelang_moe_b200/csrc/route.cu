@@ -927,7 +927,10 @@ ep_unique_kernel(const int32_t* __restrict__ topk_idx, const int32_t* __restrict
     if (t < Tl)
       for (int s = 0; s < k; ++s) {
         const int32_t id = topk_idx[t * k + s];
-        if ((uint32_t)id < (uint32_t)(G * El)) mask |= 1u << (id_map[id] / El);   // ids out of range travel nowhere
+        if ((uint32_t)id < (uint32_t)(G * El)) {            // ids out of range, or mapped to no slot, travel nowhere
+          const int v = id_map[id];
+          if (v >= 0) mask |= 1u << (v / El);
+        }
       }
     int32_t in_warp[16];
 #pragma unroll

@@ -47,14 +47,24 @@ def expert_cost(rows: float, tile_rows: int = 128, stream_tiles: float = 1.6) ->
     return max(stream_tiles, float(-(-int(rows) // tile_rows)))
 
 
-def balanced_placement(load: Sequence[float], world: int, cost=None) -> List[int]:
-    """Greedy longest-processing-time assignment with exactly E/world experts per rank:
-    costliest expert first, to the least loaded rank that still has a free slot.
-    ``load`` is rows per expert; ``cost`` maps rows to time (default: rows themselves)."""
+def tile_cost(rows: float, tile_rows: int = 128) -> float:
+    """Row tiles an expert occupies in the grouped GEMMs.  A tile takes about the same time whether its expert is
+    large (tensor bound) or owns that one tile only (its weights stream from HBM meanwhile), so tiles are what a rank's
+    GEMM time is proportional to; an expert without rows costs nothing."""
+    return 0.0 if rows <= 0 else float(-(-int(rows) // tile_rows))
+
+
+def balanced_placement(load: Sequence[float], world: int, cost=None, max_per_rank: Optional[int] = None) -> List[int]:
+    """Greedy longest-processing-time assignment: costliest expert first, to the least loaded rank that still has a
+    free slot.  ``load`` is rows per expert; ``cost`` maps rows to time (default: rows themselves).  With
+    ``max_per_rank`` = E/world (the default) every rank ends up with exactly E/world experts; a larger value lets the
+    rank that holds a very popular expert take fewer of the others (see EPPlan's ``e_slots``)."""
     if cost is not None:
         load = [cost(v) for v in load]
     E = len(load)
-    per = E // world
+    per = E // world if max_per_rank is None else max_per_rank
+    if per * world < E:
+        raise ValueError(f"{world} ranks with at most {per} experts each cannot hold {E} experts")
     order = sorted(range(E), key=lambda e: (-float(load[e]), e))
     tot = [0.0] * world
     cnt = [0] * world
@@ -69,26 +79,41 @@ def balanced_placement(load: Sequence[float], world: int, cost=None) -> List[int
 
 @dataclass
 class EPPlan:
-    """Static sharding of E experts over `world` ranks."""
+    """Static sharding of E experts over `world` ranks.
+
+    Every rank has ``e_local`` expert slots (``e_slots`` if given, else E / world); a rank may hold fewer experts than
+    slots, and the unused slots simply never receive rows.  The kernels number experts by slot, rank-major:
+    ``n_slots = world * e_local`` histogram bins, ``id_map[e] = rank * e_local + slot``; entries of ``id_map`` past the
+    real experts are -1, which the histogram reports as an id out of range."""
     n_experts: int
     world: int
     expert_to_rank: List[int]
+    e_slots: Optional[int] = None
     local_experts: List[List[int]] = field(init=False)   # per rank: global ids in local slot order
-    id_map: List[int] = field(init=False)                 # global id -> rank * E_local + slot
+    id_map: List[int] = field(init=False)                 # global id -> rank * e_local + slot
 
     def __post_init__(self):
         E, G = self.n_experts, self.world
-        if E % G:
+        if self.e_slots is None and E % G:
             raise ValueError(f"{E} experts do not split evenly over {G} ranks")
-        self.e_local = E // G
+        self.e_local = E // G if self.e_slots is None else int(self.e_slots)
+        self.n_slots = G * self.e_local
         self.local_experts = [[] for _ in range(G)]
-        self.id_map = [0] * E
+        self.id_map = [-1] * max(E, self.n_slots)
         for e in range(E):
             r = self.expert_to_rank[e]
             self.id_map[e] = r * self.e_local + len(self.local_experts[r])
             self.local_experts[r].append(e)
-        if any(len(l) != self.e_local for l in self.local_experts):
-            raise ValueError("placement must give every rank the same number of experts")
+        if any(len(l) > self.e_local for l in self.local_experts):
+            raise ValueError(f"placement gives a rank more experts than its {self.e_local} slots")
+
+    def padded_local_experts(self, rank: int) -> List[int]:
+        """The rank's experts followed by repeats of its first one up to e_local entries: what to stack as the
+        rank's weight tensors (the padding slots never receive rows, their weights are never read)."""
+        mine = self.local_experts[rank]
+        if not mine:
+            raise ValueError(f"rank {rank} holds no expert")
+        return mine + [mine[0]] * (self.e_local - len(mine))
 
     def imbalance(self, counts_per_expert: Sequence[float], cost=None) -> float:
         """max over ranks / mean over ranks of routed rows (or of cost(rows)) under this placement."""
@@ -127,7 +152,7 @@ def ep_forward(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, plan: 
     x_local bf16 [T_local,H]; logits_local fp32 [T_local,E]; Wg/Wu [E_local,I,H], Wd [E_local,H,I]
     for this rank's experts in slot order.  Returns out bf16 [T_local,H].
     """
-    G, El, E = plan.world, plan.e_local, plan.n_experts
+    G, El, E = plan.world, plan.e_local, plan.n_slots
     Tl, H = x_local.shape
     n = Tl * k
     st = stage if stage is not None else (lambda name: _null)
@@ -259,7 +284,7 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
     buffer, the combine exchange is the down GEMM's epilogue storing into the owner's return buffer.
     The histograms are exchanged by a kernel over peer memory as well; three time-limited barriers per layer, no
     collective-library call and no host synchronisation."""
-    G, El, E = plan.world, plan.e_local, plan.n_experts
+    G, El, E = plan.world, plan.e_local, plan.n_slots
     Tl, H = x_local.shape
     rank = dist.get_rank(group)
     st = stage if stage is not None else (lambda name: _null)
@@ -376,16 +401,24 @@ class EPRunner:
         # placement from the expert loads of a calibration batch with the same popularity law
         # (a different noise draw than the timed batch): what a serving system knows in advance
         load = self._calibration_load(cfg, calib_seed)
-        if placement == "balanced":      # by routed rows
+        e_slots = None
+        if placement == "balanced":
+            # by row tiles, and a rank may hold up to a quarter more experts than E / world: the rank of a very popular
+            # expert then takes fewer of the others instead of running one wave of tiles longer than everybody else
+            e_slots = E // world + max(1, E // world // 4)
+            e2r = balanced_placement(load, world, cost=tile_cost, max_per_rank=e_slots)
+        elif placement == "rows":        # by routed rows, exactly E / world experts per rank
             e2r = balanced_placement(load, world)
-        elif placement == "time":        # by modelled time; with a fixed expert count per rank it cannot beat "balanced":
-            e2r = balanced_placement(load, world, cost=expert_cost)   # the rank of the hottest expert still holds 31 others
+        elif placement == "time":        # by modelled time, exactly E / world experts per rank
+            e2r = balanced_placement(load, world, cost=expert_cost)
         else:
             e2r = contiguous_placement(E, world)
-        self.plan = EPPlan(E, world, e2r)
+        self.plan = EPPlan(E, world, e2r, e_slots)
+        if e_slots is not None:          # no more slots than the fullest rank uses
+            self.plan = EPPlan(E, world, e2r, max(len(l) for l in self.plan.local_experts))
         self.id_map_dev = torch.tensor(self.plan.id_map, dtype=torch.int32, device=device)
-        self.Wg, self.Wu, self.Wd = make_weights(cfg, device, experts=self.plan.local_experts[rank])
-        need = _lib.load().moe_route_histogram_workspace(self.Tl * k, E)
+        self.Wg, self.Wu, self.Wd = make_weights(cfg, device, experts=self.plan.padded_local_experts(rank))
+        need = _lib.load().moe_route_histogram_workspace(self.Tl * k, self.plan.n_slots)
         self.bufs = {"hist_ws": torch.empty(max(need, 4), dtype=torch.uint8, device=device)}
         self.imbalance = None
         self.exchange = exchange
@@ -421,9 +454,10 @@ class EPRunner:
         Tl, r, dev = self.Tl, self.rank, self.dev
         rc = self._routed_counts(logits_cpu)
         self.imbalance = self.plan.imbalance(rc)
-        self.cost_imbalance = self.plan.imbalance(rc, cost=expert_cost)
+        self.cost_imbalance = self.plan.imbalance(rc, cost=tile_cost)
         naive = EPPlan(self.plan.n_experts, self.world, contiguous_placement(self.plan.n_experts, self.world))
-        self.contiguous_imbalance = (naive.imbalance(rc), naive.imbalance(rc, cost=expert_cost))   # experts in id order
+        self.contiguous_imbalance = (naive.imbalance(rc), naive.imbalance(rc, cost=tile_cost))   # experts in id order
+        self.experts_per_rank = [len(l) for l in self.plan.local_experts]
         x_l = x_cpu[r * Tl:(r + 1) * Tl].contiguous()
         lg_l = logits_cpu[r * Tl:(r + 1) * Tl].contiguous()
         x, lg = x_l.to(dev), lg_l.to(dev)
