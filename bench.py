@@ -1114,13 +1114,73 @@ def run_mhc(args):
                       "parity_ok": all(r["parity_ok"] for r in results), "results": results}), flush=True)
 
 
+def run_ep_ranks(args):
+    """What each rank's two expert GEMMs cost at G-way expert parallelism (--gpus G, run on ONE GPU): for every placement
+    rule and every rank, the up + down GEMM over that rank's experts and the rows the c5 batch sends them, weights
+    random.  All (placement, rank) cases are interleaved over several rounds so that clock drift hits them alike; the
+    slowest rank of a placement is what the other ranks wait for at the return barrier."""
+    import random
+    from oracle import moe_oracle as O
+    from tilelang_moe_b200 import ep, inputs, ops
+    dev = torch.device("cuda", 0)
+    cfg = WORKLOADS["c5"]
+    T, E, k, H, I = (cfg[n] for n in ("T", "E", "k", "H", "I"))
+    G = max(args.gpus, 2)
+    cnt = torch.bincount(O.topk_softmax(inputs.zipf_logits(T, E, 1.1, seed=0), k, "A")[1].reshape(-1), minlength=E).tolist()
+    calib = inputs.zipf_logits(T, E, 1.1, seed=0, noise_seed=1001)
+    load = torch.bincount(O.topk_softmax(calib, k, "A")[1].reshape(-1), minlength=E).tolist()
+    per = E // G
+    slots = per + max(1, per // 4)
+    plans = {"contiguous": ep.EPPlan(E, G, ep.contiguous_placement(E, G)),
+             "rows, E/G experts per rank": ep.EPPlan(E, G, ep.balanced_placement(load, G))}
+    for name, cost in (("row tiles, spare slots (default)", ep.tile_cost), ("time model, spare slots", ep.expert_cost)):
+        e2r = ep.balanced_placement(load, G, cost=cost, max_per_rank=slots)
+        plans[name] = ep.EPPlan(E, G, e2r, max(e2r.count(r) for r in range(G)))
+    EL = max(p.e_local for p in plans.values())
+    Wg = torch.randn(EL, I, H, device=dev, dtype=torch.bfloat16) * 0.02
+    Wu = torch.randn(EL, I, H, device=dev, dtype=torch.bfloat16) * 0.02
+    Wd = torch.randn(EL, H, I, device=dev, dtype=torch.bfloat16) * 0.02
+    cap = max(sum(cnt[e] for e in l) for p in plans.values() for l in p.local_experts)
+    A = torch.randn(cap, H, device=dev, dtype=torch.bfloat16)
+    act = torch.empty(cap, I, device=dev, dtype=torch.bfloat16)
+    y = torch.empty(cap, H, device=dev, dtype=torch.bfloat16)
+    cases = {}
+    for name, plan in plans.items():
+        for r in range(G):
+            rows = [cnt[e] for e in plan.local_experts[r]] + [0] * (plan.e_local - len(plan.local_experts[r]))
+            offs = torch.tensor([0] + torch.tensor(rows).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+            cases[(name, r)] = (offs, plan.e_local, sum(rows), sum(-(-v // 128) for v in rows), len(plan.local_experts[r]))
+    res = {c: [] for c in cases}
+    keys = list(cases)
+    for rnd in range(args.steps // 4 + 2):
+        random.Random(rnd).shuffle(keys)
+        for c in keys:
+            offs, El, n, _, _ = cases[c]
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            ops.grouped_gemm_sorted(ops.GEMM_SILU_GATE, A[:n], Wg[:El], offs, B2=Wu[:El], out=act[:n])
+            ops.grouped_gemm_sorted(ops.GEMM_PLAIN, act[:n], Wd[:El], offs, out=y[:n])
+            b.record()
+            torch.cuda.synchronize()
+            if rnd > 0:
+                res[c].append(a.elapsed_time(b))
+    ops.check_status(dev)
+    out = {"workload": f"up + down expert GEMM of every rank at {G}-way expert parallelism, emulated on one GPU", "placements": {}}
+    for name in plans:
+        ms = [round(statistics.median(res[(name, r)]), 3) for r in range(G)]
+        out["placements"][name] = {"ms_max": max(ms), "ms_mean": round(sum(ms) / G, 3), "ms_by_rank": ms,
+                                   "row_tiles_by_rank": [cases[(name, r)][3] for r in range(G)],
+                                   "experts_by_rank": [cases[(name, r)][4] for r in range(G)]}
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["c2", "router", "gemm_grid", "mhc"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["c2", "router", "gemm_grid", "mhc", "ep_ranks"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="c5: skip the router / c2 / c3 blocks of the line")
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled-token check against the CPU oracle")
@@ -1136,6 +1196,8 @@ def main():
         return run_router(args)
     if args.workload == "gemm_grid":
         return run_gemm_grid(args)
+    if args.workload == "ep_ranks":
+        return run_ep_ranks(args)
     if args.workload == "mhc":
         return run_mhc(args)
     if args.workload == "c2":
