@@ -20,6 +20,7 @@ namespace moe {
 constexpr int RUNIT = 1024;        // entries per warp (large inputs)
 constexpr int RUNIT_SMALL = 128;   // entries per warp when the whole input is small: more warps, shorter serial walks
 constexpr int64_t RSMALL_MAX = 16384;
+constexpr int64_t RSINGLE_MAX = 4096;    // up to here (half of it with many experts) one CTA does the whole stage in one launch
 constexpr int RWPB = 8;            // warps per CTA in the count / scatter kernels
 
 // Expert id of flat entry i; with an id_map (int32 [E]) the id is translated, e.g. to the
@@ -541,7 +542,17 @@ int moe::route_histogram_ex(const void* topk_idx, int idx_is_int64, int64_t n, i
   if (need > 0 && (!ws || ws_bytes < need)) return fail(MOE_ERR_WORKSPACE, "route_histogram: workspace %zu < %zu", ws_bytes, need);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const bool small = n <= RSMALL_MAX;
-  if (small && n > 0 && E <= 1024) {   // one CTA, one launch
+  // MOE_B200_ROUTE_SINGLE_MAX moves the size up to which one CTA does the whole stage (for measurements; at most RSMALL_MAX)
+  static const int64_t single_max = [] {
+    const char* v = getenv("MOE_B200_ROUTE_SINGLE_MAX");
+    const int64_t m = v ? atoll(v) : RSINGLE_MAX;
+    return m < RSMALL_MAX ? m : RSMALL_MAX;
+  }();
+  // measured inside a CUDA graph (us, one CTA / three kernels): E = 256: n = 2048 8.9 / 7.0, 4096 14.2 / 8.4, 16384
+  // 45.6 / 13.6; E = 9: 3072 7.4 / 7.3, 4096 8.7 / 7.8, 16384 23.9 / 14.2.  One launch instead of three is worth
+  // a few microseconds of host time outside a graph, so the single CTA keeps the smallest inputs only.
+  const bool single = n <= single_max && (n <= RSINGLE_MAX / 2 || E <= 64);
+  if (single && n > 0 && E <= 1024) {   // one CTA, one launch
     const size_t smem1 = (size_t)33 * E * 4;
     if (smem1 > 48 * 1024)
       MOE_CUDA_CHECK(cudaFuncSetAttribute(route_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
