@@ -19,7 +19,13 @@ namespace moe {
 // ------------------------------------------------------------------------------------
 constexpr int RUNIT = 1024;        // entries per warp (large inputs)
 constexpr int RUNIT_SMALL = 128;   // entries per warp when the whole input is small: more warps, shorter serial walks
-constexpr int64_t RSMALL_MAX = 16384;
+constexpr int64_t RSMALL_MAX = 65536;    // up to here the three kernels cut the list into the small units (one warp each) ...
+constexpr int64_t RSMALL_TABLE = 131072; // ... as long as the units x experts table the scan kernel walks stays this small
+// measured inside a CUDA graph, E = 256 (us, small / large units): n = 32768 18 / 36, 65536 30 / ~45; beyond that the
+// table walk of the scan kernel outweighs the extra warps (n = 262144: 90 with small units, 524288: 57 with large)
+__host__ __device__ inline bool route_small_units(int64_t n, int E) {
+  return n <= RSMALL_MAX && ((n + RUNIT_SMALL - 1) / RUNIT_SMALL) * (int64_t)E <= RSMALL_TABLE;
+}
 constexpr int64_t RSINGLE_MAX = 4096;    // up to here (half of it with many experts) one CTA does the whole stage in one launch
 constexpr int RWPB = 8;            // warps per CTA in the count / scatter kernels
 
@@ -82,16 +88,33 @@ route_scan_kernel(int32_t* __restrict__ unit_counts, int64_t n_units, int E, int
                   int32_t* __restrict__ offsets) {
   __shared__ int32_t warp_tot[32];
   __shared__ int32_t carry_s;
+  __shared__ int32_t part[1024];     // [P][Ec]: entries of expert e in the p-th share of the units
   const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
   if (tid == 0) carry_s = 0;
   __syncthreads();
+  // Up to 1024 experts at a time, consecutive lanes on consecutive experts (coalesced rows of the table); with fewer
+  // experts than threads, P threads share an expert's column, each walking a contiguous share of the units
+  const int Ec = E >= 1024 ? 1024 : ((E + 31) & ~31);
+  const int P = 1024 / Ec;
+  const int p = tid / Ec, el = tid - p * Ec;
+  const int64_t u_lo = n_units * p / P, u_hi = n_units * (p + 1) / P;
   for (int base = 0; base < E; base += 1024) {
-    const int e = base + tid;
-    int32_t total = 0;
-    if (e < E)
-      for (int64_t u = 0; u < n_units; ++u) total += unit_counts[u * E + e];
-    // exclusive scan of `total` over this chunk of experts
-    int32_t inc = total;
+    const int e = base + el;
+    int32_t mine = 0;
+    if (e < E && p < P)
+      for (int64_t u = u_lo; u < u_hi; ++u) mine += unit_counts[u * E + e];
+    if (p < P) part[p * Ec + el] = mine;
+    __syncthreads();
+    int32_t total = 0, ahead = 0;        // whole column; entries in the shares before this thread's
+    if (p < P)
+      for (int q = 0; q < P; ++q) {
+        const int32_t v = part[q * Ec + el];
+        total += v;
+        if (q < p) ahead += v;
+      }
+    // exclusive scan of the column totals over this chunk of experts: threads 0 .. Ec-1 carry them, the rest zero
+    const int32_t mine_tot = p == 0 ? total : 0;
+    int32_t inc = mine_tot;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int32_t v = __shfl_up_sync(0xFFFFFFFFu, inc, o);
@@ -101,18 +124,18 @@ route_scan_kernel(int32_t* __restrict__ unit_counts, int64_t n_units, int E, int
     __syncthreads();
     int32_t before = carry_s;
     for (int w2 = 0; w2 < wid; ++w2) before += warp_tot[w2];
-    const int32_t start = before + inc - total;
-    if (e < E) {
-      counts[e] = total;
-      offsets[e] = start;
-      int32_t run = start;
-      for (int64_t u = 0; u < n_units; ++u) {
+    const int32_t start = before + inc - mine_tot;
+    if (p == 0) part[el] = start;        // row 0 is free again: every thread has read what it needed
+    if (p == 0 && e < E) { counts[e] = total; offsets[e] = start; }
+    __syncthreads();
+    if (e < E && p < P) {
+      int32_t run = part[el] + ahead;
+      for (int64_t u = u_lo; u < u_hi; ++u) {
         const int32_t c = unit_counts[u * E + e];
         unit_counts[u * E + e] = run;
         run += c;
       }
     }
-    __syncthreads();
     if (tid == 1023) carry_s = before + inc;
     __syncthreads();
   }
@@ -159,7 +182,7 @@ route_scatter_kernel(const void* __restrict__ ids, int is64, int64_t n, int E, c
   }
 }
 
-// Small inputs (n <= RSMALL_MAX): the whole stage in one CTA and one launch.  Counts by shared-memory atomics, an
+// Small inputs (n <= RSINGLE_MAX): the whole stage in one CTA and one launch.  Counts by shared-memory atomics, an
 // exclusive scan over the experts, then the stable permutation in rounds of 1024 consecutive entries: inside a
 // round an entry's place is its expert's running start + the entries of that expert in earlier warps of the round
 // (one count per warp and expert, written by the first lane of each match group) + its rank among equal ids of
@@ -178,9 +201,9 @@ route_small_kernel(const void* __restrict__ ids, int is64, int n, int E, const i
   for (int i = tid; i < 33 * E; i += 1024) sh[i] = 0;
   if (tid == 0) carry_s = 0;
   __syncthreads();
-  // a thread owns entries tid, tid + 1024, ...: at most RSMALL_MAX / 1024 of them, kept in registers for the
+  // a thread owns entries tid, tid + 1024, ...: at most RSINGLE_MAX / 1024 of them, kept in registers for the
   // permutation rounds below (the loads are independent, so they are all in flight together)
-  constexpr int ROUNDS = RSMALL_MAX / 1024;
+  constexpr int ROUNDS = RSINGLE_MAX / 1024;
   int32_t ereg[ROUNDS];
   bool bad = false;
 #pragma unroll
@@ -516,7 +539,7 @@ ep_regroup_kernel(const int32_t* __restrict__ cnt, int G, int El, int32_t* __res
 // ====================================================================================
 extern "C" size_t moe_route_histogram_workspace(int64_t n, int E) {
   if (n <= 0 || E <= 0) return 0;
-  const int64_t units = moe::ceil_div64(n, n <= moe::RSMALL_MAX ? moe::RUNIT_SMALL : moe::RUNIT);
+  const int64_t units = moe::ceil_div64(n, moe::route_small_units(n, E) ? moe::RUNIT_SMALL : moe::RUNIT);
   return (size_t)units * (size_t)E * sizeof(int32_t);
 }
 
@@ -541,12 +564,12 @@ int moe::route_histogram_ex(const void* topk_idx, int idx_is_int64, int64_t n, i
   const size_t need = moe_route_histogram_workspace(n, E);
   if (need > 0 && (!ws || ws_bytes < need)) return fail(MOE_ERR_WORKSPACE, "route_histogram: workspace %zu < %zu", ws_bytes, need);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const bool small = n <= RSMALL_MAX;
+  const bool small = route_small_units(n, E);
   // MOE_B200_ROUTE_SINGLE_MAX moves the size up to which one CTA does the whole stage (for measurements; at most RSMALL_MAX)
   static const int64_t single_max = [] {
     const char* v = getenv("MOE_B200_ROUTE_SINGLE_MAX");
     const int64_t m = v ? atoll(v) : RSINGLE_MAX;
-    return m < RSMALL_MAX ? m : RSMALL_MAX;
+    return m < RSINGLE_MAX ? m : RSINGLE_MAX;
   }();
   // measured inside a CUDA graph (us, one CTA / three kernels): E = 256: n = 2048 8.9 / 7.0, 4096 14.2 / 8.4, 16384
   // 45.6 / 13.6; E = 9: 3072 7.4 / 7.3, 4096 8.7 / 7.8, 16384 23.9 / 14.2.  One launch instead of three is worth
