@@ -33,7 +33,9 @@ def test_version_and_error_channel(lib):
     rc = lib.moe_route_histogram(None, 1, 10, 4, None, None, None, None, None, None, 0, None, None)
     assert rc == -1
     assert lib.moe_route_histogram_workspace(2048, 8) == 16 * 8 * 4          # small inputs: units of 128 ids
-    assert lib.moe_route_histogram_workspace(65536, 256) == 64 * 256 * 4     # large inputs: units of 1024 ids
+    assert lib.moe_route_histogram_workspace(65536, 256) == 512 * 256 * 4    # ... up to 65536 ids while the table stays small
+    assert lib.moe_route_histogram_workspace(65536, 1024) == 64 * 1024 * 4   # many experts: units of 1024 ids
+    assert lib.moe_route_histogram_workspace(1 << 20, 256) == 1024 * 256 * 4 # large inputs: units of 1024 ids
     assert lib.moe_route_histogram_workspace(0, 8) == 0
 
 
