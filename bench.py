@@ -334,7 +334,13 @@ def run_ours(args, wl_name, cfg):
             x.copy_(x_pin, non_blocking=True)
             out_pin.copy_(step(), non_blocking=True)
 
-        launches_per_step = 10 if H % 64 == 0 else 11   # router GEMV, topk, 3 x histogram, [gather,] up, down, shared up, shared down, combine
+        # kernels per layer.  Shared expert of the routed width and H % 64 == 0 (this workload): router GEMV with its
+        # top-k, histogram (one kernel for n <= 4096 entries with few experts, else three), up GEMM (gathers its rows,
+        # shared expert as one more group), down GEMM, combine.  Otherwise: + row gather, + shared up and shared down.
+        n1 = T * (k + S)
+        hist = 1 if (n1 <= 2048 or (n1 <= 4096 and E + S <= 64)) else 3
+        ride = S == 1 and H % 64 == 0
+        launches_per_step = 1 + hist + 2 + 1 + (0 if ride else (2 * (S > 0) + (H % 64 != 0)))
         tokens_per_step = T
         h2d, d2h = x_pin.numel() * 2, out_pin.numel() * 2
         parallelism = "1 GPU" + (", whole layer replayed as one CUDA graph" if args.graph else ", eager launches")

@@ -484,5 +484,6 @@ class EPRunner:
         # kernels of this library per step: topk, 3 x histogram, gather, regroup, gather, up, down, combine
         h2d = (x_pin.numel() * 2 + lg_pin.numel() * 4) * self.world
         d2h = out_pin.numel() * 2 * self.world
-        # peer exchange: topk, 3 x histogram, plan, dispatch, up, down(+scatter), combine
-        return step, step_e2e, ((10 if self.px.dedup else 9) if self.px is not None else 10), h2d, d2h
+        # peer exchange: topk, 3 x histogram, [unique,] histogram exchange, plan, dispatch, barrier, up, down (+ scatter),
+        # barrier, combine; NCCL variant: topk, 3 x histogram, gather, regroup, gather, up, down, combine
+        return step, step_e2e, ((13 if self.px.dedup else 12) if self.px is not None else 10), h2d, d2h
