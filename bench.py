@@ -776,7 +776,9 @@ def c3_block(dev, flush=None):
     flops = 2.0 * T * H * E + (T * k + T * S) * 6.0 * H * I
     row = {"us_eager": round(us_eager, 2), "us_graph": round(us_graph, 2), "tokens_per_s_graph": round(T / us_graph * 1e6),
            "TFLOPs_graph": round(flops / us_graph / 1e6, 1),
-           "l2": "56 MB of weights stay in L2 between calls (warm); the *_l2_flushed figures follow a 256 MB write"}
+           "l2": "56 MB of weights stay in L2 between calls (warm); the *_l2_flushed figures follow a 256 MB write",
+           "how": "median of single calls, each between two events with a synchronise after it: us_eager includes the host's "
+                  "launch time of one call, which back-to-back calls (--workload c3) hide"}
     if flush is not None:
         row["us_eager_l2_flushed"] = round(_event_us(fwd, 30, flush), 2)
         row["us_graph_l2_flushed"] = round(_event_us(replay, 30, flush), 2)
