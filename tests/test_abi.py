@@ -45,3 +45,24 @@ def test_cpu_tensors_are_rejected():
     from tilelang_moe_b200 import kernels
     with pytest.raises(ValueError):
         kernels.topk_softmax(torch.randn(4, 8), 2)
+
+
+def test_every_public_name_of_the_reference_package_exists():
+    """The names the reference's kernels/__init__.py exports (its __all__, :67-101): code written against any of them
+    must find it here."""
+    import tilelang_moe_b200.kernels as K
+    reference_all = [
+        "topk_radix_tilelang", "topk_softmax_separate", "topk_softmax_separate_compiled", "topk_softmax_fused",
+        "topk_softmax_selection", "topk_softmax_sonic", "topk_softmax_bitonic", "topk_softmax_tilelang_separate",
+        "topk_softmax_best", "topk_softmax",
+        "grouped_gemm_loop", "grouped_gemm_loop_compiled", "grouped_gemm_padded", "grouped_gemm_tilelang",
+        "grouped_gemm_pytorch", "grouped_gemm_best", "grouped_gemm",
+        "mhc_pre_pytorch", "mhc_pre_pytorch_compiled", "mhc_post_pytorch", "mhc_post_pytorch_compiled",
+        "mhc_pre_tilelang_official", "mhc_pre_tilelang_optimized", "mhc_pre_tilelang_splitk", "mhc_pre",
+        "mhc_post_tilelang_official", "mhc_post",
+        "fusedmoe_pytorch", "fusedmoe_pytorch_compiled", "fusedmoe_tilelang", "generate_fusedmoe_inputs",
+        "FusedMoETileLang",
+    ]
+    missing = [n for n in reference_all if not callable(getattr(K, n, None))]
+    assert not missing, missing
+    assert set(reference_all) <= set(K.__all__)

@@ -242,3 +242,22 @@ def test_few_token_router_split_along_k(cuda, lib, T, H, E, K, dtype, mode):
     assert torch.equal(s32, s)
     if T >= 64:   # with inputs on a coarse grid the split sums are exact, so they equal the unsplit GEMM's logits
         assert torch.equal(lg, ops.router_logits(X, W))
+
+
+def test_variant_names_of_the_reference_follow_their_conventions(cuda, lib):
+    """The reference's other public names: fused / selection / sonic / bitonic select first and normalise over the k
+    chosen, separate / tilelang_separate normalise over all experts first, topk_radix_tilelang returns indices only."""
+    from tilelang_moe_b200 import kernels as K
+    logits = torch.randn(333, 160, generator=torch.Generator().manual_seed(5))
+    sB, iB = O.topk_softmax(logits, 6, "B")
+    sA, iA = O.topk_softmax(logits, 6, "A")
+    d = logits.to(cuda)
+    for f in (K.topk_softmax_fused, K.topk_softmax_selection, K.topk_softmax_sonic, K.topk_softmax_bitonic, K.topk_softmax_best):
+        s, i = f(d, 6)
+        assert torch.equal(i.cpu(), iB)
+        torch.testing.assert_close(s.cpu(), sB, rtol=1e-6, atol=1e-30)
+    for f in (K.topk_softmax_separate, K.topk_softmax_separate_compiled, K.topk_softmax_tilelang_separate):
+        s, i = f(d, 6)
+        assert torch.equal(i.cpu(), iA)
+        torch.testing.assert_close(s.cpu(), sA, rtol=1e-6, atol=1e-30)
+    assert torch.equal(K.topk_radix_tilelang(d, 6).cpu(), iB)

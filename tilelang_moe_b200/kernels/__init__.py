@@ -31,6 +31,13 @@ from .. import ops as _ops
 __all__ = [
     "topk_softmax", "topk_softmax_best", "grouped_gemm", "grouped_gemm_best", "fusedmoe_tilelang", "fusedmoe",
     "FusedMoETileLang", "FusedMoE", "generate_fusedmoe_inputs", "route_histogram", "mhc_pre", "mhc_post",
+    # the reference's other public names (its strategy variants and its PyTorch baselines): the same operator each
+    "topk_softmax_fused", "topk_softmax_selection", "topk_softmax_sonic", "topk_softmax_bitonic",
+    "topk_softmax_separate", "topk_softmax_separate_compiled", "topk_softmax_tilelang_separate", "topk_radix_tilelang",
+    "grouped_gemm_loop", "grouped_gemm_loop_compiled", "grouped_gemm_padded", "grouped_gemm_tilelang",
+    "grouped_gemm_pytorch", "fusedmoe_pytorch", "fusedmoe_pytorch_compiled",
+    "mhc_pre_pytorch", "mhc_pre_pytorch_compiled", "mhc_pre_tilelang_official", "mhc_pre_tilelang_optimized",
+    "mhc_pre_tilelang_splitk", "mhc_post_pytorch", "mhc_post_pytorch_compiled", "mhc_post_tilelang_official",
 ]
 
 
@@ -249,3 +256,49 @@ def mhc_post(x: torch.Tensor, residual: torch.Tensor, post_layer_mix: torch.Tens
              comb_res_mix: torch.Tensor) -> torch.Tensor:
     """mHC post block (reference kernels/mhc_tilelang.py:575-582): bf16 (T, hc_mult, hidden)."""
     return _ops.mhc_post(x, residual, post_layer_mix, comb_res_mix)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The reference exports every strategy variant and every PyTorch baseline of an operator under its own name
+# (reference kernels/__init__.py:4-101).  Here each operator has one implementation, so the other names are the same
+# function with the variant's convention: code written against any of them keeps working.
+# ---------------------------------------------------------------------------------------------------------------
+def topk_softmax_fused(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Top-k first, softmax over the k selected (reference kernels/topk_softmax_baseline.py:39-68)."""
+    return topk_softmax(logits, k, mode="B")
+
+
+topk_softmax_selection = topk_softmax_fused     # reference kernels/topk_softmax_tilelang.py:983-1001
+topk_softmax_sonic = topk_softmax_fused         # its alias, :1005
+topk_softmax_bitonic = topk_softmax_fused       # :895-921
+
+
+def topk_softmax_separate(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax over all experts, then top-k (reference kernels/topk_softmax_baseline.py:15-36)."""
+    return topk_softmax(logits, k, mode="A")
+
+
+topk_softmax_separate_compiled = topk_softmax_separate
+topk_softmax_tilelang_separate = topk_softmax_separate     # reference kernels/topk_softmax_tilelang.py:1013-1040
+
+
+def topk_radix_tilelang(logits: torch.Tensor, topk: int = 6) -> torch.Tensor:
+    """Indices of the top-k logits only (reference kernels/topk_softmax_tilelang.py:205-240); int64 here."""
+    return topk_softmax(logits, int(topk), mode="B")[1]
+
+
+grouped_gemm_loop = grouped_gemm               # reference kernels/grouped_gemm_baseline.py:14-57
+grouped_gemm_loop_compiled = grouped_gemm
+grouped_gemm_padded = grouped_gemm             # :60-118
+grouped_gemm_tilelang = grouped_gemm           # reference kernels/grouped_gemm_tilelang.py:606-680
+grouped_gemm_pytorch = grouped_gemm            # :542-603
+fusedmoe_pytorch = fusedmoe_tilelang           # reference kernels/fusedmoe_baseline.py:171-203
+fusedmoe_pytorch_compiled = fusedmoe_tilelang  # :285-308
+mhc_pre_pytorch = mhc_pre                      # reference kernels/mhc_baseline.py:48-127
+mhc_pre_pytorch_compiled = mhc_pre
+mhc_pre_tilelang_official = mhc_pre            # reference kernels/mhc_tilelang.py:363-403
+mhc_pre_tilelang_optimized = mhc_pre           # :406-446
+mhc_pre_tilelang_splitk = mhc_pre              # :449-491
+mhc_post_pytorch = mhc_post                    # reference kernels/mhc_baseline.py:130-170
+mhc_post_pytorch_compiled = mhc_post
+mhc_post_tilelang_official = mhc_post          # reference kernels/mhc_tilelang.py:548-572
