@@ -261,3 +261,30 @@ def test_variant_names_of_the_reference_follow_their_conventions(cuda, lib):
         assert torch.equal(i.cpu(), iA)
         torch.testing.assert_close(s.cpu(), sA, rtol=1e-6, atol=1e-30)
     assert torch.equal(K.topk_radix_tilelang(d, 6).cpu(), iB)
+
+
+@pytest.mark.parametrize("H,E,K", [(3584, 64, 8), (5120, 160, 6)])
+def test_fused_router_factories_of_the_reference_module(cuda, lib, H, E, K):
+    """kernels.router_gemm_topk_softmax as the reference's tests/test_router_fusion_correctness.py uses it: a factory
+    call per shape, then kernel(X[T,H], W[H,E_padded]); pass = every row selects the expert set of
+    topk(X.float() @ W.float())."""
+    from tilelang_moe_b200.kernels import router_gemm_topk_softmax as R
+    torch.manual_seed(0)
+    X = torch.randn(256, H, device=cuda, dtype=torch.bfloat16)
+    W = torch.randn(H, E, device=cuda, dtype=torch.bfloat16)
+    Ep = R._next_pow2(E)
+    Wp = torch.zeros(H, Ep, device=cuda, dtype=torch.bfloat16)
+    Wp[:, :E] = W
+    logits = X.float() @ W.float()
+    vals, ref_i = torch.topk(logits, K, dim=-1)
+    ref_s = torch.softmax(vals, dim=-1)
+    sv = torch.sort(logits, dim=-1, descending=True).values
+    clear = ((sv[:, :K] - sv[:, 1:K + 1]).min(-1).values > 1e-2)          # rows whose order no rounding can change
+    for kern in (R.fused_router_tma_auto_bitonic_kernel(256, H, E, Ep, K, block_M=64, block_K=64, num_stages=2, threads=256),
+                 R.get_fused_router_kernel("cpasync_selection", 256, H, E, K)):
+        scores, idx = kern(X, Wp)
+        ops.check_status(cuda)
+        assert torch.equal(torch.sort(idx[clear], -1).values, torch.sort(ref_i[clear], -1).values)
+        assert (scores[clear] - ref_s[clear]).abs().max().item() < 2e-3
+    with pytest.raises(ValueError):
+        R.get_fused_router_kernel("no_such_algorithm", 256, H, E, K)
