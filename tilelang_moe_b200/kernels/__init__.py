@@ -35,7 +35,8 @@ __all__ = [
     "topk_softmax_fused", "topk_softmax_selection", "topk_softmax_sonic", "topk_softmax_bitonic",
     "topk_softmax_separate", "topk_softmax_separate_compiled", "topk_softmax_tilelang_separate", "topk_radix_tilelang",
     "grouped_gemm_loop", "grouped_gemm_loop_compiled", "grouped_gemm_padded", "grouped_gemm_tilelang",
-    "grouped_gemm_pytorch", "fusedmoe_pytorch", "fusedmoe_pytorch_compiled",
+    "grouped_gemm_pytorch", "fusedmoe_pytorch", "fusedmoe_pytorch_compiled", "fusedmoe_tilelang_streams", "fusedmoe_best",
+    "FusedMoETileLangStreams",
     "mhc_pre_pytorch", "mhc_pre_pytorch_compiled", "mhc_pre_tilelang_official", "mhc_pre_tilelang_optimized",
     "mhc_pre_tilelang_splitk", "mhc_post_pytorch", "mhc_post_pytorch_compiled", "mhc_post_tilelang_official",
 ]
@@ -292,6 +293,9 @@ grouped_gemm_loop_compiled = grouped_gemm
 grouped_gemm_padded = grouped_gemm             # :60-118
 grouped_gemm_tilelang = grouped_gemm           # reference kernels/grouped_gemm_tilelang.py:606-680
 grouped_gemm_pytorch = grouped_gemm            # :542-603
+fusedmoe_tilelang_streams = fusedmoe_tilelang  # reference kernels/fusedmoe_tilelang.py:559-602 (its two-stream variant)
+fusedmoe_best = fusedmoe_tilelang              # :654-690
+FusedMoETileLangStreams = FusedMoETileLang     # :428-556
 fusedmoe_pytorch = fusedmoe_tilelang           # reference kernels/fusedmoe_baseline.py:171-203
 fusedmoe_pytorch_compiled = fusedmoe_tilelang  # :285-308
 mhc_pre_pytorch = mhc_pre                      # reference kernels/mhc_baseline.py:48-127
