@@ -36,7 +36,9 @@ __all__ = [
     "topk_softmax_separate", "topk_softmax_separate_compiled", "topk_softmax_tilelang_separate", "topk_radix_tilelang",
     "grouped_gemm_loop", "grouped_gemm_loop_compiled", "grouped_gemm_padded", "grouped_gemm_tilelang",
     "grouped_gemm_pytorch", "fusedmoe_pytorch", "fusedmoe_pytorch_compiled", "fusedmoe_tilelang_streams", "fusedmoe_best",
-    "FusedMoETileLangStreams",
+    "FusedMoETileLangStreams", "topk_softmax_conv_a_renorm", "topk_softmax_conv_b_unfused",
+    "topk_softmax_conv_b_radix_unfused", "topk_softmax_bitonic_v2", "topk_softmax_bitonic_v3", "grouped_gemm_tilelang_v2",
+    "grouped_gemm_tilelang_v3",
     "mhc_pre_pytorch", "mhc_pre_pytorch_compiled", "mhc_pre_tilelang_official", "mhc_pre_tilelang_optimized",
     "mhc_pre_tilelang_splitk", "mhc_post_pytorch", "mhc_post_pytorch_compiled", "mhc_post_tilelang_official",
 ]
@@ -279,6 +281,15 @@ def topk_softmax_separate(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, t
     return topk_softmax(logits, k, mode="A")
 
 
+def topk_softmax_conv_a_renorm(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Softmax over all experts, top-k, then renormalised to sum 1 (reference kernels/topk_softmax_baseline.py:223-236)."""
+    return topk_softmax(logits, k, mode="A_renorm")
+
+
+topk_softmax_conv_b_unfused = topk_softmax_fused            # reference kernels/topk_softmax_baseline.py:241
+topk_softmax_conv_b_radix_unfused = topk_softmax_fused      # reference kernels/topk_softmax_tilelang.py:1139-1159
+topk_softmax_bitonic_v2 = topk_softmax_fused                # :924-951
+topk_softmax_bitonic_v3 = topk_softmax_fused                # :954-980
 topk_softmax_separate_compiled = topk_softmax_separate
 topk_softmax_tilelang_separate = topk_softmax_separate     # reference kernels/topk_softmax_tilelang.py:1013-1040
 
@@ -293,6 +304,8 @@ grouped_gemm_loop_compiled = grouped_gemm
 grouped_gemm_padded = grouped_gemm             # :60-118
 grouped_gemm_tilelang = grouped_gemm           # reference kernels/grouped_gemm_tilelang.py:606-680
 grouped_gemm_pytorch = grouped_gemm            # :542-603
+grouped_gemm_tilelang_v2 = grouped_gemm        # :682-768
+grouped_gemm_tilelang_v3 = grouped_gemm        # :771-856
 fusedmoe_tilelang_streams = fusedmoe_tilelang  # reference kernels/fusedmoe_tilelang.py:559-602 (its two-stream variant)
 fusedmoe_best = fusedmoe_tilelang              # :654-690
 FusedMoETileLangStreams = FusedMoETileLang     # :428-556
