@@ -29,7 +29,13 @@ def test_fixture(cuda, lib):
 
 @pytest.mark.parametrize("T,k,E,dtype", [(1, 1, 1, torch.int64), (1024, 2, 8, torch.int64), (8192, 8, 256, torch.int32),
                                          (4096, 2, 8, torch.int64), (333, 3, 17, torch.int32), (5000, 6, 160, torch.int64),
-                                         (100000, 4, 64, torch.int32), (70, 8, 1024, torch.int64)])
+                                         (100000, 4, 64, torch.int32), (70, 8, 1024, torch.int64),
+                                         # three-kernel path: more experts than threads in the scan kernel (two chunks);
+                                         # an expert count that leaves scan threads unused (96 -> 10 shares of the
+                                         # units); small units with 16 shares; large units right above the switch
+                                         (3000, 4, 2048, torch.int32), (9000, 8, 96, torch.int64),
+                                         (6000, 8, 40, torch.int32), (8200, 8, 256, torch.int32),
+                                         (1030, 4, 300, torch.int32)])
 def test_shapes(cuda, lib, T, k, E, dtype):
     g = torch.Generator().manual_seed(T + k + E)
     idx = torch.argsort(torch.rand(T, E, generator=g), dim=1)[:, :k].contiguous().to(dtype) if E >= k and T * E < 5e6 \
