@@ -243,6 +243,31 @@ def test_share_counts_fills_every_table_and_its_wait_is_limited(cuda, lib):
     assert torch.equal(tables[1][:8], counts)       # row [0][0] at the narrower width of this call
 
 
+def test_share_counts_builds_the_whole_table_for_eight_ranks(cuda, lib):
+    """Eight ranks' histogram exchange, one rank after the other on one GPU (every rank's flags pre-set to the epoch, so
+    no launch waits for another): afterwards every rank's table holds every rank's vector in the slot of the step."""
+    from tilelang_moe_b200 import ops
+    G, n, extra_n, epoch, slot = 8, 272, 8, 3, 1
+    width = n + extra_n
+    g = torch.Generator().manual_seed(1)
+    vecs = [torch.randint(0, 500, (width,), generator=g, dtype=torch.int32).to(cuda) for _ in range(G)]
+    tables = [torch.full((2 * G * width,), -7, dtype=torch.int32, device=cuda) for _ in range(G)]
+    flags = [torch.zeros(64, dtype=torch.int32, device=cuda) for _ in range(G)]
+    for f in flags:
+        f[3 * 16:3 * 16 + G] = epoch
+    tptrs = ops._ptr_array([t.data_ptr() for t in tables])
+    fptrs = ops._ptr_array([f.data_ptr() for f in flags])
+    for r in range(G):
+        ops.ep_share_counts(vecs[r][:n].contiguous(), vecs[r][n:].contiguous(), tptrs, slot, fptrs, r, 3, epoch, timeout_us=2000)
+    torch.cuda.synchronize(cuda)
+    ops.check_status(cuda)
+    want = torch.stack(vecs)
+    for t in tables:
+        v = t.view(2, G, width)
+        assert torch.equal(v[slot], want)
+        assert bool((v[1 - slot] == -7).all())
+
+
 def test_dispatch_ignores_entries_with_an_expert_id_out_of_range(cuda, lib):
     """One routed entry carries id -1: the histogram reports it (status 1) and leaves it out of the permutation; the
     dispatch kernels must then stop at the live entries - nothing is read through the unwritten tail of the permutation
