@@ -69,6 +69,7 @@ class ClockSampler:
     def __init__(self, index: int, period_s: float = 0.004):
         period_s = float(os.environ.get("MOE_B200_CLOCK_PERIOD_MS", period_s * 1e3)) / 1e3
         self.index, self.period, self.samples, self.reasons = index, period_s, [], set()
+        self.power_w, self.power_limit_w, self.sm_min = [], None, None
         self.max_mhz, self._stop, self._thread, self._nvml, self.proc = None, threading.Event(), None, None, None
 
     def start(self):
@@ -82,6 +83,10 @@ class ClockSampler:
                 phys = int(vis.split(",")[self.index])
             self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            try:
+                self.power_limit_w = pynvml.nvmlDeviceGetEnforcedPowerLimit(self._h) / 1000.0
+            except Exception:
+                self.power_limit_w = None
             self._nvml = pynvml
             self._thread = threading.Thread(target=self._loop, daemon=True)
             self._thread.start()
@@ -99,9 +104,21 @@ class ClockSampler:
                 for name, bit in self.REASONS:
                     if mask & bit:
                         self.reasons.add(name)
+                self.power_w.append(self._power(nv))
             except Exception:
                 pass
             time.sleep(self.period)
+
+    def _power(self, nv):
+        """Board power in watts (a read-only query): the instantaneous field where the driver offers it, else the
+        one-second average."""
+        try:
+            v = nv.nvmlDeviceGetFieldValues(self._h, [nv.NVML_FI_DEV_POWER_INSTANT])[0]
+            if v.nvmlReturn == 0:
+                return v.value.uiVal / 1000.0
+        except Exception:
+            pass
+        return nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0
 
     def _start_smi(self):
         q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
@@ -132,8 +149,15 @@ class ClockSampler:
         if self.proc is not None:
             self.proc.terminate()
         sm = self.samples
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz, "samples": len(sm),
-                "reasons": sorted(self.reasons), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
+        out = {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz, "samples": len(sm),
+               "reasons": sorted(self.reasons), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
+        if sm:
+            out["sm_mhz_min"] = min(sm)
+        if self.power_w:
+            out["power_w"] = round(statistics.median(self.power_w), 1)
+            out["power_w_max"] = round(max(self.power_w), 1)
+            out["power_limit_w"] = self.power_limit_w
+        return out
 
 
 # --------------------------------------------------------------------------------------- inputs
@@ -413,6 +437,7 @@ def run_ours(args, wl_name, cfg):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         stage_events = []
         sampler.samples.clear()            # keep only what is sampled while the timed steps run
+        sampler.power_w.clear()
         e0.record()
         h0 = time.perf_counter()
         for _ in range(steps):
