@@ -288,3 +288,6 @@ def test_fused_router_factories_of_the_reference_module(cuda, lib, H, E, K):
         assert (scores[clear] - ref_s[clear]).abs().max().item() < 2e-3
     with pytest.raises(ValueError):
         R.get_fused_router_kernel("no_such_algorithm", 256, H, E, K)
+    lg = R.get_router_gemm_kernel(256, H, E)(X, W)                         # the stand-alone router GEMM of the same module
+    assert lg.dtype == torch.float32 and lg.shape == (256, E)
+    torch.testing.assert_close(lg, logits, rtol=1e-4, atol=1e-3)

@@ -59,6 +59,16 @@ def get_fused_router_kernel(algo: str, num_tokens: int, H: int, E: int, top_k: i
     return _make(num_tokens, H, E, top_k)
 
 
+def get_router_gemm_kernel(num_tokens: int, H: int, E: int, dtype=None):
+    """Callable(X[T,H], W[H,E]) -> fp32 logits [T,E]: the stand-alone router GEMM (reference :79-146), here
+    ``ops.router_logits`` with fp32 accumulation."""
+    def kernel(X: torch.Tensor, W: torch.Tensor) -> torch.Tensor:
+        if X.shape != (num_tokens, H) or W.shape[0] != H or W.shape[1] < E:
+            raise ValueError(f"built for X [{num_tokens},{H}] and W [{H},>={E}], got {tuple(X.shape)} and {tuple(W.shape)}")
+        return _ops.router_logits(X, _weight_eh(W, E))
+    return kernel
+
+
 def _factory(num_tokens, H, E, E_padded, top_k, block_M=64, block_K=64, num_stages=2, threads=256, dtype=None):
     """The reference's per-algorithm factories take the padded expert count as well (:149, :270, :487, :639, :858, :971)."""
     return _make(num_tokens, H, E, top_k)
