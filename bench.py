@@ -412,10 +412,14 @@ def run_ours(args, wl_name, cfg):
                              "+ down-GEMM epilogue over NVLink peer memory",
                "nccl": "NCCL all-to-all"}[args.exchange]
         per = runner.experts_per_rank
-        parallelism = (f"ep{world}: {min(per)}-{max(per)} experts per GPU (placed by row tiles of a calibration batch), "
+        experts = f"{per[0]} experts per GPU" if len(set(per)) == 1 else f"{min(per)}-{max(per)} experts per GPU"
+        parallelism = (f"ep{world}: {experts} (placed from the loads of a calibration batch), "
                        f"tokens split {T // world} per rank, {how}")
         imbalance = {"rows": runner.imbalance, "modelled_time": runner.cost_imbalance,
-                     "placement": "load-aware (row tiles of a calibration batch of the same popularity law; a rank may hold up to a quarter more experts than E / ranks)",
+                     "experts_per_gpu": runner.experts_per_rank,
+                     "placement": "load-aware, from a calibration batch of the same popularity law: E / ranks experts per GPU with rows "
+                                  "balanced, or - where that leaves one GPU clearly more row tiles than the others - row tiles "
+                                  "balanced with up to a quarter more experts than E / ranks on a GPU",
                      "contiguous_placement_would_give": {"rows": runner.contiguous_imbalance[0],
                                                          "modelled_time": runner.contiguous_imbalance[1]}}
 
@@ -515,6 +519,22 @@ def run_ours(args, wl_name, cfg):
                             "memory, both directions together), nothing else running: the time below which no "
                             "arrangement of the steps can bring e2e on this box"}
         del src, dst, din, dout
+
+    # the same steps with exactly E / ranks experts on every GPU (rows of the calibration batch balanced under that rule),
+    # beside the default placement, which lets the rank of a very popular expert hold fewer of the others
+    equal_count = None
+    if world > 1 and not args.no_extra and len(set(runner.experts_per_rank)) > 1:
+        r2 = ep.EPRunner(cfg, rank, world, dev, make_weights, placement="rows", exchange=args.exchange)
+        step2 = r2.bench_closures(x_cpu, logits_cpu)[0]
+        for _ in range(3):
+            step2()
+        blocks2 = [timed(step2, args.steps)[0] for _ in range(5)]
+        ops.check_status(dev)
+        equal_count = {"experts_per_gpu": E // world, "ms_per_step": round(statistics.median(blocks2) / args.steps, 4),
+                       "tokens_per_s": round(tokens_per_step * args.steps / (statistics.median(blocks2) * 1e-3)),
+                       "blocks": len(blocks2), "rows_max_over_mean": r2.imbalance}
+        del r2, step2
+        torch.cuda.empty_cache()
 
     # per-stage device time from the events recorded inside the timed steps
     stages = {}
@@ -650,6 +670,7 @@ def run_ours(args, wl_name, cfg):
         "roofline": roofline,
         "clocks": clocks,
         "parity": parity,
+        **({"equal_count_placement": equal_count} if equal_count is not None else {}),
         **extra,
     }
     if world > 1:
