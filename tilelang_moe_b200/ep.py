@@ -291,9 +291,18 @@ def ep_forward_peer(x_local: torch.Tensor, logits_local: torch.Tensor, k: int, p
     bufs = {} if bufs is None else bufs
     with st("route"):
         scores, idx32 = ops.topk_softmax(logits_local, k, mode="A", index_dtype=torch.int32)
+        if px.dedup:   # numbering the tokens per destination needs the top-k ids only: it runs beside the histogram kernels
+            cur = torch.cuda.current_stream(x_local.device)
+            fork = torch.cuda.Event()
+            fork.record(cur)
+            with torch.cuda.stream(px.side):
+                px.side.wait_event(fork)
+                urank, ucount = ops.ep_unique(idx32, id_map_dev, El, G, out=px.uniq_bufs)
+                numbered = torch.cuda.Event()
+                numbered.record(px.side)
         counts, offsets, perm, inv = ops.route_histogram(idx32, E, id_map=id_map_dev, workspace=bufs.get("hist_ws"))
         if px.dedup:
-            urank, ucount = ops.ep_unique(idx32, id_map_dev, El, G, out=px.uniq_bufs)
+            cur.wait_event(numbered)
     with st("counts_allgather"):
         if px.dedup:
             cnt_all = _share_counts(px, ops, counts, ucount)
