@@ -348,6 +348,18 @@ int moe_grouped_gemm_peer_scatter(const void* A, const void* B, const int32_t* o
  */
 int moe_debug_wait_probe(int64_t limit_us, int32_t* status, int32_t* outcome, void* stream);
 
+/* ---- index checks of the checked build ---------------------------------------------------------
+ * No counterpart in the reference.  A build of the library with -DMOE_BOUNDS_CHECK (python -m tilelang_moe_b200.build
+ * --check -> libmoe_b200_check.so, same ABI) compares every row index it takes out of an index table with the size of
+ * the buffer it addresses before following it: scatter destinations (site 1) and gather sources (site 2) of the
+ * grouped GEMMs, the row table of moe_combine (site 3).  An index outside the buffer is not followed (the store is
+ * skipped, the gather reads the last row instead, the combine adds nothing) and the first one is remembered.
+ * This call waits for `stream`, writes {4, site, index} of the first such index since the last call (or {0,0,0})
+ * to the host array out3, clears the record, and returns 1 in the checked build, 0 in the normal one (whose kernels
+ * carry no checks and always report {0,0,0}).
+ */
+int moe_debug_bounds_status(int32_t* out3, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -39,6 +39,7 @@ SIGNATURES = {
     "moe_ep_share_counts": (_i32, [_vp, _i32, _vp, _i32, C.POINTER(C.c_void_p), _i32, C.POINTER(C.c_void_p), _i32, _i32,
                                    _i32, _i32, _i64, _vp, _vp]),
     "moe_debug_wait_probe": (_i32, [_i64, _vp, _vp, _vp]),
+    "moe_debug_bounds_status": (_i32, [C.POINTER(C.c_int32), _vp]),
     "moe_grouped_gemm_peer_scatter": (_i32, [_vp, _vp, _vp, _vp, _vp, C.POINTER(C.c_void_p), _i32, _i64, _i64, _i64,
                                              _i32, _i32, _i32, _i32, _vp, _vp]),
     "moe_layer_workspace": (_sz, [_i64, _i32, _i32, _i32, _i32, _i32]),

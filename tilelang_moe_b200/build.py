@@ -39,22 +39,26 @@ def sources():
     return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
 
 
-def needs_build() -> bool:
-    if not LIB.exists():
+def needs_build(lib: Path = None) -> bool:
+    lib = LIB if lib is None else lib
+    if not lib.exists():
         return True
-    t = LIB.stat().st_mtime
+    t = lib.stat().st_mtime
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "moe_b200.h"]
     return any(d.stat().st_mtime > t for d in deps if d.exists())
 
 
 TRACE_LIB = PKG / "libmoe_b200_trace.so"   # --trace: same sources with -DMOE_GEMM_TRACE (tile timeline tool only)
+CHECK_LIB = PKG / "libmoe_b200_check.so"   # --check: same sources with -DMOE_BOUNDS_CHECK (index-checked accesses)
 
 
-def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Path:
-    if not trace and not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, trace: bool = False, check: bool = False) -> Path:
+    if check and not force and CHECK_LIB.exists() and not needs_build(CHECK_LIB):
+        return CHECK_LIB
+    if not trace and not check and not force and not needs_build():
         return LIB
     objs = []
-    obj_dir = PKG / ("build_trace" if trace else "build")
+    obj_dir = PKG / ("build_trace" if trace else ("build_check" if check else "build"))
     obj_dir.mkdir(exist_ok=True)
     procs = []
     for src in sources():
@@ -62,6 +66,8 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Pa
         cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
         if trace:
             cmd.insert(1, "-DMOE_GEMM_TRACE")
+        if check:
+            cmd.insert(1, "-DMOE_BOUNDS_CHECK")
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -77,7 +83,7 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Pa
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("nvcc compilation failed")
-    target = TRACE_LIB if trace else LIB
+    target = TRACE_LIB if trace else (CHECK_LIB if check else LIB)
     link = [_nvcc(), "-shared", "-o", str(target), *[str(o) for o in objs], "-gencode",
             "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -87,5 +93,6 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> Pa
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv,
+                 check="--check" in sys.argv)
     print(path)

@@ -45,7 +45,39 @@ enum : int {
   ST_BAD_EXPERT_ID = 1,     // an expert id outside [0,E) was seen
   ST_WAIT_TIMEOUT = 2,      // a bounded barrier wait gave up; status[1] = site
   ST_INTERNAL = 3,
+  ST_BAD_INDEX = 4,         // checked build only: an index-driven access outside its buffer was skipped
 };
+
+// ---- index checks of the checked build (-DMOE_BOUNDS_CHECK) ---------------------
+// Every store or load whose row comes out of an index table (scatter destinations and gather sources of the grouped
+// GEMMs, the row table of the combine) is compared with the size of its buffer first.  An index outside it is not
+// followed: the access is skipped, and {ST_BAD_INDEX, site, index} is left in a status block of the translation unit
+// (read and cleared by moe_debug_bounds_status).  Sites: 1 GEMM scatter destination, 2 GEMM gather source, 3 combine
+// row table.  The normal build compiles the checks away.
+#ifdef MOE_BOUNDS_CHECK
+static __device__ int32_t g_bounds_status[4];
+__device__ __forceinline__ bool moe_index_ok(int64_t i, int64_t n, int site) {
+  if (i >= 0 && i < n) return true;
+  if (atomicCAS(&g_bounds_status[0], 0, (int)ST_BAD_INDEX) == 0) { g_bounds_status[1] = site; g_bounds_status[2] = (int32_t)i; }
+  return false;
+}
+#define MOE_INDEX_OK(i, n, site) ::moe::moe_index_ok((int64_t)(i), (int64_t)(n), (site))
+// host side of one translation unit: copy the block out (after the stream's work) and clear it
+static inline int bounds_status_read(int32_t* out3, cudaStream_t st) {
+  int32_t h[4] = {0, 0, 0, 0};
+  const int32_t zero[4] = {0, 0, 0, 0};
+  MOE_CUDA_CHECK(cudaStreamSynchronize(st));
+  MOE_CUDA_CHECK(cudaMemcpyFromSymbol(h, g_bounds_status, sizeof(h)));
+  MOE_CUDA_CHECK(cudaMemcpyToSymbol(g_bounds_status, zero, sizeof(zero)));
+  out3[0] = h[0]; out3[1] = h[1]; out3[2] = h[2];
+  return MOE_OK;
+}
+#else
+#define MOE_INDEX_OK(i, n, site) true
+static inline int bounds_status_read(int32_t* out3, cudaStream_t) { out3[0] = out3[1] = out3[2] = 0; return MOE_OK; }
+#endif
+int bounds_status_gemm(int32_t* out3, cudaStream_t st);     // gemm_sm100.cu
+int bounds_status_route(int32_t* out3, cudaStream_t st);    // route.cu
 
 // ---- order-preserving float <-> uint32 key -----------------------------------
 // Larger float -> larger key.  -0.0 is folded into +0.0 and every NaN maps to the

@@ -129,6 +129,7 @@ struct Params {
   int l2_hints = 0;        // 128-row kernel: 0 none, 1 evict-first for weights read once, 2 + evict-last for shared weights
   int mixed = 0;           // 128-row kernel: single-tile and multi-tile experts interleaved in the tile order
   int m64 = 0;             // 128-row kernel: tiles with at most 64 live rows as M = 64 instructions
+  int64_t y_rows = 0;      // rows of Y when dst_rows scatters into it (the checked build compares every destination with it)
 };
 
 // ------------------------------------------------------------------------------ PTX wrappers
@@ -586,8 +587,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int s = 0; s < 2; ++s) {
           int r = t.row0 + half_row0 + lane + 32 * s;
           if (r > p.a_rows - 1) r = p.a_rows - 1;
-          const uint32_t v = (uint32_t)p.a_gather[r] / (uint32_t)p.a_div;
-          src_row[s] = v < (uint32_t)p.a_src_rows ? v : (uint32_t)(p.a_src_rows - 1);
+          uint32_t v = (uint32_t)p.a_gather[r] / (uint32_t)p.a_div;
+          if (v >= (uint32_t)p.a_src_rows) {      // never followed: the last row stands in (the checked build reports it)
+            (void)MOE_INDEX_OK(v, p.a_src_rows, 2);
+            v = (uint32_t)(p.a_src_rows - 1);
+          }
+          src_row[s] = v;
         }
         const unsigned char* rp[16];
         uint32_t live = 0;                                                  // bit `it`: that row belongs to the group
@@ -631,13 +636,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // sorted row handled by this thread; an M = 64 tile keeps rows 16q .. 16q+15 in the first 16 lanes of quarter q
       const bool m64 = MT == 1 && p.m64 && t.row_end - t.row0 <= 64;
       const int grow = m64 ? t.row0 + q * 16 + lane : t.row0 + half * BM + q * 32 + lane;
-      const bool row_ok = grow < t.row_end && (!m64 || lane < 16);
+      bool row_ok = grow < t.row_end && (!m64 || lane < 16);
       const int n0 = p.ksplit ? 0 : t.n_tile * OUT_COLS;
       int64_t out_row = grow;
       float w = 1.0f;
       void* ybase = p.Y;
       if (row_ok) {
-        if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) out_row = p.dst_rows[grow];
+        if (EPI != MOE_GEMM_SILU_GATE && p.dst_rows) {
+          out_row = p.dst_rows[grow];
+          if (EPI != EPI_PEER && !MOE_INDEX_OK(out_row, p.y_rows, 1)) { row_ok = false; out_row = grow; }
+        }
+      }
+      if (row_ok) {
         if (EPI == MOE_GEMM_SCALE_SCATTER) {
           if (p.w_slots > 0) {   // destination rows in runs of w_slots + 1 per token; the run's last row weighs 1
             const int64_t tok = out_row / (p.w_slots + 1);
@@ -1111,14 +1121,19 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       // the upper lanes the second half of the columns
       const int grow = t.row0 + (light ? (int)rank * (BM / 2) + (l & 63) : (int)rank * BM + l);
       const int col_half = light ? (l >> 6) : 0;
-      const bool row_ok = grow < t.row_end;
+      bool row_ok = grow < t.row_end;
       const bool any_rows = t.row0 + (light ? (int)rank * (BM / 2) + (q & 1) * 32 : (int)rank * BM + q * 32) < t.row_end;
       const int n0 = t.n_tile * OUT_COLS;
       int64_t out_row = grow;
       float w = 1.0f;
       void* ybase = p.Y;
       if (row_ok) {
-        if (!GATE && p.dst_rows) out_row = p.dst_rows[grow];
+        if (!GATE && p.dst_rows) {
+          out_row = p.dst_rows[grow];
+          if (EPI != EPI_PEER && !MOE_INDEX_OK(out_row, p.y_rows, 1)) { row_ok = false; out_row = grow; }
+        }
+      }
+      if (row_ok) {
         if (EPI == MOE_GEMM_SCALE_SCATTER) {
           if (p.w_slots > 0) {   // destination rows in runs of w_slots + 1 per token; the run's last row weighs 1
             const int64_t tok = out_row / (p.w_slots + 1);
@@ -1513,6 +1528,7 @@ static int grouped_gemm_impl(int epilogue, const void* A, const void* B, const v
   for (int g = 0; g < 16; ++g) p.peer_base[g] = (peer_base && g < n_peers) ? peer_base[g] : nullptr;
   p.w_by_dst = w_by_dst;
   p.w_slots = ga.w_slots;
+  p.y_rows = max_rows;     // a scatter permutes the sorted rows: the output has as many rows as the sorted input
   p.dense_rows = (int)ga.dense_rows;
   p.a_gather = ga.idx; p.a_src = A; p.a_div = ga.div; p.a_src_rows = (int)ga.src_rows; p.a_rows = (int)max_rows;
   // measured on the DeepSeek-V3-shaped layer: eviction hints on the weight loads 3 % of the step, the mixed tile order
@@ -1604,6 +1620,8 @@ __global__ void __launch_bounds__(32) wait_probe_kernel(unsigned long long limit
 }
 }  // namespace gemm
 }  // namespace moe
+
+int moe::bounds_status_gemm(int32_t* out3, cudaStream_t st) { return moe::bounds_status_read(out3, st); }
 
 extern "C" int moe_debug_wait_probe(int64_t limit_us, int32_t* status, int32_t* outcome, void* stream) {
   using namespace moe;

@@ -344,7 +344,8 @@ combine_kernel(const uint4* __restrict__ Yk, const uint4* __restrict__ shared, c
         if (s0 + u < k) {
           const int64_t f = t * k + s0 + u;
           const int64_t r = row_of ? (int64_t)row_of[f] : f;
-          y[u] = __ldg(Yk + r * vec_per_row + v);
+          if (!row_of || MOE_INDEX_OK(r, T * k, 3)) y[u] = __ldg(Yk + r * vec_per_row + v);
+          else y[u] = make_uint4(0u, 0u, 0u, 0u);            // checked build: a row outside Yk contributes nothing
           w[u] = scale ? scale[f] : 1.0f;
         }
       }
@@ -1213,6 +1214,26 @@ extern "C" int moe_ep_barrier(void* const* peer_flags, int G, int my_rank, int c
                                                                           (unsigned long long)timeout_us * 1000ull, status);
   MOE_CHECK_LAUNCH("ep_barrier_kernel");
   return MOE_OK;
+}
+
+int moe::bounds_status_route(int32_t* out3, cudaStream_t st) { return moe::bounds_status_read(out3, st); }
+
+extern "C" int moe_debug_bounds_status(int32_t* out3, void* stream) {
+  using namespace moe;
+  if (!out3) return fail(MOE_ERR_ARG, "debug_bounds_status: null pointer");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int32_t a[3], b[3];
+  int rc = bounds_status_gemm(a, st);
+  if (rc) return rc;
+  rc = bounds_status_route(b, st);
+  if (rc) return rc;
+  const int32_t* first = a[0] ? a : b;
+  out3[0] = first[0]; out3[1] = first[1]; out3[2] = first[2];
+#ifdef MOE_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
 }
 
 extern "C" int moe_ep_share_counts(const int32_t* counts, int n_counts, const int32_t* extra, int n_extra,

@@ -547,6 +547,18 @@ def ep_share_counts(counts: torch.Tensor, extra: Optional[torch.Tensor], peer_ta
     _lib.check(rc, "moe_ep_share_counts")
 
 
+def debug_bounds_status(device: torch.device):
+    """(checked_build, [code, site, index]): what the index checks of the checked build (libmoe_b200_check.so, loaded
+    through MOE_B200_LIBRARY) recorded since the last call; the normal build reports (False, [0, 0, 0])."""
+    import ctypes
+    out = (ctypes.c_int32 * 3)()
+    with torch.cuda.device(device):
+        rc = _lib.load().moe_debug_bounds_status(out, _stream())
+    if rc < 0:
+        _lib.check(rc, "moe_debug_bounds_status")
+    return bool(rc), [int(out[0]), int(out[1]), int(out[2])]
+
+
 def debug_wait_probe(device: torch.device, limit_us: int = 1000) -> int:
     """Run the bounded-wait self-test kernel; returns 1 if the wait succeeded (it cannot), 0 if it ran out."""
     outcome = torch.full((1,), -1, dtype=torch.int32, device=device)
